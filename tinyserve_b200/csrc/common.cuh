@@ -1,0 +1,88 @@
+// Shared helpers of the sm_100a kernels: error reporting through return codes and a
+// per-library message, element types, conversions, warp and block reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define TS_EXPORT extern "C" __attribute__((visibility("default")))
+
+// element type codes shared with the Python bindings
+enum TsDtype : int { TS_F32 = 0, TS_BF16 = 1 };
+
+static thread_local char ts_error_message[512] = "";
+
+static inline int ts_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(ts_error_message, sizeof(ts_error_message), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+#define TS_REQUIRE(cond, ...) \
+  do {                        \
+    if (!(cond)) return ts_fail(__VA_ARGS__); \
+  } while (0)
+
+#define TS_CHECK_LAUNCH(name)                                                   \
+  do {                                                                          \
+    cudaError_t e_ = cudaGetLastError();                                        \
+    if (e_ != cudaSuccess) return ts_fail("%s: %s", name, cudaGetErrorString(e_)); \
+  } while (0)
+
+#define TS_DEFINE_LAST_ERROR() \
+  TS_EXPORT const char* ts_last_error() { return ts_error_message; }
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// a weight vector that is either float or bfloat16, chosen at run time
+struct VecParam {
+  const void* ptr;
+  int is_f32;
+  __device__ __forceinline__ float operator[](int i) const {
+    return is_f32 ? static_cast<const float*>(ptr)[i]
+                  : __bfloat162float(static_cast<const __nv_bfloat16*>(ptr)[i]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < warps ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}

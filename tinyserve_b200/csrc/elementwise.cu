@@ -1,0 +1,260 @@
+// Memory-bound kernels of the forward pass: embedding lookup, (residual add +) RMSNorm,
+// gated activation, and the fused per-head norm + rotary encoding + cache write.
+// All arithmetic is 32-bit; T is the storage type of activations (float or bfloat16).
+//
+// Reference behaviour: tinykernels.py:26-61 (residual add + RMSNorm), 107-218 (q/k norm,
+// RoPE, cache write in one kernel), 277-297 (SiLU * up); serve.py:1239 (embedding).
+#include "common.cuh"
+
+TS_DEFINE_LAST_ERROR()
+
+// ------------------------------------------------------------------ embedding
+template <typename T>
+__global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int n, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * n;
+  if (id < 0 || id >= vocab) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = 0.f;
+    return;
+  }
+  const T* src = table + (size_t)id * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, float* out,
+                              int num_tokens, int n, int vocab, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && n > 0 && vocab > 0, "embed_lookup: empty input");
+  const int threads = n >= 1024 ? 256 : 128;
+  if (dtype == TS_F32)
+    embed_lookup_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, out, n, vocab);
+  else if (dtype == TS_BF16)
+    embed_lookup_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, n, vocab);
+  else
+    return ts_fail("embed_lookup: unknown dtype %d", dtype);
+  TS_CHECK_LAUNCH("embed_lookup");
+  return 0;
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// One block per output row.  v = residual[r] + x[r] (x may be null), residual[r] = v when
+// `write_residual`, out[i] = v * rsqrt(mean(v^2) + eps) * w.  With `rows`, output row i reads
+// input row rows[i].  The order of the sum depends on n and the block size only.
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
+                                   VecParam w, float eps, T* __restrict__ out,
+                                   const int* __restrict__ rows, int n, int write_residual) {
+  __shared__ float scratch[33];
+  const int i = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  const T* xr = x ? x + r * n : nullptr;
+  float* rr = residual + r * n;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = rr[c];
+    if (xr) v += to_f32<T>(xr[c]);
+    acc += v * v;
+  }
+  const float total = block_sum(acc, scratch);
+  const float rstd = rsqrtf(total / (float)n + eps);
+  T* o = out + (size_t)i * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = rr[c];
+    if (xr) v += to_f32<T>(xr[c]);
+    if (write_residual) rr[c] = v;
+    o[c] = from_f32<T>(v * rstd * w[c]);
+  }
+}
+
+TS_EXPORT int ts_add_rmsnorm(int dtype, const void* x, float* residual, const void* weight,
+                             int weight_is_f32, float eps, void* out, const int* rows,
+                             int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+  TS_REQUIRE(num_out_rows > 0 && n > 0, "add_rmsnorm: empty input");
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  VecParam w{weight, weight_is_f32};
+  if (dtype == TS_F32)
+    add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>((const float*)x, residual, w, eps, (float*)out, rows, n, write_residual);
+  else if (dtype == TS_BF16)
+    add_rmsnorm_kernel<__nv_bfloat16><<<num_out_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, residual, w, eps, (__nv_bfloat16*)out, rows, n, write_residual);
+  else
+    return ts_fail("add_rmsnorm: unknown dtype %d", dtype);
+  TS_CHECK_LAUNCH("add_rmsnorm");
+  return 0;
+}
+
+// plain RMSNorm of rows stored as T
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, VecParam w, float eps, T* __restrict__ out,
+                               int n) {
+  __shared__ float scratch[33];
+  const T* xr = x + (size_t)blockIdx.x * n;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = to_f32<T>(xr[c]);
+    acc += v * v;
+  }
+  const float rstd = rsqrtf(block_sum(acc, scratch) / (float)n + eps);
+  T* o = out + (size_t)blockIdx.x * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    o[c] = from_f32<T>(to_f32<T>(xr[c]) * rstd * w[c]);
+}
+
+TS_EXPORT int ts_rmsnorm(int dtype, const void* x, const void* weight, int weight_is_f32, float eps,
+                         void* out, int num_rows, int n, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && n > 0, "rmsnorm: empty input");
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : (n >= 64 ? 128 : 32));
+  VecParam w{weight, weight_is_f32};
+  if (dtype == TS_F32)
+    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>((const float*)x, w, eps, (float*)out, n);
+  else if (dtype == TS_BF16)
+    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, w, eps, (__nv_bfloat16*)out, n);
+  else
+    return ts_fail("rmsnorm: unknown dtype %d", dtype);
+  TS_CHECK_LAUNCH("rmsnorm");
+  return 0;
+}
+
+// ------------------------------------------------------------------ gated activation
+// in [rows, 2 * inter] = gate | up  ->  out [rows, inter] = act(gate) * up
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+
+__device__ __forceinline__ float activate(float g, int act) {
+  if (act == ACT_SILU) return g / (1.f + expf(-g));
+  const float c = 0.7978845608028654f;
+  return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+
+template <typename T>
+__global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
+                                        int act) {
+  const size_t row = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= inter) return;
+  const T* r = in + row * 2 * inter;
+  out[row * inter + c] = from_f32<T>(activate(to_f32<T>(r[c]), act) * to_f32<T>(r[inter + c]));
+}
+
+TS_EXPORT int ts_gated_activation(int dtype, const void* in, void* out, int num_rows, int inter,
+                                  int act, cudaStream_t stream) {
+  TS_REQUIRE(num_rows > 0 && inter > 0, "gated_activation: empty input");
+  TS_REQUIRE((inter + 255) / 256 <= 65535, "gated_activation: width %d is too large", inter);
+  TS_REQUIRE(act == ACT_SILU || act == ACT_GELU_TANH, "gated_activation: unknown activation %d", act);
+  dim3 grid(num_rows, (inter + 255) / 256);
+  if (dtype == TS_F32)
+    gated_activation_kernel<float><<<grid, 256, 0, stream>>>((const float*)in, (float*)out, inter, act);
+  else if (dtype == TS_BF16)
+    gated_activation_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, act);
+  else
+    return ts_fail("gated_activation: unknown dtype %d", dtype);
+  TS_CHECK_LAUNCH("gated_activation");
+  return 0;
+}
+
+// ------------------------------------------------------------------ q/k norm + rotary + cache write
+// qkv [T, (H + 2 Hkv) * D]: q heads, k heads, v heads.  One warp per (token, head):
+//   q heads: optional RMSNorm over D, rotary, stored to q_out [T, H, D];
+//   k heads: the same, stored to the key page of the token's slot;
+//   v heads: copied to the value page.
+// A slot of -1 writes nothing.  Cache layout: [page, kv_head, slot, D].
+struct RopeArgs {
+  const float* cos;   // [positions, rotary_dim / 2]
+  const float* sin;
+  int rotary_dim;     // 0: no rotary
+  int interleaved;    // pairs (2j, 2j+1) instead of (j, j + rotary_dim / 2)
+};
+
+template <typename T>
+__global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                            const int* __restrict__ positions, RopeArgs rope,
+                                            VecParam qw, VecParam kw, int has_norm, float eps,
+                                            int H, int Hkv, int D, T* __restrict__ k_cache,
+                                            T* __restrict__ v_cache,
+                                            const int* __restrict__ slot_mapping, int page_size,
+                                            int heads_total) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= heads_total) return;
+  const int t = blockIdx.x;
+  const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
+  T* dst;
+  bool is_v = false;
+  VecParam w = qw;
+  if (head < H) {
+    dst = q_out + ((size_t)t * H + head) * D;
+  } else {
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const int kvh = head < H + Hkv ? head - H : head - H - Hkv;
+    is_v = head >= H + Hkv;
+    const size_t page = slot / page_size, in_page = slot % page_size;
+    T* base = is_v ? v_cache : k_cache;
+    dst = base + ((page * Hkv + kvh) * page_size + in_page) * D;
+    w = kw;
+  }
+  if (is_v) {
+    for (int i = lane; i < D; i += 32) dst[i] = src[i];
+    return;
+  }
+  float rstd = 1.f;
+  if (has_norm) {
+    float acc = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = to_f32<T>(src[i]);
+      acc += v * v;
+    }
+    rstd = rsqrtf(warp_sum(acc) / (float)D + eps);
+  }
+  const int R = rope.rotary_dim, half = R >> 1;
+  const int pos = positions[t];
+  for (int j = lane; j < half; j += 32) {
+    const int i0 = rope.interleaved ? 2 * j : j;
+    const int i1 = rope.interleaved ? 2 * j + 1 : j + half;
+    float a = to_f32<T>(src[i0]), b = to_f32<T>(src[i1]);
+    if (has_norm) {
+      a = a * rstd * w[i0];
+      b = b * rstd * w[i1];
+    }
+    const float c = rope.cos[(size_t)pos * half + j], s = rope.sin[(size_t)pos * half + j];
+    dst[i0] = from_f32<T>(a * c - b * s);
+    dst[i1] = from_f32<T>(b * c + a * s);
+  }
+  for (int i = R + lane; i < D; i += 32) {
+    float a = to_f32<T>(src[i]);
+    if (has_norm) a = a * rstd * w[i];
+    dst[i] = from_f32<T>(a);
+  }
+}
+
+TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, const int* positions,
+                                      const float* cos, const float* sin, int rotary_dim,
+                                      int interleaved, const void* q_weight, const void* k_weight,
+                                      int weight_is_f32, float eps, int num_tokens, int H, int Hkv,
+                                      int D, void* k_cache, void* v_cache, const int* slot_mapping,
+                                      int page_size, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && Hkv > 0 && D > 0, "qk_norm_rope_kvwrite: empty input");
+  TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
+             "qk_norm_rope_kvwrite: rotary_dim %d does not fit head size %d", rotary_dim, D);
+  TS_REQUIRE((q_weight == nullptr) == (k_weight == nullptr),
+             "qk_norm_rope_kvwrite: q and k norm weights come together");
+  TS_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0),
+             "qk_norm_rope_kvwrite: cache write without a cache");
+  const int heads_total = slot_mapping ? H + 2 * Hkv : H;
+  const int warps = 4;
+  dim3 grid(num_tokens, (heads_total + warps - 1) / warps);
+  RopeArgs rope{cos, sin, rotary_dim, interleaved};
+  VecParam qw{q_weight, weight_is_f32}, kw{k_weight, weight_is_f32};
+  const int has_norm = q_weight != nullptr;
+  if (dtype == TS_F32)
+    qk_norm_rope_kvwrite_kernel<float><<<grid, warps * 32, 0, stream>>>(
+        (const float*)qkv, (float*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D,
+        (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
+  else if (dtype == TS_BF16)
+    qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, positions, rope, qw, kw, has_norm, eps, H,
+        Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
+  else
+    return ts_fail("qk_norm_rope_kvwrite: unknown dtype %d", dtype);
+  TS_CHECK_LAUNCH("qk_norm_rope_kvwrite");
+  return 0;
+}

@@ -1,0 +1,292 @@
+"""The step function: run a batch of (request, its next tokens) from the cache.
+
+``ModelRunner`` owns the model, the device cache, the host cache manager and the
+persistent input buffers.  ``step(entries)`` packs the entries (whole prompts,
+portions of prompts and single decoded tokens, cut anywhere) into one batch, uploads
+it with one copy, runs only those tokens through the model and returns 32-bit logits
+at the wanted places.  Nothing here samples, schedules or decides who runs.
+
+tinyserve's counterpart is ``ModelRunner`` (serve.py:1604-2114): ``_pack`` builds ids,
+positions, slots, query starts, lengths and the block table per request
+(serve.py:1853-1875), ``_upload`` copies them into persistent buffers
+(serve.py:1910-1915) and decode-only batches replay captured graphs
+(serve.py:1969-2053).  It always returns the last row of every request
+(serve.py:1875, 2077); here the caller says which rows it wants."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ..cache.device import DeviceCache
+from ..cache.manager import CacheError, CacheManager, GroupSpec
+from ..config.engine_config import EngineConfig
+from ..config.registry import load_model_config
+from ..kernels import ops
+from ..weights import fill_random_on_device, load_weights
+from .batch import GroupView, StepContext, StepEntry
+from .build import build_model
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class _Runtime:
+    def __init__(self, device, max_positions, dtype):
+        self.device, self.max_positions, self.dtype = device, max_positions, dtype
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, model_config=None, random_weights=False, verbose=False):
+        ops.require_device(cfg.device)
+        self.cfg = cfg
+        self.device = torch.device(cfg.device)
+        self.dtype = _TORCH_DTYPES[cfg.dtype]
+        self.model_config = model_config or load_model_config(cfg.model)
+        self.model = build_model(self.model_config)
+        if random_weights:
+            self.weight_bytes = fill_random_on_device(self.model, self.dtype, self.device, cfg.seed)
+        else:
+            self.weight_bytes = load_weights(self.model, cfg.model, self.dtype, self.device)
+        self.model.prepare(_Runtime(self.device, cfg.max_model_len, self.dtype))
+        self.page_size = cfg.block_size
+        self.max_blocks = -(-cfg.max_model_len // self.page_size)
+        self.num_pages = self._size_cache()
+        self.device_cache = DeviceCache(self.model, self.num_pages, self.page_size,
+                                        cfg.max_num_seqs, self.dtype, self.device)
+        groups = [GroupSpec(s.kind, s.window) for s in self.model.cache_groups]
+        self.manager = CacheManager(groups, self.num_pages, self.page_size, cfg.max_num_seqs)
+        self._make_buffers()
+        self.graphs: dict = {}
+        self.kernel_launches = 0
+        if verbose:
+            print(f"[tinyserve_b200] weights {self.weight_bytes / 2**30:.2f} GiB, "
+                  f"{self.num_pages - 1} pages of {self.page_size} tokens per cache group "
+                  f"({len(groups)} group(s))", flush=True)
+
+    # ------------------------------------------------------------------ set-up
+    def _size_cache(self) -> int:
+        cfg = self.cfg
+        cap = cfg.max_num_seqs * self.max_blocks + 1
+        if cfg.num_blocks:
+            return cfg.num_blocks + 1 if cfg.num_blocks + 1 <= cap else cap
+        per_page = sum(DeviceCache.bytes_per_page(self.model, self.page_size,
+                                                  torch.empty((), dtype=self.dtype).element_size()))
+        if per_page == 0:
+            return 2
+        free, total = torch.cuda.mem_get_info(self.device)
+        # leave room for activations of a full step and for logits
+        reserve = cfg.max_num_batched_tokens * self._activation_bytes_per_token() + \
+            cfg.max_num_seqs * self.model.vocab_size * 8 + (1 << 30)
+        budget = min(total * cfg.gpu_memory_utilization - (total - free), free) - reserve
+        pages = int(budget // per_page)
+        if (pages - 1) * self.page_size < cfg.max_model_len:
+            raise CacheError(
+                f"the cache would hold {max(0, pages - 1) * self.page_size} tokens, fewer than "
+                f"max_model_len {cfg.max_model_len}: lower max_model_len or raise gpu_memory_utilization")
+        return min(pages, cap)
+
+    def _activation_bytes_per_token(self) -> int:
+        widest = self.model.hidden_size
+        for block in self.model.blocks:
+            for part in block.named_parts():
+                for spec in part.param_specs().values():
+                    if len(spec.shape) == 2:
+                        widest = max(widest, spec.shape[0])
+        return 4 * widest * 4
+
+    def _make_buffers(self):
+        cfg = self.cfg
+        N, S = cfg.max_num_batched_tokens, cfg.max_num_seqs
+        G = len(self.model.cache_groups)
+        sizes = [("token_ids", N), ("positions", N), ("logit_rows", N), ("cu_q", S + 1),
+                 ("kv_lens", S), ("state_slots", S), ("fresh", S)]
+        for g in range(G):
+            sizes.append((f"slot_mapping{g}", N))
+        for g in range(G):
+            sizes.append((f"block_table{g}", S * self.max_blocks))
+        self._offsets, total = {}, 0
+        for name, n in sizes:
+            self._offsets[name] = (total, n)
+            total += (n + 3) // 4 * 4
+        self._host = torch.zeros(total, dtype=torch.int32).pin_memory() \
+            if self.device.type == "cuda" else torch.zeros(total, dtype=torch.int32)
+        self._host_np = self._host.numpy()
+        self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+
+    def _seg(self, buf, name, n=None):
+        off, cap = self._offsets[name]
+        return buf[off:off + (cap if n is None else n)]
+
+    # ------------------------------------------------------------------ packing
+    def _pack(self, entries, pad_requests=0, pad_tokens=0):
+        """Fill the host staging buffer; returns a StepContext without device work."""
+        cfg, mgr, ps = self.cfg, self.manager, self.page_size
+        B = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        if B == 0 or T == 0:
+            raise ValueError("a step needs at least one token")
+        Bp, Tp = max(B, pad_requests), max(T, pad_tokens)
+        if Tp > cfg.max_num_batched_tokens:
+            raise ValueError(f"{Tp} tokens in one step, max_num_batched_tokens is {cfg.max_num_batched_tokens}")
+        if Bp > cfg.max_num_seqs:
+            raise ValueError(f"{Bp} requests in one step, max_num_seqs is {cfg.max_num_seqs}")
+        h = self._host_np
+        seg = lambda name, n=None: self._seg(h, name, n)
+        ids, pos, rows = seg("token_ids"), seg("positions"), seg("logit_rows")
+        cu_q, kv_lens, slots, fresh = seg("cu_q"), seg("kv_lens"), seg("state_slots"), seg("fresh")
+        G = len(self.model.cache_groups)
+        slot_maps = [seg(f"slot_mapping{g}") for g in range(G)]
+        tables = [seg(f"block_table{g}").reshape(cfg.max_num_seqs, self.max_blocks) for g in range(G)]
+        t = w = 0
+        max_q = max_kv = 0
+        cu_q[0] = 0
+        for b, e in enumerate(entries):
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.rid!r} brings no token")
+            start = mgr.num_computed(e.rid)
+            if start + n > cfg.max_model_len:
+                raise ValueError(f"request {e.rid!r} would hold {start + n} tokens, max_model_len is {cfg.max_model_len}")
+            if any(mgr.pages_needed(e.rid, n)) and not mgr.allocate(e.rid, n):
+                raise CacheError(f"no cache pages left for request {e.rid!r}")
+            ids[t:t + n] = e.tokens
+            pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+            for g in range(G):
+                pages = mgr.block_table(e.rid, g)
+                row = tables[g][b]
+                row[:len(pages)] = pages
+                row[len(pages):] = 0
+                p = np.arange(start, start + n)
+                slot_maps[g][t:t + n] = np.asarray(pages, dtype=np.int64)[p // ps] * ps + p % ps
+            for j in e.want:
+                if not 0 <= j < n:
+                    raise ValueError(f"request {e.rid!r} wants place {j} of {n} tokens")
+                rows[w] = t + j
+                w += 1
+            t += n
+            cu_q[b + 1] = t
+            kv_lens[b] = start + n
+            slots[b] = mgr.slot(e.rid)
+            fresh[b] = 1 if start == 0 else 0
+            max_q, max_kv = max(max_q, n), max(max_kv, start + n)
+        # padding of a captured shape: token rows that write nowhere, requests without tokens
+        if Tp > T:
+            ids[T:Tp] = 0
+            pos[T:Tp] = 0
+            for g in range(G):
+                slot_maps[g][T:Tp] = -1
+        for b in range(B, Bp):
+            cu_q[b + 1] = T
+            kv_lens[b] = 0
+            slots[b] = 0
+            fresh[b] = 0
+            for g in range(G):
+                tables[g][b, :] = 0
+        ctx = StepContext()
+        ctx.num_tokens, ctx.num_requests = Tp, Bp
+        ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
+        ctx.decode_only = max_q == 1
+        ctx.num_logit_rows = w
+        ctx.host = {"real_tokens": T, "real_requests": B}
+        return ctx
+
+    def _bind_device_views(self, ctx):
+        d = self._dev
+        T, B = ctx.num_tokens, ctx.num_requests
+        ctx.token_ids = self._seg(d, "token_ids", T)
+        ctx.positions = self._seg(d, "positions", T)
+        ctx.logit_rows = self._seg(d, "logit_rows", ctx.num_logit_rows)
+        ctx.cu_q = self._seg(d, "cu_q", B + 1)
+        ctx.kv_lens = self._seg(d, "kv_lens", B)
+        ctx.state_slots = self._seg(d, "state_slots", B)
+        ctx.fresh = self._seg(d, "fresh", B)
+        ctx.groups = []
+        for g in range(len(self.model.cache_groups)):
+            table = self._seg(d, f"block_table{g}").view(self.cfg.max_num_seqs, self.max_blocks)
+            ctx.groups.append(GroupView(self.page_size, self.max_blocks,
+                                        self._seg(d, f"slot_mapping{g}", T), table[:B]))
+        ctx.device_cache = self.device_cache
+        ctx.dtype = self.dtype
+        return ctx
+
+    def _upload(self):
+        self._dev.copy_(self._host, non_blocking=True)
+
+    # ------------------------------------------------------------------ stepping
+    @torch.inference_mode()
+    def step(self, entries):
+        """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the
+        device (None if nothing is wanted).  The entries' tokens are computed afterwards."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        graph = self._graph_for(entries)
+        if graph is not None:
+            logits = self._replay(graph, entries)
+        else:
+            ctx = self._bind_device_views(self._pack(entries))
+            self._upload()
+            logits = self.model.forward(ctx)
+        for e in entries:
+            self.manager.commit(e.rid, len(e.tokens))
+        return logits
+
+    # ------------------------------------------------------------------ decode graphs
+    def decode_buckets(self):
+        S = self.cfg.max_num_seqs
+        sizes = [b for b in (1, 2, 4) if b <= S] + list(range(8, S + 1, 8))
+        if S not in sizes:
+            sizes.append(S)
+        return sorted(set(sizes))
+
+    def _graph_for(self, entries):
+        if not self.graphs:
+            return None
+        if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
+            return None
+        for size in self._graph_sizes:
+            if size >= len(entries):
+                return self.graphs[size]
+        return None
+
+    @torch.inference_mode()
+    def capture_decode_graphs(self, sizes=None):
+        """Capture one graph per decode batch size: every request brings one token and
+        wants its logits.  Smaller batches run the next larger graph with empty requests."""
+        sizes = sorted(sizes or self.decode_buckets(), reverse=True)
+        pool = None
+        dummy = "__capture__"
+        self.manager.begin(dummy)
+        try:
+            for size in sizes:
+                entries = [StepEntry(dummy, [0], [0])]
+                ctx = self._pack(entries, pad_requests=size, pad_tokens=size)
+                # captured shape: `size` requests of one token, all rows wanted
+                ctx.num_logit_rows = size
+                self._seg(self._host_np, "logit_rows")[:size] = np.arange(size, dtype=np.int32)
+                ctx.max_kv_len = self.cfg.max_model_len
+                self._bind_device_views(ctx)
+                self._upload()
+                stream = torch.cuda.Stream(self.device)
+                stream.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(stream):
+                    self.model.forward(ctx)           # warm-up outside capture
+                torch.cuda.current_stream(self.device).wait_stream(stream)
+                torch.cuda.synchronize(self.device)
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(graph, pool=pool):
+                    out = self.model.forward(ctx)
+                pool = pool or graph.pool()
+                self.graphs[size] = (graph, out, size, ops.launch_count() - before)
+        finally:
+            self.manager.free(dummy)
+        self._graph_sizes = sorted(self.graphs)
+        return len(self.graphs)
+
+    def _replay(self, graph_entry, entries):
+        graph, out, size, launches = graph_entry
+        ctx = self._pack(entries, pad_requests=size, pad_tokens=size)
+        rows = self._seg(self._host_np, "logit_rows")
+        rows[:size] = np.arange(size, dtype=np.int32)
+        self._upload()
+        graph.replay()
+        ops.count_launches(launches)
+        return out[:len(entries)]

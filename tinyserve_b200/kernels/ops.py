@@ -1,0 +1,278 @@
+"""Python bindings of the CUDA kernels.  Every op here launches this package's own
+sm_100a code through ctypes (matrix products of the bfloat16 path may go to cuBLAS, as
+they do in tinyserve: serve.py:828-829).  There is no CPU path and no fallback: tensors
+must live on a CUDA device and a missing compiler or library raises."""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+
+import torch
+
+from . import build
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+SUPPORTED_HEAD_DIMS = tuple(range(16, 513, 16))
+_DTYPE = {torch.float32: 0, torch.bfloat16: 1}
+
+_launches = 0
+#: bfloat16 matrix products: "cublas" (torch.mm) or "simt" (this package's FMA kernel)
+BF16_GEMM = "cublas"
+
+
+def launch_count() -> int:
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    global _launches
+    _launches += n
+
+
+def require_device(device) -> None:
+    if not torch.cuda.is_available():
+        raise RuntimeError("tinyserve_b200 runs on a CUDA device only (sm_100a); no GPU is visible "
+                           "and there is no CPU path")
+    if torch.device(device).type != "cuda":
+        raise RuntimeError(f"tinyserve_b200 runs on CUDA devices only, got {device!r}")
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _check(lib, code, n=1):
+    if code != 0:
+        raise RuntimeError(lib.ts_last_error().decode())
+    count_launches(n)
+
+
+def _dt(t):
+    try:
+        return _DTYPE[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {t.dtype}; kernels take float32 and bfloat16") from None
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("kernel operands must be CUDA tensors: there is no CPU path")
+
+
+def _vec_flag(w, like):
+    """Norm weights are float32 or of the activations' dtype."""
+    if w.dtype == torch.float32:
+        return 1
+    if w.dtype == torch.bfloat16:
+        return 0
+    raise TypeError(f"norm weight dtype {w.dtype} is not supported")
+
+
+# ----------------------------------------------------------------------------- libraries
+def _elementwise():
+    return build.load_unit("elementwise.cu")
+
+
+def _gemm():
+    return build.load_unit("gemm_simt.cu")
+
+
+def _attention(head_dim: int):
+    if head_dim not in SUPPORTED_HEAD_DIMS:
+        raise ValueError(f"head size {head_dim} is not supported: attention takes multiples of 16 "
+                         f"up to {SUPPORTED_HEAD_DIMS[-1]}")
+    return build.load_unit("attention_simt.cu", {"TS_HEAD_DIM": head_dim})
+
+
+def _sampler():
+    return build.load_unit("sampler.cu")
+
+
+def units_for(head_dims) -> list:
+    """The (source, defines) units a model with these head sizes needs."""
+    units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("sampler.cu", {})]
+    units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
+    return units
+
+
+# ----------------------------------------------------------------------------- ops
+def embed_lookup(table, ids):
+    """float32 [T, n] = table[ids]; ids int32."""
+    _cuda(table, ids)
+    T, n = ids.shape[0], table.shape[1]
+    out = torch.empty(T, n, dtype=torch.float32, device=table.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_embed_lookup(c_int(_dt(table)), _ptr(table), _ptr(ids), _ptr(out), c_int(T),
+                                    c_int(n), c_int(table.shape[0]), _stream()))
+    return out
+
+
+def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None):
+    """residual (float32, in place) += x; returns rmsnorm(residual) * weight as ``out_dtype``.
+    ``x`` None: no add.  With ``rows`` (int32) only those rows are normalised and returned, and
+    the residual is left as it is."""
+    _cuda(x, residual, weight, rows)
+    if residual.dtype != torch.float32 or not residual.is_contiguous():
+        raise TypeError("the residual stream is contiguous float32")
+    if x is not None and (x.dtype != out_dtype or not x.is_contiguous() or x.shape != residual.shape):
+        raise TypeError("add_rmsnorm: x must be contiguous, of the compute dtype and of the residual's shape")
+    n = residual.shape[1]
+    num_out = residual.shape[0] if rows is None else rows.shape[0]
+    out = torch.empty(num_out, n, dtype=out_dtype, device=residual.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_add_rmsnorm(c_int(_DTYPE[out_dtype]), _ptr(x), _ptr(residual), _ptr(weight),
+                                   c_int(_vec_flag(weight, out_dtype)), c_float(eps), _ptr(out),
+                                   _ptr(rows), c_int(num_out), c_int(n),
+                                   c_int(0 if rows is not None else 1), _stream()))
+    return out
+
+
+def rmsnorm(x, weight, eps, out=None):
+    _cuda(x, weight)
+    shape = x.shape
+    x2 = x.reshape(-1, shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    out = torch.empty_like(x2) if out is None else out
+    lib = _elementwise()
+    _check(lib, lib.ts_rmsnorm(c_int(_dt(x2)), _ptr(x2), _ptr(weight), c_int(_vec_flag(weight, x.dtype)),
+                               c_float(eps), _ptr(out), c_int(x2.shape[0]), c_int(shape[-1]), _stream()))
+    return out.view(shape)
+
+
+def gated_activation(gate_up, activation="silu"):
+    """[rows, 2 I] (gate | up) -> act(gate) * up, [rows, I]."""
+    _cuda(gate_up)
+    rows, two_i = gate_up.shape
+    out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    lib = _elementwise()
+    _check(lib, lib.ts_gated_activation(c_int(_dt(gate_up)), _ptr(gate_up), _ptr(out), c_int(rows),
+                                        c_int(two_i // 2), c_int(ACTIVATIONS[activation]), _stream()))
+    return out
+
+
+def qk_norm_rope_kvwrite(qkv, positions, num_heads, num_kv_heads, head_dim, rotary=None,
+                         q_weight=None, k_weight=None, eps=0.0, k_cache=None, v_cache=None,
+                         slot_mapping=None, page_size=0):
+    """Per-head norm of q and k, rotary encoding, q to a [T, H, D] tensor (returned), k and v
+    to the cache slots of ``slot_mapping`` (None: nothing is written)."""
+    _cuda(qkv, positions, k_cache, v_cache, slot_mapping)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or not qkv.is_contiguous():
+        raise ValueError("qkv must be contiguous [T, (H + 2 Hkv) * D]")
+    q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    cos = rotary.cos if rotary is not None else None
+    sin = rotary.sin if rotary is not None else None
+    rot = rotary.rotary_dim if rotary is not None else 0
+    inter = int(rotary.interleaved) if rotary is not None else 0
+    if k_cache is not None and k_cache.dtype != qkv.dtype:
+        raise TypeError("cache and activations differ in dtype")
+    flag = _vec_flag(q_weight, qkv.dtype) if q_weight is not None else 0
+    if q_weight is not None and k_weight.dtype != q_weight.dtype:
+        raise TypeError("q and k norm weights differ in dtype")
+    lib = _elementwise()
+    _check(lib, lib.ts_qk_norm_rope_kvwrite(
+        c_int(_dt(qkv)), _ptr(qkv), _ptr(q), _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot),
+        c_int(inter), _ptr(q_weight), _ptr(k_weight), c_int(flag), c_float(eps), c_int(T),
+        c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), _ptr(k_cache), _ptr(v_cache),
+        _ptr(slot_mapping), c_int(page_size), _stream()))
+    return q
+
+
+NUM_SMS = 148
+
+
+def attention_splits(num_requests, max_q_len, max_kv_len, num_heads, num_kv_heads):
+    """How many key ranges a launch is cut into so that a small batch still fills the SMs
+    (tinykernels.py:865-889, for 148 SMs)."""
+    group = num_heads // num_kv_heads
+    per_tile = 32 // group if group < 32 else 1
+    blocks = -(-max_q_len // per_tile) * num_kv_heads * -(-group // 32) * num_requests
+    if blocks >= 2 * NUM_SMS or max_kv_len < 256:
+        return 1
+    want = -(-2 * NUM_SMS // blocks)
+    return max(1, min(want, max_kv_len // 128, 32))
+
+
+def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
+    """Attention of this step's queries over their requests' cached keys and values.
+    q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
+    kv_lens and the batch's maxima."""
+    _cuda(q, k_cache, v_cache)
+    T, H, D = q.shape
+    Hkv = k_cache.shape[1]
+    if num_splits is None:
+        num_splits = attention_splits(ctx.num_requests, ctx.max_q_len, ctx.max_kv_len, H, Hkv)
+    out = torch.empty_like(q)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(T * H * num_splits * 2, dtype=torch.float32, device=q.device)
+    lib = _attention(D)
+    _check(lib, lib.ts_paged_attention(
+        c_int(_dt(q)), _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table),
+        _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
+        c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
+        c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _stream()),
+        2 if num_splits > 1 else 1)
+    return out
+
+
+def linear(x, weight, bias=None, out_float32=False):
+    """x [M, K] @ weight[N, K]^T (+ bias).  float32 operands: this package's 32-bit FMA kernel
+    (no tensor cores, no reduced precision).  bfloat16 operands: cuBLAS through torch.mm, or
+    the FMA kernel when BF16_GEMM == "simt"."""
+    _cuda(x, weight, bias)
+    M, K = x.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K or x.dtype != weight.dtype:
+        raise ValueError(f"linear: x {tuple(x.shape)} {x.dtype} does not fit weight {tuple(weight.shape)} {weight.dtype}")
+    if x.dtype == torch.bfloat16 and BF16_GEMM == "cublas":
+        if out_float32:
+            out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+        else:
+            out = torch.mm(x, weight.t())
+        if bias is not None:
+            out += bias
+        return out
+    out_dtype = torch.float32 if out_float32 else x.dtype
+    out = torch.empty(M, N, dtype=out_dtype, device=x.device)
+    if x.stride(1) != 1 or weight.stride(1) != 1:
+        raise ValueError("linear: operands must be contiguous along K")
+    lib = _gemm()
+    _check(lib, lib.ts_gemm_simt(c_int(_dt(x)), c_int(_DTYPE[out_dtype]), _ptr(x), _ptr(weight),
+                                 _ptr(bias), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                 c_longlong(x.stride(0)), c_longlong(weight.stride(0)),
+                                 c_longlong(N), _stream()))
+    return out
+
+
+def sample(logits, temperature, stream_ids, steps, seed, top_k=None, top_p=None):
+    """One token per row of float32 logits.  temperature float32 [B] (0 = argmax); stream_ids
+    int64 [B] and steps int32 [B] select the noise; top_k int32 [B], top_p float32 [B] optional."""
+    _cuda(logits, temperature, stream_ids, steps, top_k, top_p)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise TypeError("sample: logits must be float32 rows")
+    B, V = logits.shape
+    out = torch.empty(B, dtype=torch.int32, device=logits.device)
+    lib = _sampler()
+    _check(lib, lib.ts_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(B), c_int(V),
+                              _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(stream_ids),
+                              _ptr(steps), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(out), _stream()))
+    return out
+
+
+def apply_repetition_penalty(logits, rows, ids, penalty):
+    """In place: rows int32 [R] of logits; ids int32 [R, n] distinct recent tokens (-1 = none);
+    penalty float32 [R]."""
+    _cuda(logits, rows, ids, penalty)
+    lib = _sampler()
+    _check(lib, lib.ts_apply_repetition_penalty(
+        _ptr(logits), c_longlong(logits.stride(0)), c_int(logits.shape[1]), _ptr(rows), _ptr(ids),
+        c_int(rows.shape[0]), c_int(ids.shape[1]), _ptr(penalty), _stream()))
+    return logits

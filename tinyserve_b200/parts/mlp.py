@@ -1,0 +1,33 @@
+"""Gated feed-forward (serve.py:908-919): down(act(gate(x)) * up(x)) with gate and up
+as one fused projection (rows gate, then up: serve.py:911-912, 916)."""
+from __future__ import annotations
+
+from ..kernels import ops
+from .base import FeedForward, ParamSpec, Source, register_feed_forward
+
+
+class GatedMLP(FeedForward):
+    tree_name = "mlp"
+
+    def __init__(self, hidden_size, intermediate_size, activation="silu"):
+        super().__init__()
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.activation = activation
+
+    def param_specs(self):
+        i = self.intermediate_size
+        return {
+            "gate_up_proj.weight": ParamSpec((2 * i, self.hidden_size), sources=(
+                Source("gate_proj.weight", 0, i), Source("up_proj.weight", i, 2 * i))),
+            "down_proj.weight": ParamSpec((self.hidden_size, i)),
+        }
+
+    def forward(self, h, ctx):
+        gate_up = ops.linear(h, self.w["gate_up_proj.weight"])
+        act = ops.gated_activation(gate_up, self.activation)
+        return ops.linear(act, self.w["down_proj.weight"])
+
+
+register_feed_forward("gated_mlp", GatedMLP)
