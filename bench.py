@@ -1,0 +1,277 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on Qwen3-8B shapes with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers L]
+
+A step is one decode step of the whole batch.  Prints ONE JSON line:
+  value     decoded tokens per second over K steps, timed on the device with CUDA events;
+            each step uploads the batch, runs the model and samples greedily on the device
+  e2e       the same through the Python entry point (LLM.add_request / LLM.step): host
+            token ids in, sampled tokens out, scheduler and cache manager included
+  prefill   one 2,048-token prompt in one step
+  roofline  bytes the decode step must read (every weight once + the live cache) / time
+  points    decode tokens per second at batch 1 and 64
+The engine runs on one GPU; with --gpus > 1 it says so and exits with 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=4096,
+                num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6,
+                tie_word_embeddings=False, max_position_embeddings=40960)
+CONTEXT = 4096
+PROMPT_LEN = 512
+PREFILL_TOKENS = 2048
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        threading.Thread(target=self._read, daemon=True).start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons}
+
+
+def decode_bytes(cfg, layers, batch, ctx):
+    h, H, Hkv, D, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                          cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    per_layer = ((H + 2 * Hkv) * D * h + h * H * D + 2 * I * h + h * I + 2 * h + 2 * D) * 2
+    weights = layers * per_layer + V * h * 2 + h * 2
+    kv = batch * ctx * layers * 2 * Hkv * D * 2
+    return weights + kv
+
+
+def prefill_flops(cfg, layers, T):
+    h, H, Hkv, D, I, V = (cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"],
+                          cfg["head_dim"], cfg["intermediate_size"], cfg["vocab_size"])
+    linear = 2 * T * layers * ((H + 2 * Hkv) * D * h + h * H * D + 3 * I * h) + 2 * V * h
+    attention = layers * 4 * H * D * T * (T + 1) // 2
+    return linear + attention
+
+
+def run_decode(llm, batch, steps, warmup, seed, clock=None):
+    """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` decode steps."""
+    import torch
+    from tinyserve_b200.engine.batch import StepEntry
+    from tinyserve_b200.kernels import ops
+    runner, vocab = llm.runner, llm.runner.model.vocab_size
+    gen = torch.Generator().manual_seed(seed)
+    rids = [f"bench{batch}_{i}" for i in range(batch)]
+    temps = torch.zeros(batch, dtype=torch.float32, device=runner.device)
+    streams = torch.zeros(batch, dtype=torch.int64, device=runner.device)
+    counters = torch.zeros(batch, dtype=torch.int32, device=runner.device)
+    host = torch.empty(batch, dtype=torch.int32).pin_memory()
+    last = []
+    for rid in rids:
+        runner.manager.begin(rid)
+    per_step = max(1, runner.cfg.max_num_batched_tokens // PROMPT_LEN)
+    for i in range(0, batch, per_step):
+        group = rids[i:i + per_step]
+        prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in group]
+        logits = runner.step([StepEntry(r, p, [PROMPT_LEN - 1]) for r, p in zip(group, prompts)])
+        last += logits.argmax(-1).tolist()
+
+    def one_step(tokens):
+        logits = runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, tokens)])
+        out = ops.sample(logits, temps, streams, counters, 0)
+        host.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return host.tolist()
+
+    for _ in range(warmup):
+        last = one_step(last)
+    torch.cuda.synchronize()
+    if clock:
+        clock.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count()
+    start.record()
+    for _ in range(steps):
+        last = one_step(last)
+    end.record()
+    torch.cuda.synchronize()
+    clocks = clock.stop() if clock else None
+    ms = start.elapsed_time(end) / steps
+    ctx = PROMPT_LEN + warmup + steps / 2
+    for rid in rids:
+        runner.manager.free(rid)
+    return {"ms": ms, "tok_s": batch * 1000.0 / ms, "ctx": ctx,
+            "launches": ops.launch_count() - launches0, "clocks": clocks}
+
+
+def run_e2e(llm, batch, steps, warmup, seed):
+    """The same decode through LLM.add_request / LLM.step, wall clock, host ids in and out."""
+    import torch
+    from tinyserve_b200 import SamplingParams
+    vocab = llm.runner.model.vocab_size
+    gen = torch.Generator().manual_seed(seed + 1)
+    params = SamplingParams(temperature=0.0, max_tokens=warmup + steps + 1, repetition_penalty=1.0,
+                            ignore_eos=True)
+    for i in range(batch):
+        llm.add_request(torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist(), params,
+                        request_id=f"e2e{i}")
+    while any(r.num_computed_tokens < r.prompt_len for r in llm.requests.values()) or llm.scheduler.waiting:
+        llm.step()
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(llm.step())
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    for rid in list(llm.requests):
+        llm.abort(rid)
+    h2d = llm.runner._dev.numel() * 4
+    return {"value": produced / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": batch * 4}
+
+
+def run_prefill(llm, seed, repeats=3):
+    import torch
+    from tinyserve_b200.engine.batch import StepEntry
+    runner, vocab = llm.runner, llm.runner.model.vocab_size
+    gen = torch.Generator().manual_seed(seed + 2)
+    times = []
+    for i in range(repeats + 1):
+        rid = f"prefill{i}"
+        runner.manager.begin(rid)
+        ids = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry(rid, ids, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+        runner.manager.free(rid)
+    return min(times[1:])
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
+    ap.add_argument("--impl", default="tinyserve_b200")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "priyammaz/tinyserve has no setup.py or pyproject.toml: the offline pip "
+                          "install into baseline/_ref fails with 'not installable'"}))
+        return 0
+    if a.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
+        return 2
+    import torch
+    from tinyserve_b200 import LLM, Qwen3Config
+    from tinyserve_b200.kernels import ops
+    warmup = max(a.warmup, 3)
+    raw = dict(QWEN3_8B, num_hidden_layers=a.layers)
+    config = Qwen3Config.from_dict(raw)
+    peaks = load_peaks()
+    sizes = sorted({1, a.batch, 64}) if not a.no_points else [a.batch]
+    llm = LLM(model_config=config, random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
+              block_size=16, max_num_seqs=max(sizes), max_num_batched_tokens=PREFILL_TOKENS,
+              num_blocks=max(sizes) * (CONTEXT // 16) // 2 + 256, use_cuda_graphs=False, seed=a.seed)
+    llm.runner.capture_decode_graphs(sizes)
+
+    main_run = run_decode(llm, a.batch, a.steps, warmup, a.seed, ClockSampler())
+    e2e = run_e2e(llm, a.batch, a.steps, warmup, a.seed)
+    points, prefill = {}, None
+    if not a.no_points:
+        for b in (1, 64):
+            r = run_decode(llm, b, min(a.steps, 64), warmup, a.seed + b)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+        ms = run_prefill(llm, a.seed)
+        flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
+        prefill = {"value": round(PREFILL_TOKENS * 1000.0 / ms, 1), "tokens": PREFILL_TOKENS,
+                   "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    nbytes = decode_bytes(raw, a.layers, a.batch, main_run["ctx"])
+    achieved = nbytes / (main_run["ms"] * 1e-3) / 1e9
+    line = {
+        "metric": "decode tok/s (Qwen3-8B shapes, random weights)", "value": round(main_run["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": warmup,
+        "ms_per_step": round(main_run["ms"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(main_run["tok_s"] / (42.2 * a.batch), 3) if a.batch == 1 else None,
+        "dtype": "bf16", "data": "synthetic", "impl": "tinyserve_b200",
+        "config": {"model": "Qwen3-8B shapes", "global_batch": a.batch, "seq_len": CONTEXT,
+                   "parallelism": "none", "layers": a.layers,
+                   "layers_of_model": QWEN3_8B["num_hidden_layers"], "hidden": raw["hidden_size"],
+                   "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+                   "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
+                   "vocab": raw["vocab_size"], "prompt_len": PROMPT_LEN, "block_size": 16,
+                   "l2": "inputs larger than L2 (weights read every step)",
+                   "peaks": peaks["source"], "peak_hbm_gbs": peaks["hbm_gbs"],
+                   "peak_bf16_tflops": peaks["bf16_tflops"], "bf16_gemm": ops.BF16_GEMM},
+        "clocks": main_run["clocks"], "e2e": {k: (round(v, 1) if isinstance(v, float) else v)
+                                               for k, v in e2e.items()},
+        "gpu_launches": main_run["launches"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
+    }
+    if prefill:
+        line["prefill"] = prefill
+    if points:
+        line["points"] = points
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

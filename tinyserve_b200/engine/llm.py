@@ -1,0 +1,214 @@
+"""The Python entry point: ``LLM(model_dir).generate(prompts, SamplingParams(...))``.
+
+The surface is tinyserve's ``Engine`` (serve.py:2381-2712): ``add_request``, ``step``,
+``abort``, ``has_work`` and ``generate``, which adds every prompt and steps until all are
+done, returning ``Output`` objects in request order (serve.py:2703-2712).  A step here is
+schedule -> run the batch -> sample -> read the tokens back -> finish or go on; tinyserve
+runs the host one step ahead of the device (serve.py:2509-2601), which this loop does not.
+A prompt is a string (needs the tokenizer files in the model folder) or a list of ids."""
+from __future__ import annotations
+
+import json
+import os
+import time
+import uuid
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from ..config.engine_config import EngineConfig
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+from .runner import ModelRunner
+from .scheduler import Request, Scheduler
+from .text import Detokenizer, apply_stop_strings, load_tokenizer
+
+
+@dataclass
+class Output:
+    """What a finished (or running) request has produced (serve.py:2295-2307)."""
+
+    request_id: str
+    text: str
+    delta: str
+    token_ids: list
+    finished: bool
+    finish_reason: Optional[str]
+    num_prompt_tokens: int
+    num_cached_tokens: int = 0
+    logprobs: Optional[list] = None
+    was_preempted: bool = False
+    was_chunked_prefill: bool = False
+
+
+def _stop_ids(model_dir, tokenizer) -> set:
+    """EOS of the tokenizer plus generation_config.json's eos_token_id (serve.py:2392-2403)."""
+    ids = set()
+    if tokenizer is not None and tokenizer.eos_token_id is not None:
+        ids.add(tokenizer.eos_token_id)
+    path = os.path.join(model_dir, "generation_config.json") if model_dir else ""
+    if path and os.path.isfile(path):
+        with open(path) as fh:
+            eos = json.load(fh).get("eos_token_id")
+        ids |= set(eos if isinstance(eos, list) else [eos])
+    ids.discard(None)
+    return ids
+
+
+class LLM:
+    def __init__(self, model: str = "", *, model_config=None, random_weights: bool = False,
+                 verbose: bool = False, **engine_options):
+        """``model``: a folder with config.json and safetensors.  ``engine_options`` are the
+        fields of ``EngineConfig`` (dtype, max_model_len, block_size, max_num_seqs,
+        max_num_batched_tokens, gpu_memory_utilization, num_blocks, use_cuda_graphs, seed).
+        With ``model_config`` and ``random_weights`` the weights are drawn on the device and no
+        folder is read."""
+        t0 = time.time()
+        self.cfg = EngineConfig(model=model, **engine_options)
+        self.runner = ModelRunner(self.cfg, model_config=model_config,
+                                  random_weights=random_weights, verbose=verbose)
+        self.tokenizer = load_tokenizer(model) if model else None
+        self.stop_ids = _stop_ids(model, self.tokenizer)
+        self.scheduler = Scheduler(self.runner.manager, self.cfg.max_num_seqs,
+                                   self.cfg.max_num_batched_tokens)
+        self.sampler = Sampler(self.cfg.seed, self.runner.device)
+        if self.cfg.use_cuda_graphs:
+            self.runner.capture_decode_graphs()
+        self.requests: dict = {}
+        self.detok: dict = {}
+        self.num_prompt_tokens_run = 0
+        self.num_generated_tokens = 0
+        self.num_steps = 0
+        self._tokens_host = torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory()
+        if verbose:
+            print(f"[tinyserve_b200] engine ready in {time.time() - t0:.1f}s", flush=True)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt, params: SamplingParams, request_id: Optional[str] = None) -> str:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("a text prompt needs tokenizer files in the model folder; "
+                                 "pass token ids instead")
+            ids = self.tokenizer.encode(prompt)
+        else:
+            ids = [int(t) for t in prompt]
+        if not 0 < len(ids) < self.cfg.max_model_len:
+            raise ValueError(f"prompt of {len(ids)} tokens: must be 1..max_model_len-1 "
+                             f"({self.cfg.max_model_len - 1})")
+        vocab = self.runner.model.vocab_size
+        if any(t < 0 or t >= vocab for t in ids):
+            raise ValueError(f"prompt holds a token id outside [0, {vocab})")
+        capacity = (self.runner.num_pages - 1) * self.runner.page_size
+        if len(ids) + 1 > capacity:
+            raise ValueError(f"prompt of {len(ids)} tokens does not fit the cache of {capacity} tokens")
+        rid = request_id or uuid.uuid4().hex
+        if rid in self.requests:
+            raise ValueError(f"request id {rid!r} is in use")
+        self.requests[rid] = req = Request(rid, ids, params)
+        self.scheduler.add(req)
+        self.detok[rid] = Detokenizer(self.tokenizer)
+        return rid
+
+    def abort(self, request_id: str) -> None:
+        """Stop a request and give its pages back (serve.py:2474-2479)."""
+        req = self.requests.pop(request_id, None)
+        if req is not None and not req.finished:
+            self.scheduler.finish(req, "abort")
+            self.detok.pop(request_id, None)
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    # ------------------------------------------------------------------ one step
+    @torch.inference_mode()
+    def step(self) -> list:
+        batch = self.scheduler.schedule()
+        outputs = [self._output(r) for r in self._take_dropped()]
+        if not batch:
+            return outputs
+        entries, live = [], []
+        for s in batch:
+            req = s.req
+            tokens = req.token_ids[s.num_computed:s.num_computed + s.num_new]
+            want = [s.num_new - 1] if s.completes_prompt else []
+            if not s.completes_prompt:
+                req.was_chunked_prefill = True
+            else:
+                live.append(req)
+            if s.num_computed < req.prompt_len:
+                self.num_prompt_tokens_run += min(s.num_new, req.prompt_len - s.num_computed)
+            entries.append(StepEntry(req.request_id, tokens, want))
+        logits = self.runner.step(entries)
+        self.num_steps += 1
+        if not live:
+            return outputs
+        forced = [r for r in live if r.params.forced_token_ids is not None]
+        raw = logits.clone() if any(r.params.return_logprobs for r in live) else None
+        tokens_dev = self.sampler(logits, live)
+        n = len(live)
+        self._tokens_host[:n].copy_(tokens_dev, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        tokens = self._tokens_host[:n].tolist()
+        self.num_generated_tokens += n
+        for i, req in enumerate(live):
+            tok = tokens[i]
+            if forced and req.params.forced_token_ids is not None:
+                tok = int(req.params.forced_token_ids[len(req.output_ids)])
+            req.token_ids.append(tok)
+            if req.params.return_logprobs:
+                req.logprobs.append(raw[i].log_softmax(-1).cpu())
+            outputs.append(self._after_token(req, tok))
+        return outputs
+
+    def _take_dropped(self):
+        dropped, self.scheduler.dropped = self.scheduler.dropped, []
+        return dropped
+
+    def _after_token(self, req: Request, tok: int) -> Output:
+        p = req.params
+        if tok in self.stop_ids and not p.ignore_eos:
+            self.scheduler.finish(req, "stop")
+        elif len(req.output_ids) >= p.max_tokens or req.num_tokens >= self.cfg.max_model_len:
+            self.scheduler.finish(req, "length")
+        return self._output(req)
+
+    def _output(self, req: Request) -> Output:
+        d = self.detok.get(req.request_id)
+        text = delta = ""
+        if d is not None and d.tok is not None:
+            delta = d.update(req.output_ids, req.finished)
+            text = d.text
+            if req.params.stop:
+                text, hit = apply_stop_strings(d.text, req.params.stop)
+                if hit and not req.finished:
+                    self.scheduler.finish(req, "stop")
+                elif req.finished and not hit:
+                    text = d.text
+                delta, d.released = text[d.released:], len(text)
+        out = Output(req.request_id, text, delta, req.output_ids, req.finished, req.finish_reason,
+                     req.prompt_len, 0, req.logprobs if req.params.return_logprobs else None,
+                     req.was_preempted, req.was_chunked_prefill)
+        if req.finished:
+            self.detok.pop(req.request_id, None)
+            self.requests.pop(req.request_id, None)
+        return out
+
+    # ------------------------------------------------------------------ offline API
+    def generate(self, prompts: list, params) -> list:
+        """Add every prompt, step until all are done; outputs in request order."""
+        params = params if isinstance(params, list) else [params] * len(prompts)
+        rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
+        done: dict = {}
+        while self.has_work():
+            for o in self.step():
+                if o.finished:
+                    done[o.request_id] = o
+        return [done[r] for r in rids]
+
+    def stats(self) -> dict:
+        """The figures of tinyserve's log line (serve.py:2494-2507)."""
+        return {"prompt_tokens_run": self.num_prompt_tokens_run,
+                "generated_tokens": self.num_generated_tokens, "steps": self.num_steps,
+                "running": len(self.scheduler.running), "waiting": len(self.scheduler.waiting),
+                "kv_cache_usage": self.runner.manager.usage()}

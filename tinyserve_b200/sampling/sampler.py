@@ -1,0 +1,71 @@
+"""Batched sampling on the device: one call for rows with mixed settings.
+
+Order as in tinyserve's ``sample`` (serve.py:1501-1588): repetition penalty on the
+logits, then argmax for greedy rows, else temperature, top-k, top-p and Gumbel-max.
+Unlike there, the noise of a row depends only on (engine seed, the request's stream,
+how many tokens the request has generated), not on the batch around it."""
+from __future__ import annotations
+
+import zlib
+
+import torch
+
+from ..kernels import ops
+
+
+def stream_of(request_id, params) -> int:
+    """The request's noise stream: its ``seed`` if given, else a hash of its id."""
+    if params.seed is not None:
+        return int(params.seed) & (2 ** 63 - 1)
+    return zlib.crc32(str(request_id).encode()) | (1 << 40)
+
+
+def recent_tokens(params, token_ids) -> list:
+    """Distinct tokens the repetition penalty applies to (serve.py:1469-1476)."""
+    if params.repetition_penalty == 1.0 or params.repeat_last_n == 0:
+        return []
+    window = token_ids if params.repeat_last_n < 0 else token_ids[-params.repeat_last_n:]
+    return sorted(set(window))
+
+
+class Sampler:
+    def __init__(self, seed: int, device):
+        self.seed = int(seed)
+        self.device = device
+
+    def __call__(self, logits, requests):
+        """logits float32 [B, V] (modified in place by the penalty); ``requests``: objects with
+        request_id, params, token_ids, prompt_len.  Returns int32 [B] on the device."""
+        B = logits.shape[0]
+        temps, ks, ps, streams, steps = [], [], [], [], []
+        pen_rows, pen_ids, pen_vals = [], [], []
+        for i, r in enumerate(requests):
+            p = r.params
+            temps.append(float(p.temperature))
+            ks.append(int(p.top_k) if p.top_k and p.top_k > 0 else 0)
+            ps.append(float(p.top_p))
+            streams.append(stream_of(r.request_id, p))
+            steps.append(len(r.token_ids) - r.prompt_len)
+            ids = recent_tokens(p, r.token_ids)
+            if ids:
+                pen_rows.append(i)
+                pen_ids.append(ids)
+                pen_vals.append(float(p.repetition_penalty))
+        dev = self.device
+        if pen_rows:
+            width = max(len(x) for x in pen_ids)
+            table = torch.full((len(pen_rows), width), -1, dtype=torch.int32)
+            for j, ids in enumerate(pen_ids):
+                table[j, :len(ids)] = torch.tensor(ids, dtype=torch.int32)
+            ops.apply_repetition_penalty(logits, torch.tensor(pen_rows, dtype=torch.int32, device=dev),
+                                         table.to(dev), torch.tensor(pen_vals, dtype=torch.float32, device=dev))
+        need_k = any(k > 0 for k, t in zip(ks, temps) if t > 0)
+        need_p = any(p < 1.0 for p, t in zip(ps, temps) if t > 0)
+        return ops.sample(
+            logits,
+            torch.tensor(temps, dtype=torch.float32, device=dev),
+            torch.tensor(streams, dtype=torch.int64, device=dev),
+            torch.tensor(steps, dtype=torch.int32, device=dev),
+            self.seed,
+            top_k=torch.tensor(ks, dtype=torch.int32, device=dev) if need_k else None,
+            top_p=torch.tensor(ps, dtype=torch.float32, device=dev) if need_p else None)
