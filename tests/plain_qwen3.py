@@ -212,18 +212,15 @@ def philox4x32(counter, key):
 def gumbel_noise(seed, stream, step, vocab):
     """Noise of the sampler for one row: token v uses word v % 4 of
     philox(counter=(v // 4, step, stream_lo, stream_hi), key=(seed_lo, seed_hi));
-    u = (word + 0.5) / 2^32 lies in (0, 1); the noise is -log(-log(u)), in float32."""
-    out = np.empty(vocab, dtype=np.float32)
+    u = ((word >> 9) + 0.5) * 2^-23 lies in (0, 1); the noise is -log(-log(u))."""
+    out = np.empty(vocab, dtype=np.float64)
     key = (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
     for base in range(0, vocab, 4):
         words = philox4x32((base // 4, step & 0xFFFFFFFF, stream & 0xFFFFFFFF,
                             (stream >> 32) & 0xFFFFFFFF), key)
         for j in range(min(4, vocab - base)):
-            u = np.float32((np.float32(words[j]) + np.float32(0.5)) * np.float32(2.0 ** -32))
-            out[base + j] = u
-    # float32(word) can round up to 2^32, giving u = 1; the sampler clamps as below
-    out = np.minimum(out, np.float32(1.0 - 2.0 ** -24))
-    return -np.log(-np.log(out.astype(np.float64)))
+            out[base + j] = ((words[j] >> 9) + 0.5) * 2.0 ** -23
+    return -np.log(-np.log(out))
 
 
 def sample_row(row, temperature, seed, stream, step):
