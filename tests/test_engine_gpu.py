@@ -1,0 +1,200 @@
+"""The entry point, the scheduler on the device, and each part alone."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import make_model_dir, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def llm_for(folder, dtype, **kw):
+    from tinyserve_b200 import LLM
+    opts = dict(dtype=dtype, max_model_len=256, block_size=16, max_num_seqs=8,
+                max_num_batched_tokens=256, num_blocks=64, use_cuda_graphs=False)
+    opts.update(kw)
+    return LLM(folder, **opts)
+
+
+def greedy(max_tokens):
+    from tinyserve_b200 import SamplingParams
+    return SamplingParams(temperature=0.0, max_tokens=max_tokens, repetition_penalty=1.0, ignore_eos=True)
+
+
+def near_best(cfg, weights, prompt, out_ids, slack):
+    """Every generated token is, under the plain logits of its own prefix, within ``slack``
+    of the best token (bfloat16 may choose the other side of a near tie)."""
+    ids = list(prompt)
+    for tok in out_ids:
+        row = plain.logits(cfg, weights, ids)[-1]
+        assert row[tok] >= row.max() - slack * row.abs().max(), (len(ids), tok, int(row.argmax()))
+        ids.append(tok)
+
+
+def test_greedy_generation_tiny_a(tmp_path):
+    """Three requests with prompts of 5, 17 and 31 tokens, 16 greedy tokens each."""
+    folder = make_model_dir(tmp_path, "A", seed=31)
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_ids(256, n, seed=n) for n in (5, 17, 31)]
+    outs = llm_for(folder, "float32").generate(prompts, greedy(16))
+    for p, o in zip(prompts, outs):
+        assert o.finished and o.finish_reason == "length" and o.num_prompt_tokens == len(p)
+        assert o.token_ids == plain.greedy_generate(cfg, weights, p, 16)
+    for graphs in (False, True):
+        outs16 = llm_for(folder, "bfloat16", use_cuda_graphs=graphs).generate(prompts, greedy(16))
+        for p, o in zip(prompts, outs16):
+            assert len(o.token_ids) == 16
+            near_best(cfg, weights, p, o.token_ids, 0.03)
+
+
+def test_temperature_generation_tiny_b_with_chunked_prefill(tmp_path):
+    """Five requests (1, 9, 40, 63, 100 tokens), 24 tokens at temperature 0.8, pages of 8, a
+    budget of 32 tokens a step.  Every token is the arg-max of the plain logits / T plus the
+    documented noise; the same tokens come out alone and in the batch."""
+    from tinyserve_b200 import SamplingParams
+    folder = make_model_dir(tmp_path, "B", seed=32)
+    cfg, weights = plain.load_folder(folder)
+    prompts = [random_ids(384, n, seed=n) for n in (1, 9, 40, 63, 100)]
+    params = [SamplingParams(temperature=0.8, max_tokens=24, repetition_penalty=1.0, ignore_eos=True,
+                             seed=1000 + i) for i in range(5)]
+    kw = dict(block_size=8, max_num_batched_tokens=32, max_num_seqs=4, num_blocks=80, seed=7)
+    outs = llm_for(folder, "float32", **kw).generate(prompts, params)
+    assert any(o.was_chunked_prefill for o in outs)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        ids = list(p)
+        for step, tok in enumerate(o.token_ids):
+            row = plain.logits(cfg, weights, ids)[-1]
+            noisy = row.numpy() / 0.8 + plain.gumbel_noise(7, 1000 + i, step, 384)
+            assert noisy[tok] >= noisy.max() - 1e-4, (i, step)
+            ids.append(tok)
+    alone = llm_for(folder, "float32", **kw).generate([prompts[3]], [params[3]])[0]
+    assert alone.token_ids == outs[3].token_ids
+
+
+def test_preemption_recomputes_the_same_tokens(tmp_path):
+    folder = make_model_dir(tmp_path, "A", seed=33)
+    prompts = [random_ids(256, n, seed=n) for n in (30, 28, 26)]
+    roomy = llm_for(folder, "float32").generate(prompts, greedy(40))
+    tight = llm_for(folder, "float32", num_blocks=9)       # 144 tokens of cache for 3 x ~70
+    outs = tight.generate(prompts, greedy(40))
+    assert any(o.was_preempted for o in outs)
+    assert [o.token_ids for o in outs] == [o.token_ids for o in roomy]
+    tight.runner.manager.check_invariants()
+    assert tight.runner.manager.num_free_pages() == 9
+
+
+def test_entry_point_options(tmp_path):
+    from tinyserve_b200 import SamplingParams
+    folder = make_model_dir(tmp_path, "A", seed=34)
+    cfg, weights = plain.load_folder(folder)
+    llm = llm_for(folder, "float32")
+    p = random_ids(256, 12, seed=1)
+    first = int(plain.logits(cfg, weights, p)[-1].argmax())
+    # the stop id ends the request (no tokenizer here, so the engine is told the id)
+    llm.stop_ids = {first}
+    out = llm.generate([p], SamplingParams(temperature=0, max_tokens=5, repetition_penalty=1.0))[0]
+    assert out.token_ids == [first] and out.finish_reason == "stop"
+    llm.stop_ids = set()
+    # forced tokens and the distributions that met them
+    forced = [3, 4, 5]
+    out = llm.generate([p], SamplingParams(temperature=0, max_tokens=3, repetition_penalty=1.0,
+                                           forced_token_ids=forced, return_logprobs=True))[0]
+    assert out.token_ids == forced and len(out.logprobs) == 3
+    ref = torch.log_softmax(plain.logits(cfg, weights, p + forced[:2])[-1], -1)
+    assert (out.logprobs[2].double() - ref).abs().max().item() < 1e-4
+    # the repetition penalty changes the choice exactly as the plain formula says
+    out = llm.generate([p], SamplingParams(temperature=0, max_tokens=2, repetition_penalty=50.0,
+                                           repeat_last_n=-1, ignore_eos=True))[0]
+    ids = list(p)
+    for tok in out.token_ids:
+        row = plain.repetition_penalty(plain.logits(cfg, weights, ids)[-1], ids, 50.0)
+        assert tok == int(row.argmax())
+        ids.append(tok)
+    with pytest.raises(ValueError, match="tokenizer"):
+        llm.add_request("text", greedy(1))
+    with pytest.raises(ValueError, match="token id"):
+        llm.add_request([1, 999], greedy(1))
+    with pytest.raises(ValueError, match="max_model_len"):
+        llm.add_request(list(range(200)) * 2, greedy(1))
+    rid = llm.add_request(p, greedy(50))
+    llm.step()
+    llm.abort(rid)
+    assert not llm.has_work() and llm.runner.manager.num_free_pages() == 64
+    assert llm.stats()["generated_tokens"] > 0
+
+
+def test_engine_fails_loudly_without_its_kernels(tmp_path, monkeypatch):
+    from tinyserve_b200.kernels import build, ops
+    monkeypatch.setattr(build, "_loaded", {})
+    monkeypatch.setattr(build, "compile_unit", lambda *a, **k: str(tmp_path / "missing.so"))
+    with pytest.raises(OSError):
+        ops.embed_lookup(torch.zeros(4, 8, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.require_device("cpu")
+
+
+# ----------------------------------------------------------------------------- parts alone
+@pytest.fixture(scope="module")
+def part_runner(tmp_path_factory):
+    from tinyserve_b200.config import EngineConfig
+    from tinyserve_b200.engine.runner import ModelRunner
+    folder = make_model_dir(tmp_path_factory.mktemp("parts"), "C", seed=40, store_dtype="float32")
+    runner = ModelRunner(EngineConfig(model=folder, dtype="float32", max_model_len=128, block_size=8,
+                                      max_num_seqs=2, max_num_batched_tokens=128, num_blocks=32))
+    cfg, weights = plain.load_folder(folder)
+    return runner, cfg, weights
+
+
+def _context(runner, n):
+    from tinyserve_b200.engine.batch import StepEntry
+    runner.manager.begin("x")
+    ctx = runner._bind_device_views(runner._pack([StepEntry("x", [1] * n, [])]))
+    runner._upload()
+    return ctx
+
+
+@pytest.mark.parametrize("layer", [0, 3])
+def test_parts_alone(part_runner, layer):
+    runner, cfg, w = part_runner
+    T, hid = 50, cfg["hidden_size"]
+    g = torch.Generator().manual_seed(layer)
+    h = torch.randn(T, hid, generator=g)
+    res = torch.randn(T, hid, generator=g)
+    block = runner.model.blocks[layer]
+    call = runner.model.calls[layer]
+    ctx = _context(runner, T)
+    try:
+        p = f"model.layers.{layer}."
+        cos, sin = plain.rope_tables(cfg["head_dim"], cfg["rope_theta"], T, torch.float64)
+        window = plain.layer_window(cfg, layer)
+        assert block.mixer.window == window == (40 if layer >= 2 else 0)
+        # mixer
+        got = block.mixer.forward(h.cuda(), ctx, call)
+        want = plain.attention_block(h.double(), w, p + "self_attn.", cfg, cos, sin, window)
+        assert (got.double().cpu() - want).abs().max().item() < 1e-5 * want.abs().max().item()
+        # feed-forward
+        got = block.ffn.forward(h.cuda(), ctx)
+        want = plain.swiglu_mlp(h.double(), w, p + "mlp.")
+        assert (got.double().cpu() - want).abs().max().item() < 1e-5 * want.abs().max().item()
+        # norm with the residual sum
+        r = res.clone().cuda()
+        got = block.input_norm.add_forward(h.cuda(), r)
+        want = plain.rms_norm(res.double() + h.double(), w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        assert (got.double().cpu() - want).abs().max().item() < 1e-5
+        assert torch.equal(r.cpu(), res + h)
+        # the block: x and residual in, next x out, residual advanced
+        r = res.clone().cuda()
+        x_next = block.forward(h.cuda(), r, ctx, call)
+        full = plain.decoder_layer(res.double() + h.double(), w, layer, cfg, cos, sin, window)
+        assert ((r.double() + x_next.double()).cpu() - full).abs().max().item() < 1e-5 * full.abs().max().item()
+    finally:
+        runner.manager.free("x")
+
+
+def test_position_encoding_alone(part_runner):
+    runner, cfg, _ = part_runner
+    rot = runner.model.blocks[0].mixer.position
+    cos, sin = plain.rope_tables(cfg["head_dim"], cfg["rope_theta"], 128, torch.float32)
+    assert torch.equal(rot.cos.cpu(), cos) and torch.equal(rot.sin.cpu(), sin)
+    assert rot.cos.data_ptr() == runner.model.blocks[3].mixer.position.cos.data_ptr(), "one table is shared"

@@ -1,0 +1,333 @@
+"""Each CUDA kernel alone against a plain float64 reference written here, at sizes other
+than the engine's tiny models use.  Inputs are made so that a fault shows: a far key that
+dominates, a window's edge, pages in shuffled order."""
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}     # relative to the reference's scale
+
+
+def ops():
+    from tinyserve_b200.kernels import ops as o
+    return o
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+def close(got, want, dtype, what=""):
+    want = want.double().cpu()
+    err = (got.double().cpu() - want).abs().max().item()
+    scale = max(want.abs().max().item(), 1e-6)
+    assert err <= TOL[dtype] * scale, f"{what}: error {err:.3e} at scale {scale:.3e}"
+
+
+# ----------------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_lookup(dtype):
+    table = rnd(301, 72, dtype=dtype)
+    ids = torch.tensor([0, 300, 7, 7, 123], dtype=torch.int32).cuda()
+    out = ops().embed_lookup(table, ids)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [72, 100, 1000, 4104])
+@pytest.mark.parametrize("wdtype", ["same", "f32"])
+def test_add_rmsnorm(dtype, n, wdtype):
+    rows, eps = 7, 3e-6
+    x = rnd(rows, n, seed=1, dtype=dtype)
+    res = rnd(rows, n, seed=2, scale=3.0)
+    w = rnd(n, seed=3, dtype=torch.float32 if wdtype == "f32" else dtype) + 1
+    want_res = res.double() + x.double()
+    want = want_res * torch.rsqrt(want_res.pow(2).mean(-1, keepdim=True) + eps) * w.double()
+    r = res.clone()
+    out = ops().add_rmsnorm(x, r, w, eps, dtype)
+    close(out, want, dtype, "norm")
+    assert (r.double() - want_res).abs().max().item() < 1e-6, "the residual sum is 32-bit"
+    # without x: the residual is only normalised
+    r2 = res.clone()
+    out = ops().add_rmsnorm(None, r2, w, eps, dtype)
+    v = res.double()
+    close(out, v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * w.double(), dtype, "no add")
+    assert torch.equal(r2, res)
+    # gathered rows: only those rows, the residual untouched
+    idx = torch.tensor([5, 0, 5], dtype=torch.int32).cuda()
+    r3 = res.clone()
+    out = ops().add_rmsnorm(x, r3, w, eps, dtype, rows=idx)
+    close(out, want[idx.long().cpu()], dtype, "gather")
+    assert torch.equal(r3, res)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rmsnorm_and_gated_activation(dtype):
+    x = rnd(5, 3, 48, seed=4, dtype=dtype)
+    w = rnd(48, seed=5, dtype=dtype)
+    v = x.double()
+    close(ops().rmsnorm(x, w, 1e-5), v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5) * w.double(),
+          dtype, "rmsnorm")
+    gu = rnd(9, 200, seed=6, dtype=dtype, scale=2.0)
+    g, u = gu.double().chunk(2, -1)
+    close(ops().gated_activation(gu, "silu"), g / (1 + torch.exp(-g)) * u, dtype, "silu")
+    close(ops().gated_activation(gu, "gelu_tanh"),
+          torch.nn.functional.gelu(g, approximate="tanh") * u, dtype, "gelu")
+
+
+def _rope_ref(x, pos, cos, sin, R, interleaved):
+    xr, rest = x[..., :R], x[..., R:]
+    c, s = cos[pos][:, None].double(), sin[pos][:, None].double()
+    if interleaved:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2)
+    else:
+        a, b = xr.chunk(2, -1)
+        out = torch.cat([a * c - b * s, b * c + a * s], -1)
+    return torch.cat([out, rest], -1)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hkv,D,R,inter,norm,page", [
+    (6, 3, 48, 48, False, True, 8), (8, 2, 128, 128, False, True, 16), (5, 5, 16, 16, False, False, 4),
+    (4, 1, 80, 32, False, True, 16), (3, 3, 64, 64, True, True, 8), (2, 2, 96, 0, False, True, 16),
+])
+def test_qk_norm_rope_kvwrite(dtype, H, Hkv, D, R, inter, norm, page):
+    from tinyserve_b200.parts.rotary import Rotary
+    T, pages, eps = 11, 6, 1e-5
+    qkv = rnd(T, (H + 2 * Hkv) * D, seed=7, dtype=dtype)
+    pos = torch.tensor([0, 1, 2, 30, 31, 32, 5, 6, 7, 63, 9], dtype=torch.int32).cuda()
+    slots = torch.randperm(pages * page, generator=torch.Generator().manual_seed(3))[:T].int().cuda()
+    slots[5] = -1                       # this token writes nothing
+    rot = None
+    if R:
+        rot = Rotary(R, 1e4, "interleaved" if inter else "half")
+        rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(R, 1e4, 64))
+    wdt = torch.float32 if D == 48 else dtype
+    qw, kw = (rnd(D, seed=8, dtype=wdt) + 1, rnd(D, seed=9, dtype=wdt) + 1) if norm else (None, None)
+    kc = torch.full((pages, Hkv, page, D), 7.0, dtype=dtype).cuda()
+    vc = torch.full((pages, Hkv, page, D), 7.0, dtype=dtype).cuda()
+    q = ops().qk_norm_rope_kvwrite(qkv, pos, H, Hkv, D, rotary=rot, q_weight=qw, k_weight=kw, eps=eps,
+                                   k_cache=kc, v_cache=vc, slot_mapping=slots, page_size=page)
+    x = qkv.double().cpu()
+    qr, kr, vr = x.split([H * D, Hkv * D, Hkv * D], -1)
+    qr, kr, vr = qr.view(T, H, D), kr.view(T, Hkv, D), vr.view(T, Hkv, D)
+    if norm:
+        n = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w.double().cpu()
+        qr, kr = n(qr, qw), n(kr, kw)
+    if R:
+        p = pos.long().cpu()
+        qr, kr = (_rope_ref(t, p, rot.cos.cpu(), rot.sin.cpu(), R, inter) for t in (qr, kr))
+    close(q, qr, dtype, "q")
+    want_k = torch.full((pages, Hkv, page, D), 7.0, dtype=torch.float64)
+    want_v = want_k.clone()
+    for t, s in enumerate(slots.tolist()):
+        if s >= 0:
+            want_k[s // page, :, s % page] = kr[t]
+            want_v[s // page, :, s % page] = vr[t]
+    close(kc, want_k, dtype, "k cache")
+    assert torch.equal(vc.double().cpu(), want_v), "values are copied as they are"
+    # no slots: only q, the cache stays
+    kc2 = kc.clone()
+    q2 = ops().qk_norm_rope_kvwrite(qkv, pos, H, Hkv, D, rotary=rot, q_weight=qw, k_weight=kw, eps=eps)
+    assert torch.equal(q2, q) and torch.equal(kc2, kc)
+
+
+# ----------------------------------------------------------------------------- matrix product
+@pytest.mark.parametrize("M,N,K", [(5, 77, 50), (1, 301, 72), (70, 130, 52), (200, 96, 257), (33, 40, 8)])
+@pytest.mark.parametrize("dtypes", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+def test_gemm_simt(M, N, K, dtypes):
+    dtype, f32_out = dtypes
+    o = ops()
+    x, w, b = rnd(M, K, seed=1, dtype=dtype), rnd(N, K, seed=2, dtype=dtype), rnd(N, seed=3, dtype=dtype)
+    old, o.BF16_GEMM = o.BF16_GEMM, "simt"
+    try:
+        out = o.linear(x, w, b, out_float32=f32_out)
+        want = x.double() @ w.double().T + b.double()
+        assert out.dtype == (torch.float32 if f32_out or dtype == torch.float32 else dtype)
+        close(out, want, torch.float32 if f32_out else dtype, "gemm")
+        # a row's result does not depend on the rows around it
+        alone = o.linear(x[M // 2:M // 2 + 1].contiguous(), w, b, out_float32=f32_out)
+        assert torch.equal(alone[0], out[M // 2])
+    finally:
+        o.BF16_GEMM = old
+
+
+def test_linear_bf16_library_path():
+    x, w = rnd(9, 136, seed=1, dtype=torch.bfloat16), rnd(50, 136, seed=2, dtype=torch.bfloat16)
+    out = ops().linear(x, w, out_float32=True)
+    assert out.dtype == torch.float32
+    close(out, x.double() @ w.double().T, torch.float32, "bf16 in, f32 out")
+    close(ops().linear(x, w), x.double() @ w.double().T, torch.bfloat16, "bf16")
+
+
+# ----------------------------------------------------------------------------- attention
+def _paged(k, v, page, num_pages, seed):
+    """Scatter per-request keys/values [n, Hkv, D] into shuffled pages.  Returns caches and a
+    block table.  Unused slots hold large values, so that reading them shows."""
+    Hkv, D = k[0].shape[1:]
+    g = torch.Generator().manual_seed(seed)
+    order = (torch.randperm(num_pages - 1, generator=g) + 1).tolist()
+    kc = torch.full((num_pages, Hkv, page, D), 50.0, dtype=k[0].dtype)
+    vc = torch.full((num_pages, Hkv, page, D), -50.0, dtype=k[0].dtype)
+    max_blocks = max(-(-x.shape[0] // page) for x in k) + 2
+    table = torch.zeros(len(k), max_blocks, dtype=torch.int32)
+    for b, (kb, vb) in enumerate(zip(k, v)):
+        for i in range(-(-kb.shape[0] // page)):
+            pg = order.pop()
+            table[b, i] = pg
+            n = min(page, kb.shape[0] - i * page)
+            kc[pg, :, :n] = kb[i * page:i * page + n].transpose(0, 1)
+            vc[pg, :, :n] = vb[i * page:i * page + n].transpose(0, 1)
+    return kc.cuda(), vc.cuda(), table.cuda()
+
+
+def _attention_ref(q, k, v, q_lens, scale, window):
+    """float64 reference: request b's last q_lens[b] positions attend to its keys."""
+    out, at = [], 0
+    for kb, vb, n in zip(k, v, q_lens):
+        kv = kb.shape[0]
+        qb = q[at:at + n].double()
+        G = qb.shape[1] // kb.shape[1]
+        kk, vv = kb.double().repeat_interleave(G, 1), vb.double().repeat_interleave(G, 1)
+        s = torch.einsum("thd,shd->hts", qb, kk) * scale
+        pos = torch.arange(kv - n, kv)
+        j = torch.arange(kv)
+        vis = j[None] <= pos[:, None]
+        if window > 0:
+            vis &= j[None] > pos[:, None] - window
+        s = s.masked_fill(~vis[None], float("-inf"))
+        out.append(torch.einsum("hts,shd->thd", s.softmax(-1), vv))
+        at += n
+    return torch.cat(out)
+
+
+def _run_attention(q, kc, vc, table, q_lens, kv_lens, page, scale, window, splits):
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).cuda()
+    ctx = SimpleNamespace(cu_q=cu, kv_lens=torch.tensor(kv_lens, dtype=torch.int32).cuda(),
+                          num_requests=len(q_lens), max_q_len=max(q_lens), max_kv_len=max(kv_lens))
+    view = SimpleNamespace(block_table=table, page_size=page)
+    return ops().paged_attention(q, kc, vc, view, ctx, scale, window, num_splits=splits)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hkv,D,page", [(6, 2, 48, 8), (4, 4, 16, 16), (8, 1, 64, 4), (40, 1, 32, 16),
+                                           (5, 5, 80, 32), (16, 2, 128, 16)])
+@pytest.mark.parametrize("window,splits", [(0, 1), (0, 3), (23, 1), (23, 4)])
+def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits):
+    # a whole prompt, a decode token, a portion after a prefix, two tokens, a long decode
+    kv_lens, q_lens = [70, 133, 97, 2, 300], [70, 1, 29, 2, 1]
+    k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    v = [rnd(n, Hkv, D, seed=20 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    q = rnd(sum(q_lens), H, D, seed=30, dtype=dtype)
+    kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=1)
+    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
+    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("splits", [1, 5])
+def test_attention_finds_one_far_key(dtype, splits):
+    """Among 700 keys one, on a page of its own early in the sequence, matches the query: the
+    output must be that key's value."""
+    H, Hkv, D, page, n, far = 4, 2, 32, 16, 700, 37
+    k = rnd(n, Hkv, D, seed=1, dtype=dtype, scale=0.1).cpu()
+    v = rnd(n, Hkv, D, seed=2, dtype=dtype).cpu()
+    q = rnd(1, H, D, seed=3, dtype=dtype, scale=0.1)
+    direction = torch.ones(D) / math.sqrt(D)
+    k[far] = (direction * 40).to(dtype)
+    q[0, :] = (direction * 40).to(dtype).cuda()
+    kc, vc, table = _paged([k], [v], page, 60, seed=2)
+    out = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, 0, splits)
+    want = v[far].repeat_interleave(H // Hkv, 0)
+    assert (out[0].float().cpu() - want.float()).abs().max().item() < 1e-3
+    # with a window that ends one key after it, it is hidden; one wider, it is seen
+    hidden = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, n - 1 - far, splits)
+    assert (hidden[0].float().cpu() - want.float()).abs().max().item() > 0.1
+    seen = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, n - far, splits)
+    assert (seen[0].float().cpu() - want.float()).abs().max().item() < 1e-3
+
+
+def test_attention_refuses_what_it_cannot_do():
+    o = ops()
+    with pytest.raises(ValueError, match="head size"):
+        o._attention(24)
+    q = rnd(1, 3, 16)
+    kc = torch.zeros(2, 2, 4, 16).cuda()
+    view = SimpleNamespace(block_table=torch.zeros(1, 2, dtype=torch.int32).cuda(), page_size=4)
+    ctx = SimpleNamespace(cu_q=torch.tensor([0, 1], dtype=torch.int32).cuda(),
+                          kv_lens=torch.tensor([1], dtype=torch.int32).cuda(), num_requests=1,
+                          max_q_len=1, max_kv_len=1)
+    with pytest.raises(RuntimeError, match="heads"):
+        o.paged_attention(q, kc, kc, view, ctx, 1.0)          # 3 heads over 2 KV heads
+    with pytest.raises(RuntimeError, match="CUDA"):
+        o.rmsnorm(torch.zeros(2, 8), torch.ones(8), 1e-6)
+
+
+# ----------------------------------------------------------------------------- sampling
+def test_sampler_greedy_and_ties():
+    logits = rnd(5, 301, seed=1)
+    logits[2, 17] = logits[2, 250] = 9.0          # a tie goes to the lowest id
+    z = torch.zeros(5, device="cuda")
+    out = ops().sample(logits, z, z.long(), z.int(), 0)
+    want = logits.argmax(-1)
+    assert out.tolist()[:2] == want.tolist()[:2] and out[2].item() == 17
+
+
+def test_sampler_matches_the_documented_noise():
+    import numpy as np
+    import plain_qwen3 as plain
+    B, V, seed = 6, 301, 99
+    logits = rnd(B, V, seed=2, scale=2.0)
+    temps = torch.tensor([0.8, 1.0, 0.3, 1.7, 0.0, 0.8]).cuda()
+    streams = torch.tensor([5, 5, 2 ** 40 + 3, 9, 9, 123456789012], dtype=torch.int64).cuda()
+    steps = torch.tensor([0, 1, 7, 3, 3, 0], dtype=torch.int32).cuda()
+    out = ops().sample(logits, temps, streams, steps, seed).tolist()
+    for i in range(B):
+        row = logits[i].cpu()
+        if temps[i] == 0:
+            assert out[i] == int(row.argmax())
+            continue
+        noisy = row.double().numpy() / float(temps[i]) + plain.gumbel_noise(seed, int(streams[i]), int(steps[i]), V)
+        top = np.sort(noisy)[-2:]
+        if top[1] - top[0] > 1e-4:
+            assert out[i] == int(np.argmax(noisy)), i
+    # the same row in another batch, at another place, draws the same token
+    again = ops().sample(logits[[3, 0]].contiguous(), temps[[3, 0]], streams[[3, 0]], steps[[3, 0]], seed)
+    assert again.tolist() == [out[3], out[0]]
+
+
+def test_sampler_top_k_top_p_keep_the_right_tokens():
+    import plain_qwen3 as plain
+    B, V = 8, 301
+    logits = rnd(B, V, seed=3, scale=2.5)
+    temps = torch.full((B,), 0.9).cuda()
+    top_k = torch.tensor([1, 5, 0, 40, 0, 3, 300, 0], dtype=torch.int32).cuda()
+    top_p = torch.tensor([1.0, 1.0, 0.5, 0.9, 0.05, 0.6, 0.99, 1.0]).cuda()
+    kept = [plain.top_k_top_p_mask(logits[i].cpu(), 0.9, int(top_k[i]), float(top_p[i])) for i in range(B)]
+    seen = [set() for _ in range(B)]
+    for trial in range(200):
+        steps = torch.full((B,), trial, dtype=torch.int32).cuda()
+        out = ops().sample(logits, temps, torch.arange(B).cuda(), steps, 1, top_k=top_k, top_p=top_p)
+        for i, t in enumerate(out.tolist()):
+            seen[i].add(t)
+            assert not torch.isinf(kept[i][t]), f"row {i} drew token {t}, which top-k/top-p drops"
+    assert seen[0] == {int(logits[0].argmax())} and len(seen[4]) <= 2
+    sizes = [int((~torch.isinf(k)).sum()) for k in kept]
+    assert sizes[1] == 5 and len(seen[1]) >= 3 and len(seen[7]) > 10
+
+
+def test_repetition_penalty():
+    logits = torch.tensor([[2.0, -1.0, 0.5, 0.0], [1.0, 1.0, -1.0, -2.0], [3.0, 3.0, 3.0, 3.0]]).cuda()
+    rows = torch.tensor([0, 2], dtype=torch.int32).cuda()
+    ids = torch.tensor([[0, 1, -1], [3, -1, -1]], dtype=torch.int32).cuda()
+    ops().apply_repetition_penalty(logits, rows, ids, torch.tensor([1.1, 2.0]).cuda())
+    want = torch.tensor([[2.0 / 1.1, -1.1, 0.5, 0.0], [1.0, 1.0, -1.0, -2.0], [3.0, 3.0, 3.0, 1.5]])
+    assert torch.allclose(logits.cpu(), want)

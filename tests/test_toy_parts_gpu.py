@@ -1,0 +1,172 @@
+"""Generality of the parts: a toy mixer with state of its own, defined here, is registered,
+built into a model beside an attention layer, loaded with random weights and stepped through
+the engine, portions and mixed batches included, without any change to the package."""
+from dataclasses import dataclass
+from typing import ClassVar
+
+import pytest
+import torch
+
+from helpers import random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def _register():
+    from tinyserve_b200.config import (LayerCall, LayerSpec, ModelConfig, ModelSpec, PartSpec,
+                                       register_architecture)
+    from tinyserve_b200.parts import Mixer, ParamSpec, StateSpec, register_mixer
+
+    class DecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + x_t per request; out_t = s_t @ W^T.  The state s lives in
+        the request's state slot between steps."""
+        tree_name = "decay"
+
+        def __init__(self, hidden_size, decay):
+            super().__init__()
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def param_specs(self):
+            return {"proj.weight": ParamSpec((self.hidden_size, self.hidden_size))}
+
+        def state_spec(self):
+            return StateSpec((self.hidden_size,), "float32")
+
+        def forward(self, h, ctx, call):
+            state = ctx.state(call.state)
+            cu, slots, fresh = ctx.host["cu_q"], ctx.host["state_slots"], ctx.host["fresh"]
+            out = torch.empty_like(h, dtype=torch.float32)
+            for b in range(ctx.num_requests):
+                s = torch.zeros_like(state[slots[b]]) if fresh[b] else state[slots[b]].clone()
+                for t in range(cu[b], cu[b + 1]):
+                    s = self.decay * s + h[t].float()
+                    out[t] = s
+                if cu[b + 1] > cu[b]:
+                    state[slots[b]] = s
+            return (out @ self.w["proj.weight"].float().T).to(h.dtype)
+
+    @dataclass(frozen=True)
+    class ToyConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyDecayForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+        decay: float = 0.5
+        heads: int = 2
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["decay"], raw["heads"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size,
+                    "hidden_size": self.hidden_size, "decay": self.decay, "heads": self.heads}
+
+        def model_spec(self):
+            h = self.hidden_size
+            norm = PartSpec("rmsnorm", {"eps": 1e-5})
+            ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 2 * h, "activation": "gelu_tanh"})
+            toy = LayerSpec(PartSpec("toy_decay", {"hidden_size": h, "decay": self.decay}), ffn, norm)
+            attn = LayerSpec(PartSpec("attention", {
+                "hidden_size": h, "num_heads": self.heads, "num_kv_heads": 1, "head_dim": 16,
+                "position": PartSpec("rotary", {"rotary_dim": 8, "theta": 100.0, "pairing": "interleaved"})}),
+                ffn, norm)
+            # the toy layer runs twice (two states), the attention layer between them
+            order = (LayerCall(0, 0), LayerCall(1, 1), LayerCall(0, 2))
+            return ModelSpec(self.vocab_size, h, (toy, attn), order, norm, True)
+
+    register_mixer("toy_decay", DecayMixer)
+    register_architecture(ToyConfig.architecture, ToyConfig)
+    return ToyConfig
+
+
+def _plain_toy(weights, cfg, ids):
+    """The toy model on a whole sequence, float64, written out by hand."""
+    w = {k: v.double() for k, v in weights.items()}
+    h = cfg.hidden_size
+    norm = lambda x, wt: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * wt
+    r = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    T = len(ids)
+
+    def ffn(x, p):
+        g, u = x @ w[p + "gate_proj.weight"].T, x @ w[p + "up_proj.weight"].T
+        return (torch.nn.functional.gelu(g, approximate="tanh") * u) @ w[p + "down_proj.weight"].T
+
+    def decay_mixer(x, p):
+        s, out = torch.zeros(h, dtype=torch.float64), []
+        for t in range(T):
+            s = cfg.decay * s + x[t]
+            out.append(s)
+        return torch.stack(out) @ w[p + "proj.weight"].T
+
+    def attention(x, p):
+        H, D, R = cfg.heads, 16, 8
+        q = (x @ w[p + "q_proj.weight"].T).view(T, H, D)
+        k = (x @ w[p + "k_proj.weight"].T).view(T, 1, D)
+        v = (x @ w[p + "v_proj.weight"].T).view(T, 1, D)
+        inv = 1.0 / 100.0 ** (torch.arange(0, R, 2, dtype=torch.float64) / R)
+        ang = torch.outer(torch.arange(T, dtype=torch.float64), inv)
+        c, s = ang.cos().float().double()[:, None], ang.sin().float().double()[:, None]
+
+        def rope(z):
+            a, b = z[..., 0:R:2], z[..., 1:R:2]
+            rot = torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2)
+            return torch.cat([rot, z[..., R:]], -1)
+        q, k = rope(q), rope(k)
+        sc = torch.einsum("thd,sd->hts", q, k[:, 0]) * D ** -0.5
+        mask = torch.arange(T)[None] <= torch.arange(T)[:, None]
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        o = torch.einsum("hts,sd->thd", sc.softmax(-1), v[:, 0]).reshape(T, H * D)
+        return o @ w[p + "o_proj.weight"].T
+
+    for layer, kind in ((0, "decay"), (1, "attn"), (0, "decay")):
+        p = f"model.layers.{layer}."
+        x = norm(r, w[p + "input_layernorm.weight"])
+        r = r + (decay_mixer(x, p + "decay.") if kind == "decay" else attention(x, p + "self_attn."))
+        r = r + ffn(norm(r, w[p + "post_attention_layernorm.weight"]), p + "mlp.")
+    return norm(r, w["model.norm.weight"]) @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+def test_toy_mixer_with_state_runs_through_the_engine(dtype, tol, tmp_path):
+    import os
+    from safetensors.torch import load_file
+    from tinyserve_b200.config import ARCHITECTURES, EngineConfig
+    from tinyserve_b200.engine.batch import StepEntry
+    from tinyserve_b200.engine.runner import ModelRunner
+    from tinyserve_b200.parts.base import MIXERS
+    from tinyserve_b200.weights import write_random_model
+    ToyConfig = _register()
+    try:
+        cfg = ToyConfig(vocab_size=97, hidden_size=40, decay=0.7, heads=3)
+        folder = write_random_model(cfg, str(tmp_path), seed=3)
+        weights = load_file(os.path.join(folder, "model.safetensors"))
+        assert "model.layers.0.decay.proj.weight" in weights
+        runner = ModelRunner(EngineConfig(model=folder, dtype=dtype, max_model_len=128, block_size=8,
+                                          max_num_seqs=3, max_num_batched_tokens=64, num_blocks=24))
+        assert len(runner.model.state_entries) == 2 and runner.model.group_sizes == [1]
+        assert runner.device_cache.states[0].shape == (3, 40)
+        a, b = random_ids(97, 50, seed=1), random_ids(97, 23, seed=2)
+        ref_a, ref_b = _plain_toy(weights, cfg, a), _plain_toy(weights, cfg, b)
+        mgr = runner.manager
+        mgr.begin("a"); mgr.begin("b")
+        got_a, got_b = [], []
+        # a in portions; b joins later, decodes beside a's portions; slots are used again after
+        got_a.append(runner.step([StepEntry("a", a[:17], list(range(17)))]))
+        out = runner.step([StepEntry("a", a[17:19], [0, 1]), StepEntry("b", b[:20], list(range(20)))])
+        got_a.append(out[:2]); got_b.append(out[2:])
+        for t in range(20, 23):
+            out = runner.step([StepEntry("b", [b[t]], [0]), StepEntry("a", a[19 + (t - 20) * 9:28 + (t - 20) * 9], list(range(9)))])
+            got_b.append(out[:1]); got_a.append(out[1:])
+        got_a.append(runner.step([StepEntry("a", a[46:], list(range(4)))]))
+        mgr.free("a"); mgr.free("b")
+        for got, ref in ((torch.cat(got_a), ref_a), (torch.cat(got_b), ref_b)):
+            assert (got.double().cpu() - ref).abs().max().item() < tol * ref.abs().max().item()
+        # a new request in a used slot starts from a zero state
+        mgr.begin("c")
+        out = runner.step([StepEntry("c", b, list(range(23)))])
+        assert (out.double().cpu() - ref_b).abs().max().item() < tol * ref_b.abs().max().item()
+        mgr.free("c")
+        mgr.check_invariants()
+    finally:
+        ARCHITECTURES.pop("ToyDecayForCausalLM", None)
+        MIXERS.pop("toy_decay", None)

@@ -186,7 +186,9 @@ class ModelRunner:
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
         ctx.decode_only = max_q == 1
         ctx.num_logit_rows = w
-        ctx.host = {"real_tokens": T, "real_requests": B}
+        ctx.host = {"real_tokens": T, "real_requests": B, "cu_q": cu_q[:Bp + 1].tolist(),
+                    "kv_lens": kv_lens[:Bp].tolist(), "state_slots": slots[:Bp].tolist(),
+                    "fresh": fresh[:Bp].tolist()}
         return ctx
 
     def _bind_device_views(self, ctx):
