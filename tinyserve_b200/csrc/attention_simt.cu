@@ -293,3 +293,47 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
   }
   return 0;
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See attention_static_scratch.h: the same kernels, with the split scratch in a fixed array of
+// the library image instead of caller memory.  Host code may not use the array's name as a
+// pointer (it is a host-side stand-in for the symbol); its device address comes from
+// cudaGetSymbolAddress, once per device, and is what the kernels are given.
+#include "attention_static_scratch.h"
+
+static __device__ __align__(256) float ts_static_scratch[TS_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* static_scratch_address[MAX_DEVICES] = {nullptr};
+}  // namespace
+
+TS_EXPORT int ts_paged_attention_static_scratch(
+    int dtype, const void* q, void* out, const void* k_cache, const void* v_cache,
+    const int* block_table, const int* cu_q, const int* kv_lens, int num_tokens, int num_requests,
+    int max_q_len, int H, int Hkv, int page_size, int max_blocks, float scale, int window,
+    int num_splits, cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && H > 0 && num_splits >= 1, "paged_attention_static_scratch: empty batch");
+  const long long rows = (long long)num_tokens * H * num_splits;
+  const long long need = rows * (D + 2);
+  TS_REQUIRE(need <= (long long)TS_STATIC_SCRATCH_FLOATS,
+             "paged_attention_static_scratch: %d tokens x %d heads x %d splits need %lld floats of "
+             "scratch, the static array holds %d",
+             num_tokens, H, num_splits, need, (int)TS_STATIC_SCRATCH_FLOATS);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return ts_fail("paged_attention_static_scratch: %s", cudaGetErrorString(e));
+  TS_REQUIRE(device >= 0 && device < MAX_DEVICES, "paged_attention_static_scratch: device %d out of range", device);
+  if (static_scratch_address[device] == nullptr) {
+    float* address = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), ts_static_scratch);
+    if (e != cudaSuccess || address == nullptr)
+      return ts_fail("paged_attention_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    static_scratch_address[device] = address;
+  }
+  float* part_o = static_scratch_address[device];
+  float* part_ml = part_o + rows * D;
+  return ts_paged_attention(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
+                            num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window,
+                            num_splits, part_o, part_ml, stream);
+}
