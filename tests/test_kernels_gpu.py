@@ -217,11 +217,22 @@ def _run_attention(q, kc, vc, table, q_lens, kv_lens, page, scale, window, split
     return ops().paged_attention(q, kc, vc, view, ctx, scale, window, num_splits=splits)
 
 
+@pytest.fixture(params=["mma", "simt"])
+def bf16_attention(request):
+    """Both bfloat16 attention back ends: tensor cores and the 32-bit FMA kernel."""
+    o = ops()
+    old, o.BF16_ATTENTION = o.BF16_ATTENTION, request.param
+    yield request.param
+    o.BF16_ATTENTION = old
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(6, 2, 48, 8), (4, 4, 16, 16), (8, 1, 64, 4), (40, 1, 32, 16),
-                                           (5, 5, 80, 32), (16, 2, 128, 16)])
+                                           (5, 5, 80, 32), (16, 2, 128, 16), (80, 1, 16, 8), (4, 2, 256, 16)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 3), (23, 1), (23, 4)])
-def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits):
+def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention):
+    if dtype == torch.float32 and bf16_attention == "simt":
+        pytest.skip("float32 has one back end")
     # a whole prompt, a decode token, a portion after a prefix, two tokens, a long decode
     kv_lens, q_lens = [70, 133, 97, 2, 300], [70, 1, 29, 2, 1]
     k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
@@ -233,8 +244,25 @@ def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32)])
+@pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])
+def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention):
+    """Every request brings one token: the decode kernels."""
+    if dtype == torch.float32 and bf16_attention == "simt":
+        pytest.skip("float32 has one back end")
+    kv_lens = [1, 64, 65, 300, 129, 1000, 17]
+    q_lens = [1] * len(kv_lens)
+    k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    v = [rnd(n, Hkv, D, seed=20 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    q = rnd(len(kv_lens), H, D, seed=30, dtype=dtype)
+    kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=4)
+    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
+    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "decode attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("splits", [1, 5])
-def test_attention_finds_one_far_key(dtype, splits):
+def test_attention_finds_one_far_key(dtype, splits, bf16_attention):
     """Among 700 keys one, on a page of its own early in the sequence, matches the query: the
     output must be that key's value."""
     H, Hkv, D, page, n, far = 4, 2, 32, 16, 700, 37

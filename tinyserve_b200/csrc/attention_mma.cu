@@ -1,0 +1,500 @@
+// Paged grouped-query attention on the tensor cores for bfloat16, one head size per build
+// (-DTS_HEAD_DIM=..., a multiple of 16 up to 256).
+//
+// Two kernels share the tile code:
+//   prefill: a block of 4 warps handles 64 rows = (query, head of one KV group) pairs and walks
+//            the visible keys in tiles of 64, K and V double-buffered in shared memory by cp.async;
+//   decode : requests that bring one token.  A block handles the heads of one KV group (up to 16
+//            rows) and one of `num_splits` key ranges; its 4 warps take 16 keys each of every
+//            64-key tile (3 stages in flight) and merge their partial softmax at the end.  The
+//            ranges are merged by attention_combine_kernel.
+// Scores, running maxima, sums and the output accumulate in 32-bit; exp2 with scale * log2(e);
+// the probabilities are rounded to bfloat16 for P * V, as tinykernels.py:386-413 and 993 do.
+// Visibility as serve.py:668-680: key j is seen by the query at position p iff j <= p and, with a
+// window W > 0, j > p - W.  Keys are found through the block table; the cache layout is
+// [page, kv_head, slot, head_dim].
+#include "common.cuh"
+
+#ifndef TS_HEAD_DIM
+#error "compile with -DTS_HEAD_DIM=<head size, a multiple of 16>"
+#endif
+
+TS_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int D = TS_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
+constexpr int CH = D / 8;                 // 16-byte chunks of a row
+constexpr int ROW_BYTES = D * 2 + 16;     // rows are padded by one chunk: ldmatrix without conflicts
+constexpr int THREADS = 128;
+constexpr int BN = 64;                    // keys of a tile
+constexpr int BM = 64;                    // rows of a prefill block
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr bool Q_IN_REGS = D <= 128;
+
+struct MmaAttnParams {
+  const bf16* q;            // [T, H, D]
+  bf16* out;                // [T, H, D]
+  const bf16* k_cache;      // [pages, Hkv, page_size, D]
+  const bf16* v_cache;
+  const int* block_table;   // [B, max_blocks]
+  const int* cu_q;          // [B + 1]
+  const int* kv_lens;       // [B]
+  float* part_o;            // [T, H, splits, D]
+  float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
+  int H, Hkv, page_shift, page_mask, max_blocks;
+  int heads_per_tile, queries_per_tile, head_tiles;
+  int num_splits, window;
+  float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+// 16 bytes global -> shared; `valid` false writes zeros (the source is not read)
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// NKEYS keys from j0 on -> shared memory (keys and values); keys outside [j_lo, j_hi) become zeros
+template <int NKEYS>
+__device__ __forceinline__ void load_kv_tile(char* ks, char* vs, const MmaAttnParams& p, const int* bt,
+                                             int kvh, int j0, int j_lo, int j_hi) {
+  for (int i = threadIdx.x; i < NKEYS * CH; i += THREADS) {
+    const int key = i / CH, c = i % CH;
+    const int j = j0 + key;
+    const bool valid = j >= j_lo && j < j_hi;
+    size_t off = 0;
+    if (valid) {
+      const size_t page = bt[j >> p.page_shift];
+      off = (((page * p.Hkv + kvh) << p.page_shift) + (j & p.page_mask)) * D + c * 8;
+    }
+    cp_async16(smem_u32(ks + key * ROW_BYTES + c * 16), p.k_cache + off, valid);
+    cp_async16(smem_u32(vs + key * ROW_BYTES + c * 16), p.v_cache + off, valid);
+  }
+}
+
+// S[16 x (8 * NT)] += Q[16 x D] * K^T for the NT*8 keys that start at row `key0` of the K tile.
+// `qs` points at this warp's 16 query rows in shared memory (used when the fragments are not held
+// in registers); `qf` holds them otherwise.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const char* qs, const uint32_t (*qf)[4],
+                                        const char* ks, int key0, int lane) {
+  static_assert(NT % 2 == 0, "key tiles come in pairs");
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kstep = 0; kstep < D / 16; ++kstep) {
+    uint32_t a[4];
+    if (Q_IN_REGS) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) a[e] = qf[kstep][e];
+    } else {
+      ldmatrix_x4(a, smem_u32(qs + ((mi & 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi >> 1)) * 16));
+    }
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      ldmatrix_x4(b, smem_u32(ks + (key0 + np * 16 + (mi >> 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi & 1)) * 16));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// O[16 x D] += P[16 x (8 * NT)] * V for the keys that start at row `key0` of the V tile
+template <int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[NT][4], const char* vs,
+                                        int key0, int lane) {
+  const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, smem_u32(vs + (key0 + kk * 16 + (mi & 1) * 8 + r) * ROW_BYTES + (dp * 2 + (mi >> 1)) * 16));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Online softmax of one tile for the two rows a lane holds (g and g + 8 of the warp's 16).
+// s holds raw scores on entry and probabilities on exit.  `jbase` is the position of column 0.
+// pos[h] is the position of row h's query, lo[h] the lowest visible key; a row with pos < 0 sees
+// nothing.
+template <int NT>
+__device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
+                                             float (&l)[2], const int (&pos)[2], const int (&lo)[2],
+                                             int jbase, float scale_log2, int lane) {
+  const int t = lane & 3;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = jbase + nt * 8 + 2 * t + e;
+        const bool visible = j <= pos[h] && j >= lo[h];
+        const float v = visible ? s[nt][2 * h + e] * scale_log2 : -INFINITY;
+        s[nt][2 * h + e] = v;
+        mx = fmaxf(mx, v);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[h], mx);
+    const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+    const float alpha = exp2f(m[h] - m_safe);          // m[h] = -inf gives 0
+    float sum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float pr = exp2f(s[nt][2 * h + e] - m_safe);
+        s[nt][2 * h + e] = pr;
+        sum += pr;
+      }
+    l[h] = l[h] * alpha + sum;       // the four lanes of a row are added up at the end
+    m[h] = m_new;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o[dt][2 * h] *= alpha;
+      o[dt][2 * h + 1] *= alpha;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ prefill (any q_len)
+__global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) {
+  extern __shared__ __align__(16) char smem[];
+  char* Qs = smem;                           // [BM][ROW_BYTES]
+  char* Ks = Qs + BM * ROW_BYTES;            // [2][BN][ROW_BYTES]
+  char* Vs = Ks + 2 * BN * ROW_BYTES;        // [2][BN][ROW_BYTES]
+
+  const int b = blockIdx.z;
+  const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int q0 = blockIdx.x * p.queries_per_tile;
+  if (q0 >= q_len) return;
+  const int kv_len = p.kv_lens[b];
+  const int G = p.H / p.Hkv, GT = p.heads_per_tile, QPT = p.queries_per_tile;
+  const int g0 = head_tile * GT;
+  const int nq = min(QPT, q_len - q0);
+  const int n_valid = QPT > 1 ? nq * GT : min(GT, G - g0);      // valid rows are a prefix
+  const int pos0 = kv_len - q_len + q0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int* bt = p.block_table + (size_t)b * p.max_blocks;
+
+  for (int i = threadIdx.x; i < BM * CH; i += THREADS) {
+    const int r = i / CH, c = i % CH;
+    const bool valid = r < n_valid;
+    const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
+    const bf16* src = valid ? p.q + ((size_t)(q_begin + q0 + qi) * p.H + kvh * G + g0 + gg) * D + c * 8 : p.q;
+    cp_async16(smem_u32(Qs + r * ROW_BYTES + c * 16), src, valid);
+  }
+  const int j_hi = min(kv_len, pos0 + nq);
+  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
+  load_kv_tile<BN>(Ks, Vs, p, bt, kvh, first_tile * BN, j_lo, j_hi);
+  cp_async_commit();
+
+  int pos[2], lo[2];
+  int warp_max_pos = -1;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    pos[h] = r < n_valid ? pos0 + (QPT > 1 ? r / GT : 0) : -1;
+    lo[h] = p.window > 0 ? max(0, pos[h] - p.window + 1) : 0;
+  }
+  {
+    const int last = min(warp * 16 + 15, n_valid - 1);
+    if (last >= warp * 16) warp_max_pos = pos0 + (QPT > 1 ? last / GT : 0);
+  }
+  float o[D / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
+  uint32_t qf[Q_IN_REGS ? D / 16 : 1][4];
+  const char* my_q = Qs + warp * 16 * ROW_BYTES;
+
+  for (int tile = first_tile; tile < end_tile; ++tile) {
+    const int buf = (tile - first_tile) & 1;
+    if (tile + 1 < end_tile)
+      load_kv_tile<BN>(Ks + (buf ^ 1) * BN * ROW_BYTES, Vs + (buf ^ 1) * BN * ROW_BYTES, p, bt, kvh,
+                       (tile + 1) * BN, j_lo, j_hi);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    if (Q_IN_REGS && tile == first_tile) {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int kstep = 0; kstep < D / 16; ++kstep)
+        ldmatrix_x4(qf[kstep], smem_u32(my_q + ((mi & 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi >> 1)) * 16));
+    }
+    if (tile * BN <= warp_max_pos) {      // a warp whose rows all stand before this tile skips it
+      float s[BN / 8][4];
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+      qk_tile<BN / 8>(s, my_q, qf, Ks + buf * BN * ROW_BYTES, 0, lane);
+      softmax_tile<BN / 8>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
+      pv_tile<BN / 8>(o, s, Vs + buf * BN * ROW_BYTES, 0, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int r = warp * 16 + g + 8 * h;
+    float sum = l[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (r >= n_valid) continue;
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+    const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
+    bf16* dst = p.out + ((size_t)(q_begin + q0 + qi) * p.H + kvh * G + g0 + gg) * D;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt)
+      *reinterpret_cast<__nv_bfloat162*>(dst + dt * 8 + 2 * t) =
+          __floats2bfloat162_rn(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
+  }
+}
+
+// ------------------------------------------------------------------ decode (q_len == 1)
+constexpr int DEC_STAGES = 3;
+
+__global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
+  extern __shared__ __align__(16) char smem[];
+  char* Qs = smem;                                   // [16][ROW_BYTES]
+  char* Ks = Qs + 16 * ROW_BYTES;                    // [DEC_STAGES][BN][ROW_BYTES]
+  char* Vs = Ks + DEC_STAGES * BN * ROW_BYTES;       // [DEC_STAGES][BN][ROW_BYTES]
+
+  const int b = blockIdx.z, split = blockIdx.y;
+  const int kvh = blockIdx.x / p.head_tiles, head_tile = blockIdx.x % p.head_tiles;
+  const int q_begin = p.cu_q[b];
+  if (p.cu_q[b + 1] - q_begin != 1) return;
+  const int kv_len = p.kv_lens[b];
+  const int G = p.H / p.Hkv, g0 = head_tile * 16, ng = min(16, G - g0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2;
+  const int* bt = p.block_table + (size_t)b * p.max_blocks;
+  const int qpos = kv_len - 1;
+  const int j_hi = kv_len, j_lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+  const int first_tile = j_lo / BN, total = (j_hi + BN - 1) / BN - first_tile;
+  const int per_split = (total + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = first_tile + split * per_split;
+  const int n_tiles = max(0, min(first_tile + total, tile_begin + per_split) - tile_begin);
+
+  for (int i = threadIdx.x; i < 16 * CH; i += THREADS) {
+    const int r = i / CH, c = i % CH;
+    const bool valid = r < ng;
+    const bf16* src = valid ? p.q + ((size_t)q_begin * p.H + kvh * G + g0 + r) * D + c * 8 : p.q;
+    cp_async16(smem_u32(Qs + r * ROW_BYTES + c * 16), src, valid);
+  }
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s) {
+    if (s < n_tiles)
+      load_kv_tile<BN>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+    cp_async_commit();
+  }
+  int pos[2], lo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    pos[h] = g + 8 * h < ng ? qpos : -1;
+    lo[h] = j_lo;
+  }
+  float o[D / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dt][e] = 0.f;
+  uint32_t qf[Q_IN_REGS ? D / 16 : 1][4];
+
+  for (int it = 0; it < n_tiles; ++it) {
+    const int nxt = it + DEC_STAGES - 1;
+    if (nxt < n_tiles) {
+      const int nb = nxt % DEC_STAGES;
+      load_kv_tile<BN>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_hi);
+    }
+    cp_async_commit();
+    cp_async_wait<DEC_STAGES - 1>();
+    __syncthreads();
+    if (Q_IN_REGS && it == 0) {
+      const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+      for (int kstep = 0; kstep < D / 16; ++kstep)
+        ldmatrix_x4(qf[kstep], smem_u32(Qs + ((mi & 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi >> 1)) * 16));
+    }
+    const int buf = it % DEC_STAGES;
+    const int jbase = (tile_begin + it) * BN + warp * 16;
+    if (jbase < j_hi) {
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      qk_tile<2>(s, Qs, qf, Ks + buf * BN * ROW_BYTES, warp * 16, lane);
+      softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane);
+      pv_tile<2>(o, s, Vs + buf * BN * ROW_BYTES, warp * 16, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps' partial softmax through shared memory (the K buffers are free now)
+  float* sm_o = reinterpret_cast<float*>(Ks);                  // [4][16][D]
+  float* sm_ml = sm_o + 4 * 16 * D;                            // [4][16][2]
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float sum = l[h];
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    const int r = g + 8 * h;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      sm_o[(warp * 16 + r) * D + dt * 8 + 2 * (lane & 3)] = o[dt][2 * h];
+      sm_o[(warp * 16 + r) * D + dt * 8 + 2 * (lane & 3) + 1] = o[dt][2 * h + 1];
+    }
+    if ((lane & 3) == 0) {
+      sm_ml[(warp * 16 + r) * 2] = m[h];
+      sm_ml[(warp * 16 + r) * 2 + 1] = sum;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng * D; i += THREADS) {
+    const int r = i / D, d = i % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mx = fmaxf(mx, sm_ml[(w * 16 + r) * 2]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm_ml[(w * 16 + r) * 2];
+      const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - mx);
+      num = fmaf(wgt, sm_o[(w * 16 + r) * D + d], num);
+      den = fmaf(wgt, sm_ml[(w * 16 + r) * 2 + 1], den);
+    }
+    const size_t row = (size_t)q_begin * p.H + kvh * G + g0 + r;
+    if (p.num_splits == 1) {
+      p.out[row * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      p.part_o[(row * p.num_splits + split) * D + d] = num;
+      if (d == 0) {
+        p.part_ml[(row * p.num_splits + split) * 2] = mx;
+        p.part_ml[(row * p.num_splits + split) * 2 + 1] = den;
+      }
+    }
+  }
+}
+
+// out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         bf16* __restrict__ out, int num_splits, int H) {
+  const size_t row = blockIdx.x;
+  const float* ml = part_ml + row * num_splits * 2;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
+  float den = 0.f;
+  for (int s = 0; s < num_splits; ++s) den += ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - mx) * ml[2 * s + 1];
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float w = ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - mx);
+      v = fmaf(w, part_o[(row * num_splits + s) * D + d], v);
+    }
+    out[row * D + d] = __float2bfloat16_rn(v * inv);
+  }
+}
+
+}  // namespace
+
+TS_EXPORT int ts_attention_mma_head_dim() { return D; }
+
+// decode_only != 0: every request brings one token (requests with another count are skipped);
+// num_splits > 1 needs scratch: part_o T*H*splits*D floats, part_ml T*H*splits*2 floats.
+TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                     const int* block_table, const int* cu_q, const int* kv_lens,
+                                     int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
+                                     int page_size, int max_blocks, float scale, int window,
+                                     int num_splits, float* part_o, float* part_ml, int decode_only,
+                                     cudaStream_t stream) {
+  TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
+  TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
+  TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
+  TS_REQUIRE(num_splits >= 1 && num_splits <= 64, "paged_attention_mma: num_splits %d out of range", num_splits);
+  TS_REQUIRE(num_splits == 1 || (decode_only && part_o && part_ml), "paged_attention_mma: splits are for decode and need scratch");
+  TS_REQUIRE(num_requests <= 65535, "paged_attention_mma: more than 65535 requests");
+  MmaAttnParams p;
+  p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
+  p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
+  p.H = H; p.Hkv = Hkv; p.max_blocks = max_blocks;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < page_size) ++p.page_shift;
+  p.page_mask = page_size - 1;
+  p.num_splits = num_splits; p.window = window; p.scale_log2 = scale * LOG2E;
+  const int G = H / Hkv;
+  cudaError_t e;
+  if (decode_only) {
+    p.heads_per_tile = 16; p.queries_per_tile = 1; p.head_tiles = (G + 15) / 16;
+    const size_t smem = (size_t)(16 + 2 * DEC_STAGES * BN) * ROW_BYTES;
+    static bool configured = false;
+    if (!configured) {
+      e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return ts_fail("paged_attention_mma: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    dim3 grid(Hkv * p.head_tiles, num_splits, num_requests);
+    attn_decode_kernel<<<grid, THREADS, smem, stream>>>(p);
+    TS_CHECK_LAUNCH("attn_decode");
+    if (num_splits > 1) {
+      attention_combine_kernel<<<num_tokens * H, D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream>>>(part_o, part_ml, p.out, num_splits, H);
+      TS_CHECK_LAUNCH("attention_combine");
+    }
+    return 0;
+  }
+  p.heads_per_tile = G < BM ? G : BM;
+  p.queries_per_tile = G < BM ? BM / G : 1;
+  p.head_tiles = (G + p.heads_per_tile - 1) / p.heads_per_tile;
+  const long long gy = (long long)Hkv * p.head_tiles;
+  TS_REQUIRE(gy <= 65535, "paged_attention_mma: too many head tiles");
+  const size_t smem = (size_t)(BM + 4 * BN) * ROW_BYTES;
+  static bool configured_prefill = false;
+  if (!configured_prefill) {
+    e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return ts_fail("paged_attention_mma: %s", cudaGetErrorString(e));
+    configured_prefill = true;
+  }
+  dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
+  attn_prefill_kernel<<<grid, THREADS, smem, stream>>>(p);
+  TS_CHECK_LAUNCH("attn_prefill");
+  return 0;
+}

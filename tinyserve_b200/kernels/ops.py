@@ -18,6 +18,9 @@ _DTYPE = {torch.float32: 0, torch.bfloat16: 1}
 _launches = 0
 #: bfloat16 matrix products: "cublas" (torch.mm) or "simt" (this package's FMA kernel)
 BF16_GEMM = "cublas"
+#: bfloat16 attention: "mma" (tensor cores, head sizes up to 256) or "simt" (32-bit FMA kernel)
+BF16_ATTENTION = "mma"
+MMA_MAX_HEAD_DIM = 256
 
 
 def launch_count() -> int:
@@ -89,6 +92,10 @@ def _attention(head_dim: int):
     return build.load_unit("attention_simt.cu", {"TS_HEAD_DIM": head_dim})
 
 
+def _attention_mma(head_dim: int):
+    return build.load_unit("attention_mma.cu", {"TS_HEAD_DIM": head_dim})
+
+
 def _sampler():
     return build.load_unit("sampler.cu")
 
@@ -97,6 +104,8 @@ def units_for(head_dims) -> list:
     """The (source, defines) units a model with these head sizes needs."""
     units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("sampler.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
+    units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
+              if d <= MMA_MAX_HEAD_DIM]
     return units
 
 
@@ -199,27 +208,56 @@ def attention_splits(num_requests, max_q_len, max_kv_len, num_heads, num_kv_head
     return max(1, min(want, max_kv_len // 128, 32))
 
 
+def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
+    """Key ranges for the tensor-core decode kernel: enough blocks for two per SM, at least two
+    tiles of 64 keys per range."""
+    blocks = num_kv_heads * -(-(num_heads // num_kv_heads) // 16) * num_requests
+    want = -(-2 * NUM_SMS // blocks)
+    return max(1, min(want, max_kv_len // 128, 32))
+
+
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
     """Attention of this step's queries over their requests' cached keys and values.
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
-    kv_lens and the batch's maxima."""
+    kv_lens and the batch's maxima.  bfloat16 runs on the tensor cores (a decode kernel when
+    every request brings one token, else the prefill kernel); float32 on the 32-bit kernel."""
     _cuda(q, k_cache, v_cache)
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
+    mma = q.dtype == torch.bfloat16 and BF16_ATTENTION == "mma" and D <= MMA_MAX_HEAD_DIM \
+        and D in SUPPORTED_HEAD_DIMS
+    decode = mma and ctx.max_q_len == 1
     if num_splits is None:
-        num_splits = attention_splits(ctx.num_requests, ctx.max_q_len, ctx.max_kv_len, H, Hkv)
+        if decode:
+            num_splits = decode_splits(ctx.num_requests, ctx.max_kv_len, H, Hkv)
+        elif mma:
+            num_splits = 1
+        else:
+            num_splits = attention_splits(ctx.num_requests, ctx.max_q_len, ctx.max_kv_len, H, Hkv)
+    if mma and not decode:
+        num_splits = 1
     out = torch.empty_like(q)
     part_o = part_ml = None
     if num_splits > 1:
         part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(T * H * num_splits * 2, dtype=torch.float32, device=q.device)
+    launches = 2 if num_splits > 1 else 1
+    if mma:
+        lib = _attention_mma(D)
+        _check(lib, lib.ts_paged_attention_mma(
+            _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
+            _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
+            c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
+            c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(1 if decode else 0),
+            _stream()), launches)
+        return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention(
         c_int(_dt(q)), _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table),
         _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len),
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
         c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _stream()),
-        2 if num_splits > 1 else 1)
+        launches)
     return out
 
 
