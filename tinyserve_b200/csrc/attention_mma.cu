@@ -200,6 +200,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   char* Ks = Qs + BM * ROW_BYTES;            // [2][BN][ROW_BYTES]
   char* Vs = Ks + 2 * BN * ROW_BYTES;        // [2][BN][ROW_BYTES]
 
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.z;
   const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
@@ -301,6 +303,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   char* Ks = Qs + 16 * ROW_BYTES;                    // [DEC_STAGES][BN][ROW_BYTES]
   char* Vs = Ks + DEC_STAGES * BN * ROW_BYTES;       // [DEC_STAGES][BN][ROW_BYTES]
 
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.z, split = blockIdx.y;
   const int kvh = blockIdx.x / p.head_tiles, head_tile = blockIdx.x % p.head_tiles;
   const int q_begin = p.cu_q[b];
@@ -418,6 +422,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
 // out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int num_splits, int H) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const float* ml = part_ml + row * num_splits * 2;
   float mx = -INFINITY;
@@ -473,11 +479,10 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
       configured = true;
     }
     dim3 grid(Hkv * p.head_tiles, num_splits, num_requests);
-    attn_decode_kernel<<<grid, THREADS, smem, stream>>>(p);
-    TS_CHECK_LAUNCH("attn_decode");
+    TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
     if (num_splits > 1) {
-      attention_combine_kernel<<<num_tokens * H, D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream>>>(part_o, part_ml, p.out, num_splits, H);
-      TS_CHECK_LAUNCH("attention_combine");
+      TS_LAUNCH("attention_combine", attention_combine_kernel, num_tokens * H, D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,
+                (const float*)part_o, (const float*)part_ml, p.out, num_splits, H);
     }
     return 0;
   }
@@ -494,7 +499,6 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
     configured_prefill = true;
   }
   dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
-  attn_prefill_kernel<<<grid, THREADS, smem, stream>>>(p);
-  TS_CHECK_LAUNCH("attn_prefill");
+  TS_LAUNCH("attn_prefill", attn_prefill_kernel, grid, THREADS, smem, stream, p);
   return 0;
 }

@@ -75,6 +75,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attention_kernel(AttnParams 
   float* Vs = Ks + BN * KS;            // [BN][D]
   float* Ps = Vs + BN * D;             // [BM][BN]
 
+  pdl_trigger();
+  pdl_wait();
   const int b = blockIdx.z / p.num_splits, split = blockIdx.z % p.num_splits;
   const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
@@ -220,6 +222,8 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, T* __restrict__ out,
                                          int num_splits) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const float* ml = part_ml + row * num_splits * 2;
   float m = -INFINITY;
@@ -276,20 +280,18 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
   if (dtype == TS_F32) {
     e = cudaFuncSetAttribute(paged_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ts_fail("paged_attention: %s", cudaGetErrorString(e));
-    paged_attention_kernel<float><<<grid, WARPS * 32, smem, stream>>>(p);
+    TS_LAUNCH("paged_attention", paged_attention_kernel<float>, grid, WARPS * 32, smem, stream, p);
   } else {
     e = cudaFuncSetAttribute(paged_attention_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ts_fail("paged_attention: %s", cudaGetErrorString(e));
-    paged_attention_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(p);
+    TS_LAUNCH("paged_attention", paged_attention_kernel<__nv_bfloat16>, grid, WARPS * 32, smem, stream, p);
   }
-  TS_CHECK_LAUNCH("paged_attention");
   if (num_splits > 1) {
     const int threads = D >= 128 ? 128 : (D >= 64 ? 64 : 32);
     if (dtype == TS_F32)
-      attention_combine_kernel<float><<<num_tokens * H, threads, 0, stream>>>(part_o, part_ml, (float*)out, num_splits);
+      TS_LAUNCH("attention_combine", attention_combine_kernel<float>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (float*)out, num_splits);
     else
-      attention_combine_kernel<__nv_bfloat16><<<num_tokens * H, threads, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, num_splits);
-    TS_CHECK_LAUNCH("attention_combine");
+      TS_LAUNCH("attention_combine", attention_combine_kernel<__nv_bfloat16>, num_tokens * H, threads, 0, stream, (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, num_splits);
   }
   return 0;
 }

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 
 #define TS_EXPORT extern "C" __attribute__((visibility("default")))
 
@@ -36,6 +37,47 @@ static inline int ts_fail(const char* fmt, ...) {
 
 #define TS_DEFINE_LAST_ERROR() \
   TS_EXPORT const char* ts_last_error() { return ts_error_message; }
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// Every kernel of this package is launched so that it may start while its predecessor in the
+// stream still runs.  A kernel calls pdl_trigger() at its top (its successor may be launched as
+// soon as all of this kernel's blocks have started) and pdl_wait() before it reads anything a
+// predecessor wrote and before it writes global memory at all; pdl_wait() returns when the
+// predecessor has completed and its writes are visible.  What a kernel does before pdl_wait()
+// (set-up, fetching weights) overlaps the predecessor.  Set TINYSERVE_PDL=0 to launch plainly.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+static inline bool ts_pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("TINYSERVE_PDL");
+    enabled = (v && v[0] == '0') ? 0 : 1;
+  }
+  return enabled != 0;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ts_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ts_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+#define TS_LAUNCH(name, kernel, grid, block, smem, stream, ...)                          \
+  do {                                                                                   \
+    cudaError_t e_ = ts_launch(kernel, grid, block, smem, stream, __VA_ARGS__);          \
+    if (e_ != cudaSuccess) return ts_fail("%s: %s", name, cudaGetErrorString(e_));       \
+  } while (0)
 
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }

@@ -12,6 +12,8 @@ TS_DEFINE_LAST_ERROR()
 template <typename T>
 __global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int n, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * n;
@@ -28,12 +30,11 @@ TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, floa
   TS_REQUIRE(num_tokens > 0 && n > 0 && vocab > 0, "embed_lookup: empty input");
   const int threads = n >= 1024 ? 256 : 128;
   if (dtype == TS_F32)
-    embed_lookup_kernel<float><<<num_tokens, threads, 0, stream>>>((const float*)table, ids, out, n, vocab);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, n, vocab);
   else if (dtype == TS_BF16)
-    embed_lookup_kernel<__nv_bfloat16><<<num_tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, n, vocab);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n, vocab);
   else
     return ts_fail("embed_lookup: unknown dtype %d", dtype);
-  TS_CHECK_LAUNCH("embed_lookup");
   return 0;
 }
 
@@ -46,6 +47,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
                                    VecParam w, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int n, int write_residual) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   const size_t r = rows ? (size_t)rows[i] : (size_t)i;
   const T* xr = x ? x + r * n : nullptr;
@@ -67,20 +70,117 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   }
 }
 
+
+// The same, for rows whose length is a multiple of 4 and at most 4 * 4 * blockDim: every thread
+// keeps its elements in registers between the sum of squares and the output, and moves 16 bytes
+// at a time.
+template <typename T> struct Quad;
+template <> struct Quad<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Quad<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 q = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&q.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 q;
+    q.x = *reinterpret_cast<const uint32_t*>(&a);
+    q.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = q;
+  }
+};
+
+template <typename T, int ITEMS>
+__global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
+                                       float eps, T* __restrict__ out, const int* __restrict__ rows,
+                                       int n, int write_residual) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  // the weights are constants: fetch them while the predecessor still runs
+  float wv[ITEMS][4];
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int c = (threadIdx.x + it * blockDim.x) * 4;
+    if (c < n) {
+      if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv[it]);
+      else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv[it]);
+    }
+  }
+  pdl_wait();
+  const int i = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  float v[ITEMS][4];
+  float acc = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int c = (threadIdx.x + it * blockDim.x) * 4;
+    if (c < n) {
+      Quad<float>::load(residual + r * n + c, v[it]);
+      if (x) {
+        float xv[4];
+        Quad<T>::load(x + r * n + c, xv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[it][e] += xv[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc += v[it][e] * v[it][e];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(acc, scratch) / (float)n + eps);
+#pragma unroll
+  for (int it = 0; it < ITEMS; ++it) {
+    const int c = (threadIdx.x + it * blockDim.x) * 4;
+    if (c < n) {
+      if (write_residual) Quad<float>::store(residual + r * n + c, v[it]);
+      float o[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[e] = v[it][e] * rstd * wv[it][e];
+      Quad<T>::store(out + (size_t)i * n + c, o);
+    }
+  }
+}
+
+template <typename T>
+int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, void* out, const int* rows,
+                       int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+  const bool aligned = n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
+                                      reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w.ptr)) % 16 == 0;
+  const T* xp = static_cast<const T*>(x);
+  T* op = static_cast<T*>(out);
+  if (aligned && n <= 4 * 4 * 1024) {
+    const int quads = n / 4;
+    const int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
+    int threads = ((quads + items - 1) / items + 31) / 32 * 32;
+    if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+    else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+    else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+    return 0;
+  }
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  TS_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+  return 0;
+}
+
 TS_EXPORT int ts_add_rmsnorm(int dtype, const void* x, float* residual, const void* weight,
                              int weight_is_f32, float eps, void* out, const int* rows,
                              int num_out_rows, int n, int write_residual, cudaStream_t stream) {
   TS_REQUIRE(num_out_rows > 0 && n > 0, "add_rmsnorm: empty input");
-  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
   VecParam w{weight, weight_is_f32};
   if (dtype == TS_F32)
-    add_rmsnorm_kernel<float><<<num_out_rows, threads, 0, stream>>>((const float*)x, residual, w, eps, (float*)out, rows, n, write_residual);
-  else if (dtype == TS_BF16)
-    add_rmsnorm_kernel<__nv_bfloat16><<<num_out_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, residual, w, eps, (__nv_bfloat16*)out, rows, n, write_residual);
-  else
-    return ts_fail("add_rmsnorm: unknown dtype %d", dtype);
-  TS_CHECK_LAUNCH("add_rmsnorm");
-  return 0;
+    return launch_add_rmsnorm<float>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, stream);
+  if (dtype == TS_BF16)
+    return launch_add_rmsnorm<__nv_bfloat16>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, stream);
+  return ts_fail("add_rmsnorm: unknown dtype %d", dtype);
 }
 
 // plain RMSNorm of rows stored as T
@@ -88,6 +188,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, VecParam w, float eps, T* __restrict__ out,
                                int n) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const T* xr = x + (size_t)blockIdx.x * n;
   float acc = 0.f;
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
@@ -106,12 +208,11 @@ TS_EXPORT int ts_rmsnorm(int dtype, const void* x, const void* weight, int weigh
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : (n >= 64 ? 128 : 32));
   VecParam w{weight, weight_is_f32};
   if (dtype == TS_F32)
-    rmsnorm_kernel<float><<<num_rows, threads, 0, stream>>>((const float*)x, w, eps, (float*)out, n);
+    TS_LAUNCH("rmsnorm", rmsnorm_kernel<float>, num_rows, threads, 0, stream, (const float*)x, w, eps, (float*)out, n);
   else if (dtype == TS_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<num_rows, threads, 0, stream>>>((const __nv_bfloat16*)x, w, eps, (__nv_bfloat16*)out, n);
+    TS_LAUNCH("rmsnorm", rmsnorm_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, (const __nv_bfloat16*)x, w, eps, (__nv_bfloat16*)out, n);
   else
     return ts_fail("rmsnorm: unknown dtype %d", dtype);
-  TS_CHECK_LAUNCH("rmsnorm");
   return 0;
 }
 
@@ -128,6 +229,8 @@ __device__ __forceinline__ float activate(float g, int act) {
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
                                         int act) {
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= inter) return;
@@ -142,12 +245,11 @@ TS_EXPORT int ts_gated_activation(int dtype, const void* in, void* out, int num_
   TS_REQUIRE(act == ACT_SILU || act == ACT_GELU_TANH, "gated_activation: unknown activation %d", act);
   dim3 grid(num_rows, (inter + 255) / 256);
   if (dtype == TS_F32)
-    gated_activation_kernel<float><<<grid, 256, 0, stream>>>((const float*)in, (float*)out, inter, act);
+    TS_LAUNCH("gated_activation", gated_activation_kernel<float>, grid, 256, 0, stream, (const float*)in, (float*)out, inter, act);
   else if (dtype == TS_BF16)
-    gated_activation_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, act);
+    TS_LAUNCH("gated_activation", gated_activation_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, act);
   else
     return ts_fail("gated_activation: unknown dtype %d", dtype);
-  TS_CHECK_LAUNCH("gated_activation");
   return 0;
 }
 
@@ -172,6 +274,8 @@ __global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __rest
                                             T* __restrict__ v_cache,
                                             const int* __restrict__ slot_mapping, int page_size,
                                             int heads_total) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.y * (blockDim.x >> 5) + warp;
   if (head >= heads_total) return;
@@ -246,15 +350,14 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
   VecParam qw{q_weight, weight_is_f32}, kw{k_weight, weight_is_f32};
   const int has_norm = q_weight != nullptr;
   if (dtype == TS_F32)
-    qk_norm_rope_kvwrite_kernel<float><<<grid, warps * 32, 0, stream>>>(
-        (const float*)qkv, (float*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D,
-        (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
+    TS_LAUNCH("qk_norm_rope_kvwrite", qk_norm_rope_kvwrite_kernel<float>, grid, warps * 32, 0, stream,
+              (const float*)qkv, (float*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D,
+              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
   else if (dtype == TS_BF16)
-    qk_norm_rope_kvwrite_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, positions, rope, qw, kw, has_norm, eps, H,
-        Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
+    TS_LAUNCH("qk_norm_rope_kvwrite", qk_norm_rope_kvwrite_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
+              (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, positions, rope, qw, kw, has_norm, eps, H,
+              Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
   else
     return ts_fail("qk_norm_rope_kvwrite: unknown dtype %d", dtype);
-  TS_CHECK_LAUNCH("qk_norm_rope_kvwrite");
   return 0;
 }

@@ -65,6 +65,8 @@ gemm_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, const TI* __r
   static_assert((BM / TM) * (BN / TN) == THREADS, "tile does not match the block");
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   float acc[TM][TN];
@@ -119,14 +121,13 @@ int launch(const void* A, const void* W, const void* bias, void* C, int M, int N
   if (M > 64) {
     dim3 grid((N + 127) / 128, (M + 127) / 128);
     if (grid.y > 65535) return ts_fail("gemm: M = %d is too large", M);
-    if (vec) gemm_nt_kernel<TI, TO, 128, 128, 8, 8, true><<<grid, THREADS, 0, stream>>>(a, w, b, c, M, N, K, lda, ldw, ldc);
-    else gemm_nt_kernel<TI, TO, 128, 128, 8, 8, false><<<grid, THREADS, 0, stream>>>(a, w, b, c, M, N, K, lda, ldw, ldc);
+    if (vec) TS_LAUNCH("gemm_simt", (gemm_nt_kernel<TI, TO, 128, 128, 8, 8, true>), grid, THREADS, 0, stream, a, w, b, c, M, N, K, lda, ldw, ldc);
+    else TS_LAUNCH("gemm_simt", (gemm_nt_kernel<TI, TO, 128, 128, 8, 8, false>), grid, THREADS, 0, stream, a, w, b, c, M, N, K, lda, ldw, ldc);
   } else {
     dim3 grid((N + 63) / 64, (M + 63) / 64);
-    if (vec) gemm_nt_kernel<TI, TO, 64, 64, 4, 4, true><<<grid, THREADS, 0, stream>>>(a, w, b, c, M, N, K, lda, ldw, ldc);
-    else gemm_nt_kernel<TI, TO, 64, 64, 4, 4, false><<<grid, THREADS, 0, stream>>>(a, w, b, c, M, N, K, lda, ldw, ldc);
+    if (vec) TS_LAUNCH("gemm_simt", (gemm_nt_kernel<TI, TO, 64, 64, 4, 4, true>), grid, THREADS, 0, stream, a, w, b, c, M, N, K, lda, ldw, ldc);
+    else TS_LAUNCH("gemm_simt", (gemm_nt_kernel<TI, TO, 64, 64, 4, 4, false>), grid, THREADS, 0, stream, a, w, b, c, M, N, K, lda, ldw, ldc);
   }
-  TS_CHECK_LAUNCH("gemm_simt");
   return 0;
 }
 

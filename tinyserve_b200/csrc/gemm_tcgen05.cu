@@ -1,0 +1,392 @@
+// out[M, N] = x[M, K] * W[N, K]^T for few tokens (M up to 128), bfloat16, on the 5th-generation
+// tensor cores: the weight-streaming matrix product of decode steps.
+//
+// Roles are swapped against the usual tiling: a block takes 128 rows of W as the M side of
+// tcgen05.mma (so the weights, which are nearly all the bytes, stream through the 128 lanes of
+// the tensor core) and the tokens, padded to TILE_T in {16, 32, 64, 128}, as its N side.  The
+// accumulator D[128 weight rows x TILE_T tokens] lives in tensor memory.  Per 64-wide slice of K
+// one thread issues two TMA loads (W tile 128 x 64, x tile TILE_T x 64, 128-byte swizzle) into a
+// ring of shared-memory stages guarded by mbarriers; another thread issues four
+// tcgen05.mma (K = 16 each) per slice and commits the stage back to the loader.
+//
+// Shapes with few row tiles (N = 4096: 32 tiles for 148 SMs) are also cut along K.  Every block
+// then stores its partial tile to scratch and bumps the tile's counter; the block that arrives
+// last adds the partials in split order (so the sum is the same every run) and writes the
+// output.  Nobody waits for anybody.  Counters return to zero for the next call.
+//
+// Every mbarrier wait is bounded: if a wait runs out, the block raises the library's error flag
+// (ts_gemm_tcgen05_error), lets its copies land, frees its tensor memory and returns.
+// tinyserve leaves these products to cuBLAS (serve.py:847, 883, 916, 919, 1263).
+#include <cuda.h>
+
+#include "common.cuh"
+
+TS_DEFINE_LAST_ERROR()
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int TILE_N = 128;          // weight rows of a block (MMA M)
+constexpr int BK = 64;               // K elements of a stage: 128 bytes, one swizzle row
+constexpr int THREADS = 128;
+constexpr int W_STAGE_BYTES = TILE_N * BK * 2;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+__device__ int g_error_flag = 0;
+
+struct GemmParams {
+  void* out;            // [M, ldc] bfloat16 or float
+  float* partials;      // split-K scratch: [splits][row tiles][token tiles][TILE_T][128]
+  int* counters;        // [row tiles * token tiles], zero between calls
+  int M, N, K, ldc;
+  int splits, out_f32;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// false if the wait ran out (or another thread of the block already gave up)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(&g_error_flag, 1);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle;
+// groups of 8 rows are 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);     // start address, 16-byte units
+  d |= static_cast<uint64_t>(1) << 16;                   // leading byte offset (unused with swizzle)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                   // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                   // 128-byte swizzle
+  return d;
+}
+// instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = tile_t
+__host__ __device__ constexpr uint32_t instr_desc(int tile_t) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(tile_t >> 3) << 17) |
+         (static_cast<uint32_t>(TILE_N >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_load8(uint32_t addr, float (&v)[8]) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(addr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int TILE_T> struct Cfg {
+  static constexpr int X_STAGE_BYTES = TILE_T * BK * 2;
+  static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_STAGE_BYTES;
+  // two blocks share an SM: stay below ~100 KB of stages
+  static constexpr int STAGES = (96 * 1024) / STAGE_BYTES < 2 ? 2 : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
+  static constexpr int TMEM_COLS = TILE_T < 32 ? 32 : TILE_T;
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+};
+
+template <int TILE_T>
+__global__ void __launch_bounds__(THREADS)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmParams p) {
+  using C = Cfg<TILE_T>;
+  extern __shared__ char smem_raw[];
+  char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  char* ctrl = smem + (size_t)C::STAGES * C::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ctrl);            // [STAGES]
+  uint64_t* empty = full + C::STAGES;                            // [STAGES]
+  uint64_t* accum = empty + C::STAGES;                           // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* is_last = const_cast<int*>(abort_flag) + 1;
+
+  pdl_trigger();
+  const int n_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int per = (kb_total + p.splits - 1) / p.splits;
+  const int kb0 = split * per;
+  const int nkb = max(0, min(kb_total, kb0 + per) - kb0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(smem_u32(&full[s]), 1);
+      mbar_init(smem_u32(&empty[s]), 1);
+    }
+    mbar_init(smem_u32(accum), 1);
+    *abort_flag = 0;
+    *is_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)C::TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (threadIdx.x == 0) {
+    // loader: one slice of K per stage.  The weight tiles of the first round do not depend on
+    // the predecessor kernel: they are fetched before pdl_wait(), the token tiles after it.
+    const int pre = min(nkb, C::STAGES);
+    for (int i = 0; i < pre; ++i) {
+      const uint32_t bar = smem_u32(&full[i]);
+      mbar_expect_tx(bar, C::STAGE_BYTES);
+      tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES), &map_w, bar, (kb0 + i) * BK, n_tile * TILE_N);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem_u32(smem + (size_t)i * C::STAGE_BYTES + W_STAGE_BYTES), &map_x, smem_u32(&full[i]),
+                  (kb0 + i) * BK, t_tile * TILE_T);
+    int armed = pre;
+    for (int i = pre; i < nkb; ++i) {
+      const int s = i % C::STAGES;
+      const uint32_t round = i / C::STAGES;
+      if (!mbar_wait(smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) break;
+      const uint32_t bar = smem_u32(&full[s]);
+      mbar_expect_tx(bar, C::STAGE_BYTES);
+      char* stage = smem + (size_t)s * C::STAGE_BYTES;
+      tma_load_2d(smem_u32(stage), &map_w, bar, (kb0 + i) * BK, n_tile * TILE_N);
+      tma_load_2d(smem_u32(stage + W_STAGE_BYTES), &map_x, bar, (kb0 + i) * BK, t_tile * TILE_T);
+      armed = i + 1;
+    }
+    if (*abort_flag) {
+      // let the copies that are still in flight land before the block goes away
+      for (int i = max(0, armed - C::STAGES); i < armed; ++i) {
+        const uint32_t bar = smem_u32(&full[i % C::STAGES]);
+        for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar, (i / C::STAGES) & 1); ++w) {}
+      }
+    }
+  } else if (threadIdx.x == 32) {
+    // issuer: four MMAs of K = 16 per stage
+    pdl_wait();
+    const uint32_t idesc = instr_desc(TILE_T);
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % C::STAGES;
+      ok = mbar_wait(smem_u32(&full[s]), (i / C::STAGES) & 1, abort_flag);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const uint32_t a0 = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+      const uint32_t b0 = a0 + W_STAGE_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / 16; ++k)
+        umma(tmem_base, smem_desc(a0 + k * 32), smem_desc(b0 + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
+      tcgen05_commit(smem_u32(&empty[s]));
+    }
+    if (ok && nkb > 0) tcgen05_commit(smem_u32(accum));
+  } else {
+    pdl_wait();
+  }
+  __syncwarp();
+
+  // epilogue: lane = weight row, columns = tokens
+  bool have = nkb > 0;
+  if (have) have = mbar_wait(smem_u32(accum), 0, abort_flag);
+  have = __all_sync(0xffffffffu, have);      // tcgen05.ld is warp-wide: decide per warp
+  tcgen05_fence_after();
+  const int n = n_tile * TILE_N + warp * 32 + lane;
+  const int t0 = t_tile * TILE_T;
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  if (p.splits == 1) {
+#pragma unroll 1
+    for (int c = 0; c < TILE_T; c += 8) {
+      float v[8];
+      if (have) tmem_load8(taddr + c, v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      if (n < p.N) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int m = t0 + c + i;
+          if (m < p.M) {
+            if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = v[i];
+            else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[i]);
+          }
+        }
+      }
+    }
+  } else {
+    const int tiles = gridDim.x * gridDim.y, tile = t_tile * gridDim.x + n_tile;
+    float* mine = p.partials + ((size_t)split * tiles + tile) * (TILE_T * TILE_N);
+#pragma unroll 1
+    for (int c = 0; c < TILE_T; c += 8) {
+      float v[8];
+      if (have) tmem_load8(taddr + c, v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = v[i];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int before = atomicAdd(&p.counters[tile], 1);
+      *is_last = before == p.splits - 1;
+      if (*is_last) p.counters[tile] = 0;
+    }
+    __syncthreads();
+    if (*is_last) {
+      __threadfence();
+      const float* base = p.partials + (size_t)tile * (TILE_T * TILE_N);
+      const size_t split_stride = (size_t)tiles * (TILE_T * TILE_N);
+      // eight columns at a time, so that eight chains of loads are in flight per thread
+#pragma unroll 1
+      for (int c0 = 0; c0 < TILE_T && t0 + c0 < p.M; c0 += 8) {
+        float sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+        for (int s = 0; s < p.splits; ++s) {
+          const float* src = base + s * split_stride + c0 * TILE_N + warp * 32 + lane;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * TILE_N);
+        }
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int m = t0 + c0 + i;
+            if (m < p.M) {
+              if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = sum[i];
+              else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[i]);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// rows x K bfloat16 matrix with leading dimension ld; boxes of box_rows x 64 elements
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  const cuuint32_t box[2] = {BK, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int TILE_T>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, dim3 grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wx_kernel<TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Cfg<TILE_T>::SMEM);
+    if (e != cudaSuccess) return ts_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  TS_LAUNCH("gemm_tcgen05", gemm_wx_kernel<TILE_T>, grid, THREADS, Cfg<TILE_T>::SMEM, stream, mw, mx, p);
+  return 0;
+}
+
+}  // namespace
+
+// 1 if a block ever gave up on a wait since the library was loaded (reads device memory: syncs)
+TS_EXPORT int ts_gemm_tcgen05_error() {
+  int flag = 0;
+  if (cudaMemcpyFromSymbol(&flag, g_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  return flag;
+}
+
+// scratch floats that `splits` > 1 needs
+TS_EXPORT long long ts_gemm_tcgen05_scratch(int M, int N, int splits) {
+  const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  const long long tiles = (long long)((N + TILE_N - 1) / TILE_N) * ((M + tile_t - 1) / tile_t);
+  return splits > 1 ? (long long)splits * tiles * tile_t * TILE_N : 0;
+}
+
+// x [M, K] (leading dimension ldx), w [N, K] (ldw), out [M, N] (ldc) bfloat16 or float.
+// counters: at least (N / 128 rounded up) * (M tiles) ints, all zero, when splits > 1.
+TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                              long long ldw, long long ldc, int out_f32, int splits, float* partials,
+                              int* counters, cudaStream_t stream) {
+  TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
+  TS_REQUIRE(M <= 65535 * 128, "gemm_tcgen05: too many rows");
+  TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
+  TS_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+  TS_REQUIRE(splits >= 1 && splits <= 64, "gemm_tcgen05: splits out of range");
+  TS_REQUIRE(splits == 1 || (partials && counters), "gemm_tcgen05: split-K needs scratch and counters");
+  const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap mw, mx;
+  TS_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_N), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the weights");
+  TS_REQUIRE(make_map(&mx, x, M, K, ldx, tile_t), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the activations");
+  GemmParams p;
+  p.out = out; p.partials = partials; p.counters = counters;
+  p.M = M; p.N = N; p.K = K; p.ldc = (int)ldc; p.splits = splits; p.out_f32 = out_f32;
+  dim3 grid((N + TILE_N - 1) / TILE_N, (M + tile_t - 1) / tile_t, splits);
+  switch (tile_t) {
+    case 16: return launch<16>(mw, mx, p, grid, stream);
+    case 32: return launch<32>(mw, mx, p, grid, stream);
+    case 64: return launch<64>(mw, mx, p, grid, stream);
+    default: return launch<128>(mw, mx, p, grid, stream);
+  }
+}

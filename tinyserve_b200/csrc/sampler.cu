@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
   __shared__ unsigned long long sh_above;
   __shared__ unsigned long long sh_total;
 
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* x = a.logits + (size_t)row * a.row_stride;
   const int V = a.vocab;
@@ -234,6 +236,8 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
 __global__ void repetition_penalty_kernel(float* logits, long long row_stride, int vocab,
                                           const int* rows, const int* ids, int ids_per_row,
                                           const float* penalty) {
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   float* x = logits + (size_t)rows[r] * row_stride;
   const float p = penalty[r];
@@ -256,8 +260,7 @@ TS_EXPORT int ts_sample(const float* logits, long long row_stride, int num_rows,
   TS_REQUIRE(row_stride >= vocab, "sample: row stride smaller than the vocabulary");
   TS_REQUIRE(temperature && stream_ids && steps && out, "sample: missing argument");
   SampleArgs a{logits, row_stride, vocab, temperature, top_k, top_p, stream_ids, steps, seed, out};
-  sample_kernel<<<num_rows, THREADS, 0, stream>>>(a);
-  TS_CHECK_LAUNCH("sample");
+  TS_LAUNCH("sample", sample_kernel, num_rows, THREADS, 0, stream, a);
   return 0;
 }
 
@@ -266,8 +269,7 @@ TS_EXPORT int ts_apply_repetition_penalty(float* logits, long long row_stride, i
                                           int ids_per_row, const float* penalty,
                                           cudaStream_t stream) {
   TS_REQUIRE(num_rows > 0 && ids_per_row > 0, "repetition_penalty: empty input");
-  repetition_penalty_kernel<<<num_rows, 256, 0, stream>>>(logits, row_stride, vocab, rows, ids,
-                                                          ids_per_row, penalty);
-  TS_CHECK_LAUNCH("repetition_penalty");
+  TS_LAUNCH("repetition_penalty", repetition_penalty_kernel, num_rows, 256, 0, stream, logits, row_stride, vocab,
+            rows, ids, ids_per_row, penalty);
   return 0;
 }

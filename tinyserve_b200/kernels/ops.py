@@ -16,8 +16,10 @@ SUPPORTED_HEAD_DIMS = tuple(range(16, 513, 16))
 _DTYPE = {torch.float32: 0, torch.bfloat16: 1}
 
 _launches = 0
-#: bfloat16 matrix products: "cublas" (torch.mm) or "simt" (this package's FMA kernel)
-BF16_GEMM = "cublas"
+#: bfloat16 matrix products: "tcgen05" (this package's TMA + tcgen05 kernel for up to
+#: TCGEN05_MAX_TOKENS rows, cuBLAS above), "cublas" (torch.mm) or "simt" (the FMA kernel)
+BF16_GEMM = "tcgen05"
+TCGEN05_MAX_TOKENS = 128
 #: bfloat16 attention: "mma" (tensor cores, head sizes up to 256) or "simt" (32-bit FMA kernel)
 BF16_ATTENTION = "mma"
 MMA_MAX_HEAD_DIM = 256
@@ -85,6 +87,64 @@ def _gemm():
     return build.load_unit("gemm_simt.cu")
 
 
+def _gemm_tcgen05():
+    return build.load_unit("gemm_tcgen05.cu")
+
+
+_counters: dict = {}
+
+
+def _tile_counters(device):
+    """Zeroed tile counters of the split-K reduction; the kernel returns them to zero."""
+    key = str(device)
+    if key not in _counters:
+        _counters[key] = torch.zeros(16384, dtype=torch.int32, device=device)
+    return _counters[key]
+
+
+def gemm_splits(M, N, K):
+    """Cuts along K so that a product with few 128-row tiles still fills the SMs (about 160
+    blocks), with at least four 64-wide slices per cut; wide token tiles are cut at most in
+    two, because their partial tiles are large."""
+    tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+    tiles = -(-N // 128) * -(-M // tile_t)
+    if tiles >= NUM_SMS:
+        return 1
+    splits = max(1, min(-(-160 // tiles), -(-K // 64) // 4, 16))
+    return min(splits, 2) if tile_t >= 64 else splits
+
+
+def gemm_tcgen05_error() -> int:
+    """1 if a block of the tcgen05 kernel ever gave up on a wait (synchronises)."""
+    return _gemm_tcgen05().ts_gemm_tcgen05_error()
+
+
+def _tcgen05_ok(x, weight, bias):
+    return (bias is None and x.shape[0] <= TCGEN05_MAX_TOKENS and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0
+            and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def _linear_tcgen05(x, weight, out_float32, splits=None):
+    M, K = x.shape
+    N = weight.shape[0]
+    out = torch.empty(M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
+    if splits is None:
+        splits = gemm_splits(M, N, K)
+    lib = _gemm_tcgen05()
+    partials = counters = None
+    if splits > 1:
+        lib.ts_gemm_tcgen05_scratch.restype = c_longlong
+        need = lib.ts_gemm_tcgen05_scratch(c_int(M), c_int(N), c_int(splits))
+        partials = torch.empty(need, dtype=torch.float32, device=x.device)
+        counters = _tile_counters(x.device)
+    _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                    c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
+                                    c_int(1 if out_float32 else 0), c_int(splits), _ptr(partials),
+                                    _ptr(counters), _stream()))
+    return out
+
+
 def _attention(head_dim: int):
     if head_dim not in SUPPORTED_HEAD_DIMS:
         raise ValueError(f"head size {head_dim} is not supported: attention takes multiples of 16 "
@@ -102,7 +162,7 @@ def _sampler():
 
 def units_for(head_dims) -> list:
     """The (source, defines) units a model with these head sizes needs."""
-    units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("sampler.cu", {})]
+    units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("sampler.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
     units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
@@ -264,13 +324,16 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
 def linear(x, weight, bias=None, out_float32=False):
     """x [M, K] @ weight[N, K]^T (+ bias).  float32 operands: this package's 32-bit FMA kernel
     (no tensor cores, no reduced precision).  bfloat16 operands: cuBLAS through torch.mm, or
-    the FMA kernel when BF16_GEMM == "simt"."""
+    the FMA kernel when BF16_GEMM == "simt"; with BF16_GEMM == "tcgen05" products of up to
+    TCGEN05_MAX_TOKENS rows run on this package's TMA + tcgen05 kernel."""
     _cuda(x, weight, bias)
     M, K = x.shape
     N = weight.shape[0]
     if weight.shape[1] != K or x.dtype != weight.dtype:
         raise ValueError(f"linear: x {tuple(x.shape)} {x.dtype} does not fit weight {tuple(weight.shape)} {weight.dtype}")
-    if x.dtype == torch.bfloat16 and BF16_GEMM == "cublas":
+    if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias):
+        return _linear_tcgen05(x, weight, out_float32)
+    if x.dtype == torch.bfloat16 and BF16_GEMM in ("cublas", "tcgen05"):
         if out_float32:
             out = torch.mm(x, weight.t(), out_dtype=torch.float32)
         else:
