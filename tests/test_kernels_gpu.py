@@ -363,18 +363,23 @@ def test_repetition_penalty():
 
 # ----------------------------------------------------------------------------- tcgen05 product
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 256, 256), (16, 384, 4096), (5, 200, 72), (17, 130, 136),
-                                   (33, 4096, 1024), (64, 1000, 520), (100, 640, 192), (128, 128, 64)])
+                                   (33, 4096, 1024), (64, 1000, 520), (100, 640, 192), (128, 128, 64),
+                                   (8, 40000, 512), (3, 24576, 4096)])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("f32_out", [False, True])
-def test_gemm_tcgen05(M, N, K, splits, f32_out):
+@pytest.mark.parametrize("form", ["persistent", "tiled"])
+def test_gemm_tcgen05(M, N, K, splits, f32_out, form):
     o = ops()
     x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
-    out = o._linear_tcgen05(x, w, f32_out, splits=splits)
+    splits = min(splits, -(-K // 64))
+    # the persistent form is cut by blocks, not by splits: 148, 37 and 7 blocks
+    blocks = {1: 148, 2: 37}.get(splits, 7) if form == "persistent" else None
+    out = o._linear_tcgen05(x, w, f32_out, splits=splits, form=form, blocks=blocks)
     torch.cuda.synchronize()
     assert o.gemm_tcgen05_error() == 0, "a block gave up on a wait"
     want = x.double() @ w.double().T
     close(out, want, torch.float32 if f32_out else torch.bfloat16, "tcgen05 gemm")
-    again = o._linear_tcgen05(x, w, f32_out, splits=splits)
+    again = o._linear_tcgen05(x, w, f32_out, splits=splits, form=form, blocks=blocks)
     assert torch.equal(out, again), "the split-K sum is the same every run"
     assert int(o._tile_counters(x.device).abs().sum()) == 0, "tile counters returned to zero"
 
@@ -383,10 +388,10 @@ def test_linear_picks_tcgen05_and_falls_back():
     o = ops()
     assert o.BF16_GEMM == "tcgen05"
     x, w = rnd(8, 4096, seed=1, dtype=torch.bfloat16), rnd(4096, 4096, seed=2, dtype=torch.bfloat16, scale=0.05)
-    assert o.gemm_splits(8, 4096, 4096) > 1
     close(o.linear(x, w), x.double() @ w.double().T, torch.bfloat16, "decode-shaped")
     x2, w2 = rnd(8, 100, seed=3, dtype=torch.bfloat16), rnd(50, 100, seed=4, dtype=torch.bfloat16)
     close(o.linear(x2, w2), x2.double() @ w2.double().T, torch.bfloat16, "K not a multiple of 8: library")
+    assert o.TCGEN05_MAX_TOKENS < 300
     x3 = rnd(300, 256, seed=5, dtype=torch.bfloat16)
     close(o.linear(x3, w[:64, :256].contiguous()), x3.double() @ w[:64, :256].double().T, torch.bfloat16, "many rows")
     assert o.gemm_tcgen05_error() == 0

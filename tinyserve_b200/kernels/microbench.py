@@ -1,6 +1,6 @@
 """Time one kernel of the package at a given size, after warm-up, with CUDA events.
 
-    python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|cublas]
+    python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|tcgen05_tiled|tcgen05_persistent|cublas]
     python -m tinyserve_b200.kernels.microbench attention --batch 8 --q-len 1 --kv-len 640
     python -m tinyserve_b200.kernels.microbench norm --rows 8 --n 4096
 
@@ -49,14 +49,15 @@ def bench_gemm(a):
     copies = a.copies or max(2, min(16, int(300e6 // nbytes) + 1))
     ws = [torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
-    splits = a.splits or ops.gemm_splits(a.m, a.n, a.k)
-    if a.impl == "tcgen05":
-        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits)
+    form = "tiled" if a.impl == "tcgen05_tiled" else ("persistent" if a.impl == "tcgen05_persistent" else ops.TCGEN05_FORM)
+    splits = (a.splits or ops.gemm_splits(a.m, a.n, a.k)) if form == "tiled" else None
+    if a.impl.startswith("tcgen05"):
+        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, form=form, blocks=a.blocks or None)
     else:
         fn = lambda i: torch.mm(x, ws[i].t())
     us = _time(fn, copies, a.iters, a.graph)
-    err = ops.gemm_tcgen05_error() if a.impl == "tcgen05" else 0
-    return {"kernel": f"gemm_{a.impl}", "m": a.m, "n": a.n, "k": a.k, "splits": splits if a.impl == "tcgen05" else None,
+    err = ops.gemm_tcgen05_error() if a.impl.startswith("tcgen05") else 0
+    return {"kernel": f"gemm_{a.impl}", "m": a.m, "n": a.n, "k": a.k, "splits": splits if a.impl.startswith("tcgen05") else None,
             "us": round(us, 2), "gbs": round((nbytes + a.m * (a.n + a.k) * 2) / us / 1e3, 1),
             "tflops": round(2.0 * a.m * a.n * a.k / us / 1e6, 2), "error_flag": err}
 
@@ -106,7 +107,8 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--impl", choices=["tcgen05", "cublas"], default="tcgen05")
+    ap.add_argument("--blocks", type=int, default=0, help="blocks of the persistent product (default: one per SM)")
+    ap.add_argument("--impl", choices=["tcgen05", "tcgen05_tiled", "tcgen05_persistent", "cublas"], default="tcgen05")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--q-len", type=int, default=1)
     ap.add_argument("--kv-len", type=int, default=640)

@@ -5,6 +5,7 @@ must live on a CUDA device and a missing compiler or library raises."""
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
@@ -19,7 +20,7 @@ _launches = 0
 #: bfloat16 matrix products: "tcgen05" (this package's TMA + tcgen05 kernel for up to
 #: TCGEN05_MAX_TOKENS rows, cuBLAS above), "cublas" (torch.mm) or "simt" (the FMA kernel)
 BF16_GEMM = "tcgen05"
-TCGEN05_MAX_TOKENS = 128
+TCGEN05_MAX_TOKENS = int(os.environ.get("TINYSERVE_TCGEN05_MAX_TOKENS", "16"))
 #: bfloat16 attention: "mma" (tensor cores, head sizes up to 256) or "simt" (32-bit FMA kernel)
 BF16_ATTENTION = "mma"
 MMA_MAX_HEAD_DIM = 256
@@ -125,16 +126,37 @@ def _tcgen05_ok(x, weight, bias):
             and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def _linear_tcgen05(x, weight, out_float32, splits=None):
+#: "persistent" (stream-K: one block per SM takes an equal stretch of the work) or "tiled" (one
+#: block per row tile and K cut)
+TCGEN05_FORM = os.environ.get("TINYSERVE_GEMM_FORM", "tiled")
+_partials: dict = {}
+
+
+def _persistent_scratch(device):
+    key = str(device)
+    if key not in _partials:
+        _partials[key] = torch.empty(2 * NUM_SMS * 128 * 128, dtype=torch.float32, device=device)
+    return _partials[key]
+
+
+def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None):
     M, K = x.shape
     N = weight.shape[0]
     out = torch.empty(M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
+    form = form or TCGEN05_FORM
+    lib = _gemm_tcgen05()
+    if form == "persistent":
+        blocks = min(blocks or NUM_SMS, NUM_SMS)
+        _check(lib, lib.ts_gemm_tcgen05_persistent(
+            _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
+            c_longlong(weight.stride(0)), c_longlong(N), c_int(1 if out_float32 else 0), c_int(blocks),
+            _ptr(_persistent_scratch(x.device)), _ptr(_tile_counters(x.device)), _stream()))
+        return out
+    lib.ts_gemm_tcgen05_scratch.restype = c_longlong
     if splits is None:
         splits = gemm_splits(M, N, K)
-    lib = _gemm_tcgen05()
     partials = counters = None
     if splits > 1:
-        lib.ts_gemm_tcgen05_scratch.restype = c_longlong
         need = lib.ts_gemm_tcgen05_scratch(c_int(M), c_int(N), c_int(splits))
         partials = torch.empty(need, dtype=torch.float32, device=x.device)
         counters = _tile_counters(x.device)
