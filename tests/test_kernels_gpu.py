@@ -246,10 +246,14 @@ def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf1
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])
-def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention):
+@pytest.mark.parametrize("merge", ["launch", "kernel"])
+def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention, merge, monkeypatch):
     """Every request brings one token: the decode kernels."""
     if dtype == torch.float32 and bf16_attention == "simt":
         pytest.skip("float32 has one back end")
+    if merge == "kernel" and (dtype == torch.float32 or bf16_attention == "simt" or splits == 1):
+        pytest.skip("only the tensor-core decode kernel merges its key ranges itself")
+    monkeypatch.setattr(ops(), "DECODE_MERGE", merge)
     kv_lens = [1, 64, 65, 300, 129, 1000, 17]
     q_lens = [1] * len(kv_lens)
     k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
@@ -394,4 +398,46 @@ def test_linear_picks_tcgen05_and_falls_back():
     assert o.TCGEN05_MAX_TOKENS < 300
     x3 = rnd(300, 256, seed=5, dtype=torch.bfloat16)
     close(o.linear(x3, w[:64, :256].contiguous()), x3.double() @ w[:64, :256].double().T, torch.bfloat16, "many rows")
+    assert o.gemm_tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 1024, 4), (3, 328, 512, 2), (16, 6144, 512, 3), (40, 640, 256, 2)])
+def test_split_partials_and_their_consumers(M, N, K, splits):
+    """A product may stop at its split-K partial tiles; the next kernel adds them while it loads."""
+    from tinyserve_b200.parts.rotary import Rotary
+    o = ops()
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
+    want = x.double() @ w.double().T
+    parts = o._linear_tcgen05(x, w, False, splits=splits, partials_only=True)
+    assert isinstance(parts, o.SplitPartials) and parts.shape == (M, N)
+    close(parts.materialize(), want, torch.bfloat16, "materialize")
+    # residual add + norm straight from the partial tiles: the sum is never rounded to bfloat16
+    res = rnd(M, N, seed=3, scale=2.0)
+    wn = rnd(N, seed=4, dtype=torch.bfloat16) + 1
+    r1 = res.clone()
+    got = o.add_rmsnorm(parts, r1, wn, 1e-6, torch.bfloat16)
+    v = res.double().cpu() + want.cpu()
+    close(got, v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-6) * wn.double().cpu(), torch.bfloat16, "norm")
+    assert (r1.double().cpu() - v).abs().max().item() < 1e-3 * v.abs().max().item()
+    rows = torch.tensor([M - 1, 0], dtype=torch.int32).cuda()
+    r2 = res.clone()
+    got2 = o.add_rmsnorm(parts, r2, wn, 1e-6, torch.bfloat16, rows=rows)
+    assert torch.equal(got2, got[rows.long()]) and torch.equal(r2, res)
+    # q/k norm + rotary + cache write straight from the partial tiles
+    D = 64 if N % 64 == 0 else 8
+    heads = N // D
+    if heads >= 3 and heads % 3 == 0:
+        H = Hkv = heads // 3
+        rot = Rotary(D, 1e4, "half")
+        rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(D, 1e4, 64))
+        pos = torch.arange(M, dtype=torch.int32).cuda()
+        slots = torch.arange(16, 16 + M, dtype=torch.int32).cuda()
+        qw, kw = rnd(D, seed=5, dtype=torch.bfloat16) + 1, rnd(D, seed=6, dtype=torch.bfloat16) + 1
+        caches = [torch.zeros(8, Hkv, 16, D, dtype=torch.bfloat16).cuda() for _ in range(4)]
+        q_a = o.qk_norm_rope_kvwrite(parts, pos, H, Hkv, D, rotary=rot, q_weight=qw, k_weight=kw, eps=1e-6,
+                                     k_cache=caches[0], v_cache=caches[1], slot_mapping=slots, page_size=16)
+        q_b = o.qk_norm_rope_kvwrite(parts.materialize(), pos, H, Hkv, D, rotary=rot, q_weight=qw, k_weight=kw,
+                                     eps=1e-6, k_cache=caches[2], v_cache=caches[3], slot_mapping=slots, page_size=16)
+        for a, b in ((q_a, q_b), (caches[0], caches[2]), (caches[1], caches[3])):
+            assert (a.float() - b.float()).abs().max().item() <= 2e-2 * b.float().abs().max().item()
     assert o.gemm_tcgen05_error() == 0

@@ -7,7 +7,8 @@
 //   decode : requests that bring one token.  A block handles the heads of one KV group (up to 16
 //            rows) and one of `num_splits` key ranges; its 4 warps take 16 keys each of every
 //            64-key tile (3 stages in flight) and merge their partial softmax at the end.  The
-//            ranges are merged by attention_combine_kernel.
+//            ranges are merged by the block of a (request, KV group) that finishes last, or by
+//            attention_combine_kernel when no counters are given.
 // Scores, running maxima, sums and the output accumulate in 32-bit; exp2 with scale * log2(e);
 // the probabilities are rounded to bfloat16 for P * V, as tinykernels.py:386-413 and 993 do.
 // Visibility as serve.py:668-680: key j is seen by the query at position p iff j <= p and, with a
@@ -44,6 +45,7 @@ struct MmaAttnParams {
   const int* kv_lens;       // [B]
   float* part_o;            // [T, H, splits, D]
   float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
+  int* counters;            // [requests * gridDim.x] zeros: the block that arrives last merges the key ranges
   int H, Hkv, page_shift, page_mask, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
@@ -417,6 +419,45 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
       }
     }
   }
+  if (p.num_splits == 1 || p.counters == nullptr) return;
+
+  // The block of this (request, KV group) that arrives last merges the key ranges; nobody waits.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = p.counters + (size_t)b * gridDim.x + blockIdx.x;
+    s_last = atomicAdd(counter, 1) == p.num_splits - 1;
+    if (s_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float* sm_w = sm_o;                                           // [num_splits][16] normalised weights
+  const size_t row0 = (size_t)q_begin * p.H + kvh * G + g0;
+  for (int r = threadIdx.x; r < ng; r += THREADS) {
+    const float* ml = p.part_ml + (row0 + r) * p.num_splits * 2;
+    float mx = -INFINITY;
+    for (int s = 0; s < p.num_splits; ++s) mx = fmaxf(mx, __ldcg(ml + 2 * s));
+    float den = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float ms = __ldcg(ml + 2 * s);
+      den += ms == -INFINITY ? 0.f : exp2f(ms - mx) * __ldcg(ml + 2 * s + 1);
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (int s = 0; s < p.num_splits; ++s) {
+      const float ms = __ldcg(ml + 2 * s);
+      sm_w[s * 16 + r] = ms == -INFINITY ? 0.f : exp2f(ms - mx) * inv;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < ng * D; i += THREADS) {
+    const int r = i / D, d = i % D;
+    const float* po = p.part_o + (row0 + r) * p.num_splits * D + d;
+    float v = 0.f;
+    for (int s = 0; s < p.num_splits; ++s) v = fmaf(sm_w[s * 16 + r], __ldcg(po + (size_t)s * D), v);
+    p.out[(row0 + r) * D + d] = __float2bfloat16_rn(v);
+  }
 }
 
 // out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
@@ -447,12 +488,14 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 
 // decode_only != 0: every request brings one token (requests with another count are skipped);
 // num_splits > 1 needs scratch: part_o T*H*splits*D floats, part_ml T*H*splits*2 floats.
+// counters: num_requests * Hkv * ceil(group / 16) zeroed ints (they return to zero); with them the
+// key ranges are merged inside the decode kernel, without them by a second launch.
 TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
                                      const int* block_table, const int* cu_q, const int* kv_lens,
                                      int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                      int page_size, int max_blocks, float scale, int window,
-                                     int num_splits, float* part_o, float* part_ml, int decode_only,
-                                     cudaStream_t stream) {
+                                     int num_splits, float* part_o, float* part_ml, int* counters,
+                                     int decode_only, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
@@ -462,6 +505,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   MmaAttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
+  p.counters = counters;
   p.H = H; p.Hkv = Hkv; p.max_blocks = max_blocks;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -480,7 +524,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
     }
     dim3 grid(Hkv * p.head_tiles, num_splits, num_requests);
     TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
-    if (num_splits > 1) {
+    if (num_splits > 1 && counters == nullptr) {
       TS_LAUNCH("attention_combine", attention_combine_kernel, num_tokens * H, D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,
                 (const float*)part_o, (const float*)part_ml, p.out, num_splits, H);
     }

@@ -111,6 +111,38 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// Split-K partial tiles of a product [M, N] as gemm_tcgen05.cu leaves them when it is asked for
+// partials only: [split][token tile][row tile][token in tile][row in tile (128)], float.  A
+// consumer kernel adds the splits while it loads, in split order, so the sum is the same every run.
+struct PartialSrc {
+  const float* base;      // null: there are no partials, the consumer reads its ordinary input
+  int splits, n_tiles, t_tiles, tile_t;
+  __device__ __forceinline__ size_t offset(int s, int m, int n) const {
+    const int tile = (m / tile_t) * n_tiles + (n >> 7);
+    return (((size_t)s * (n_tiles * t_tiles) + tile) * tile_t + m % tile_t) * 128 + (n & 127);
+  }
+  __device__ __forceinline__ float load1(int m, int n) const {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += __ldcg(base + offset(s, m, n));
+    return v;
+  }
+  __device__ __forceinline__ float2 load2(int m, int n) const {      // n even
+    float2 v = make_float2(0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float2 q = __ldcg(reinterpret_cast<const float2*>(base + offset(s, m, n)));
+      v.x += q.x; v.y += q.y;
+    }
+    return v;
+  }
+  __device__ __forceinline__ void load4(int m, int n, float (&v)[4]) const {   // n a multiple of 4
+    v[0] = v[1] = v[2] = v[3] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(base + offset(s, m, n)));
+      v[0] += q.x; v[1] += q.y; v[2] += q.z; v[3] += q.w;
+    }
+  }
+};
+
 // sum over a block of up to 1024 threads; every thread gets the result.
 // `scratch` holds 33 floats of shared memory.
 __device__ __forceinline__ float block_sum(float v, float* scratch) {

@@ -45,7 +45,7 @@ TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, floa
 template <typename T>
 __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ residual,
                                    VecParam w, float eps, T* __restrict__ out,
-                                   const int* __restrict__ rows, int n, int write_residual) {
+                                   const int* __restrict__ rows, int n, int write_residual, PartialSrc ps) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -56,7 +56,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   float acc = 0.f;
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     float v = rr[c];
-    if (xr) v += to_f32<T>(xr[c]);
+    if (ps.base) v += ps.load1((int)r, c);
+    else if (xr) v += to_f32<T>(xr[c]);
     acc += v * v;
   }
   const float total = block_sum(acc, scratch);
@@ -64,7 +65,8 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ x, float* __restrict__ 
   T* o = out + (size_t)i * n;
   for (int c = threadIdx.x; c < n; c += blockDim.x) {
     float v = rr[c];
-    if (xr) v += to_f32<T>(xr[c]);
+    if (ps.base) v += ps.load1((int)r, c);
+    else if (xr) v += to_f32<T>(xr[c]);
     if (write_residual) rr[c] = v;
     o[c] = from_f32<T>(v * rstd * w[c]);
   }
@@ -103,7 +105,7 @@ template <> struct Quad<__nv_bfloat16> {
 template <typename T, int ITEMS>
 __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
                                        float eps, T* __restrict__ out, const int* __restrict__ rows,
-                                       int n, int write_residual) {
+                                       int n, int write_residual, PartialSrc ps) {
   __shared__ float scratch[33];
   pdl_trigger();
   // the weights are constants: fetch them while the predecessor still runs
@@ -126,9 +128,10 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     const int c = (threadIdx.x + it * blockDim.x) * 4;
     if (c < n) {
       Quad<float>::load(residual + r * n + c, v[it]);
-      if (x) {
+      if (ps.base || x) {
         float xv[4];
-        Quad<T>::load(x + r * n + c, xv);
+        if (ps.base) ps.load4((int)r, c, xv);
+        else Quad<T>::load(x + r * n + c, xv);
 #pragma unroll
         for (int e = 0; e < 4; ++e) v[it][e] += xv[e];
       }
@@ -152,7 +155,7 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
 
 template <typename T>
 int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, void* out, const int* rows,
-                       int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+                       int num_out_rows, int n, int write_residual, PartialSrc ps, cudaStream_t stream) {
   const bool aligned = n % 4 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(residual) |
                                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w.ptr)) % 16 == 0;
   const T* xp = static_cast<const T*>(x);
@@ -161,25 +164,30 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
     const int quads = n / 4;
     const int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
     int threads = ((quads + items - 1) / items + 31) / 32 * 32;
-    if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
-    else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
-    else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+    if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
+    else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
+    else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
     return 0;
   }
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
-  TS_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual);
+  TS_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
   return 0;
 }
 
+// With `partials` (split-K partial tiles of a product [M, n], see PartialSrc) x is their sum.
 TS_EXPORT int ts_add_rmsnorm(int dtype, const void* x, float* residual, const void* weight,
                              int weight_is_f32, float eps, void* out, const int* rows,
-                             int num_out_rows, int n, int write_residual, cudaStream_t stream) {
+                             int num_out_rows, int n, int write_residual, const float* partials,
+                             int splits, int n_tiles, int t_tiles, int tile_t, cudaStream_t stream) {
   TS_REQUIRE(num_out_rows > 0 && n > 0, "add_rmsnorm: empty input");
+  TS_REQUIRE(partials == nullptr || (x == nullptr && splits > 0 && n_tiles * 128 >= n && tile_t > 0),
+             "add_rmsnorm: partial tiles do not fit the row length");
+  PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
   VecParam w{weight, weight_is_f32};
   if (dtype == TS_F32)
-    return launch_add_rmsnorm<float>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, stream);
+    return launch_add_rmsnorm<float>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, stream);
   if (dtype == TS_BF16)
-    return launch_add_rmsnorm<__nv_bfloat16>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, stream);
+    return launch_add_rmsnorm<__nv_bfloat16>(x, residual, w, eps, out, rows, num_out_rows, n, write_residual, ps, stream);
   return ts_fail("add_rmsnorm: unknown dtype %d", dtype);
 }
 
@@ -216,6 +224,25 @@ TS_EXPORT int ts_rmsnorm(int dtype, const void* x, const void* weight, int weigh
   return 0;
 }
 
+// ------------------------------------------------------------------ split-K partial tiles -> matrix
+template <typename T>
+__global__ void reduce_partials_kernel(PartialSrc ps, T* __restrict__ out, int N) {
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x;
+  for (int n = threadIdx.x; n < N; n += blockDim.x) out[(size_t)m * N + n] = from_f32<T>(ps.load1(m, n));
+}
+
+TS_EXPORT int ts_reduce_partials(int dtype, const float* partials, int splits, int n_tiles, int t_tiles,
+                                 int tile_t, void* out, int M, int N, cudaStream_t stream) {
+  TS_REQUIRE(partials && splits > 0 && M > 0 && N > 0 && n_tiles * 128 >= N, "reduce_partials: bad arguments");
+  PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
+  if (dtype == TS_F32) TS_LAUNCH("reduce_partials", reduce_partials_kernel<float>, M, 256, 0, stream, ps, (float*)out, N);
+  else if (dtype == TS_BF16) TS_LAUNCH("reduce_partials", reduce_partials_kernel<__nv_bfloat16>, M, 256, 0, stream, ps, (__nv_bfloat16*)out, N);
+  else return ts_fail("reduce_partials: unknown dtype %d", dtype);
+  return 0;
+}
+
 // ------------------------------------------------------------------ gated activation
 // in [rows, 2 * inter] = gate | up  ->  out [rows, inter] = act(gate) * up
 enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
@@ -238,19 +265,56 @@ __global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict_
   out[row * inter + c] = from_f32<T>(activate(to_f32<T>(r[c]), act) * to_f32<T>(r[inter + c]));
 }
 
+// 16 bytes per thread and operand, for widths that are a multiple of 16 / sizeof(T)
+template <typename T>
+__global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int act) {
+  constexpr int V = 16 / sizeof(T);
+  pdl_trigger();
+  pdl_wait();
+  const size_t row = blockIdx.x;
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+  if (c >= inter) return;
+  const T* r = in + row * 2 * inter;
+  float g[V], u[V], o[V];
+#pragma unroll
+  for (int h = 0; h < V / 4; ++h) {
+    float a[4], b[4];
+    Quad<T>::load(r + c + 4 * h, a);
+    Quad<T>::load(r + inter + c + 4 * h, b);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { g[4 * h + e] = a[e]; u[4 * h + e] = b[e]; }
+  }
+#pragma unroll
+  for (int e = 0; e < V; ++e) o[e] = activate(g[e], act) * u[e];
+#pragma unroll
+  for (int h = 0; h < V / 4; ++h) {
+    float a[4] = {o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]};
+    Quad<T>::store(out + row * inter + c + 4 * h, a);
+  }
+}
+
+template <typename T>
+int launch_gated_activation(const void* in, void* out, int num_rows, int inter, int act, cudaStream_t stream) {
+  constexpr int V = 16 / sizeof(T);
+  const bool vec = inter % V == 0 && (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  if (vec) {
+    dim3 grid(num_rows, (inter / V + 255) / 256);
+    TS_LAUNCH("gated_activation", gated_activation_vec_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act);
+  } else {
+    dim3 grid(num_rows, (inter + 255) / 256);
+    TS_LAUNCH("gated_activation", gated_activation_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act);
+  }
+  return 0;
+}
+
 TS_EXPORT int ts_gated_activation(int dtype, const void* in, void* out, int num_rows, int inter,
                                   int act, cudaStream_t stream) {
   TS_REQUIRE(num_rows > 0 && inter > 0, "gated_activation: empty input");
   TS_REQUIRE((inter + 255) / 256 <= 65535, "gated_activation: width %d is too large", inter);
   TS_REQUIRE(act == ACT_SILU || act == ACT_GELU_TANH, "gated_activation: unknown activation %d", act);
-  dim3 grid(num_rows, (inter + 255) / 256);
-  if (dtype == TS_F32)
-    TS_LAUNCH("gated_activation", gated_activation_kernel<float>, grid, 256, 0, stream, (const float*)in, (float*)out, inter, act);
-  else if (dtype == TS_BF16)
-    TS_LAUNCH("gated_activation", gated_activation_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, inter, act);
-  else
-    return ts_fail("gated_activation: unknown dtype %d", dtype);
-  return 0;
+  if (dtype == TS_F32) return launch_gated_activation<float>(in, out, num_rows, inter, act, stream);
+  if (dtype == TS_BF16) return launch_gated_activation<__nv_bfloat16>(in, out, num_rows, inter, act, stream);
+  return ts_fail("gated_activation: unknown dtype %d", dtype);
 }
 
 // ------------------------------------------------------------------ q/k norm + rotary + cache write
@@ -273,7 +337,89 @@ __global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __rest
                                             int H, int Hkv, int D, T* __restrict__ k_cache,
                                             T* __restrict__ v_cache,
                                             const int* __restrict__ slot_mapping, int page_size,
-                                            int heads_total) {
+                                            int heads_total, PartialSrc ps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (head >= heads_total) return;
+  const int t = blockIdx.x;
+  const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
+  const int n0 = head * D;
+  auto in = [&](int i) { return ps.base ? ps.load1(t, n0 + i) : to_f32<T>(src[i]); };
+  T* dst;
+  bool is_v = false;
+  VecParam w = qw;
+  if (head < H) {
+    dst = q_out + ((size_t)t * H + head) * D;
+  } else {
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const int kvh = head < H + Hkv ? head - H : head - H - Hkv;
+    is_v = head >= H + Hkv;
+    const size_t page = slot / page_size, in_page = slot % page_size;
+    T* base = is_v ? v_cache : k_cache;
+    dst = base + ((page * Hkv + kvh) * page_size + in_page) * D;
+    w = kw;
+  }
+  if (is_v) {
+    for (int i = lane; i < D; i += 32) dst[i] = ps.base ? from_f32<T>(in(i)) : src[i];
+    return;
+  }
+  float rstd = 1.f;
+  if (has_norm) {
+    float acc = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = in(i);
+      acc += v * v;
+    }
+    rstd = rsqrtf(warp_sum(acc) / (float)D + eps);
+  }
+  const int R = rope.rotary_dim, half = R >> 1;
+  const int pos = positions[t];
+  for (int j = lane; j < half; j += 32) {
+    const int i0 = rope.interleaved ? 2 * j : j;
+    const int i1 = rope.interleaved ? 2 * j + 1 : j + half;
+    float a = in(i0), b = in(i1);
+    if (has_norm) {
+      a = a * rstd * w[i0];
+      b = b * rstd * w[i1];
+    }
+    const float c = rope.cos[(size_t)pos * half + j], s = rope.sin[(size_t)pos * half + j];
+    dst[i0] = from_f32<T>(a * c - b * s);
+    dst[i1] = from_f32<T>(b * c + a * s);
+  }
+  for (int i = R + lane; i < D; i += 32) {
+    float a = in(i);
+    if (has_norm) a = a * rstd * w[i];
+    dst[i] = from_f32<T>(a);
+  }
+}
+
+// Two neighbouring pairs per lane and step, for the pairing (j, j + D/2) over the whole head
+// with D / 2 even: 4- or 8-byte accesses, one cache line per warp and step.
+template <typename T> struct Duo;
+template <> struct Duo<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+};
+template <> struct Duo<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+  }
+};
+
+template <typename T, int STEPS>
+__global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                                const int* __restrict__ positions, RopeArgs rope,
+                                                VecParam qw, VecParam kw, int has_norm, float eps,
+                                                int H, int Hkv, int D, T* __restrict__ k_cache,
+                                                T* __restrict__ v_cache,
+                                                const int* __restrict__ slot_mapping, int page_size,
+                                                int heads_total, PartialSrc ps) {
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -292,41 +438,48 @@ __global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __rest
     const int kvh = head < H + Hkv ? head - H : head - H - Hkv;
     is_v = head >= H + Hkv;
     const size_t page = slot / page_size, in_page = slot % page_size;
-    T* base = is_v ? v_cache : k_cache;
-    dst = base + ((page * Hkv + kvh) * page_size + in_page) * D;
+    dst = (is_v ? v_cache : k_cache) + ((page * Hkv + kvh) * page_size + in_page) * D;
     w = kw;
   }
+  const int half = D >> 1;
+  float2 a[STEPS], b[STEPS];
+  float acc = 0.f;
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < half) {
+      a[s] = ps.base ? ps.load2(t, head * D + j) : Duo<T>::load(src + j);
+      b[s] = ps.base ? ps.load2(t, head * D + half + j) : Duo<T>::load(src + half + j);
+      acc += a[s].x * a[s].x + a[s].y * a[s].y + b[s].x * b[s].x + b[s].y * b[s].y;
+    }
+  }
   if (is_v) {
-    for (int i = lane; i < D; i += 32) dst[i] = src[i];
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+      const int j = 2 * (lane + 32 * s);
+      if (j < half) {
+        Duo<T>::store(dst + j, a[s].x, a[s].y);
+        Duo<T>::store(dst + half + j, b[s].x, b[s].y);
+      }
+    }
     return;
   }
-  float rstd = 1.f;
-  if (has_norm) {
-    float acc = 0.f;
-    for (int i = lane; i < D; i += 32) {
-      const float v = to_f32<T>(src[i]);
-      acc += v * v;
-    }
-    rstd = rsqrtf(warp_sum(acc) / (float)D + eps);
-  }
-  const int R = rope.rotary_dim, half = R >> 1;
+  const float rstd = has_norm ? rsqrtf(warp_sum(acc) / (float)D + eps) : 1.f;
   const int pos = positions[t];
-  for (int j = lane; j < half; j += 32) {
-    const int i0 = rope.interleaved ? 2 * j : j;
-    const int i1 = rope.interleaved ? 2 * j + 1 : j + half;
-    float a = to_f32<T>(src[i0]), b = to_f32<T>(src[i1]);
-    if (has_norm) {
-      a = a * rstd * w[i0];
-      b = b * rstd * w[i1];
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < half) {
+      float a0 = a[s].x, a1 = a[s].y, b0 = b[s].x, b1 = b[s].y;
+      if (has_norm) {
+        a0 *= rstd * w[j]; a1 *= rstd * w[j + 1];
+        b0 *= rstd * w[half + j]; b1 *= rstd * w[half + j + 1];
+      }
+      const float2 c = *reinterpret_cast<const float2*>(rope.cos + (size_t)pos * half + j);
+      const float2 sn = *reinterpret_cast<const float2*>(rope.sin + (size_t)pos * half + j);
+      Duo<T>::store(dst + j, a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+      Duo<T>::store(dst + half + j, b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
     }
-    const float c = rope.cos[(size_t)pos * half + j], s = rope.sin[(size_t)pos * half + j];
-    dst[i0] = from_f32<T>(a * c - b * s);
-    dst[i1] = from_f32<T>(b * c + a * s);
-  }
-  for (int i = R + lane; i < D; i += 32) {
-    float a = to_f32<T>(src[i]);
-    if (has_norm) a = a * rstd * w[i];
-    dst[i] = from_f32<T>(a);
   }
 }
 
@@ -335,7 +488,12 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
                                       int interleaved, const void* q_weight, const void* k_weight,
                                       int weight_is_f32, float eps, int num_tokens, int H, int Hkv,
                                       int D, void* k_cache, void* v_cache, const int* slot_mapping,
-                                      int page_size, cudaStream_t stream) {
+                                      int page_size, const float* partials, int splits, int n_tiles,
+                                      int t_tiles, int tile_t, cudaStream_t stream) {
+  TS_REQUIRE(partials == nullptr || (splits > 0 && n_tiles * 128 >= (H + 2 * Hkv) * D && tile_t > 0),
+             "qk_norm_rope_kvwrite: partial tiles do not fit the row length");
+  TS_REQUIRE(partials == nullptr || D % 2 == 0, "qk_norm_rope_kvwrite: partial tiles need an even head size");
+  PartialSrc ps{partials, splits, n_tiles, t_tiles, tile_t};
   TS_REQUIRE(num_tokens > 0 && H > 0 && Hkv > 0 && D > 0, "qk_norm_rope_kvwrite: empty input");
   TS_REQUIRE(rotary_dim >= 0 && rotary_dim <= D && rotary_dim % 2 == 0,
              "qk_norm_rope_kvwrite: rotary_dim %d does not fit head size %d", rotary_dim, D);
@@ -349,14 +507,32 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
   RopeArgs rope{cos, sin, rotary_dim, interleaved};
   VecParam qw{q_weight, weight_is_f32}, kw{k_weight, weight_is_f32};
   const int has_norm = q_weight != nullptr;
+  // the pairing (j, j + D/2) over the whole head, D / 2 even and at most 256: two pairs per lane
+  const bool vec = rotary_dim == D && !interleaved && (D / 2) % 2 == 0 && D <= 512 &&
+                   (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                    reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) % 8 == 0;
+#define TS_ROPE_VEC(T, STEPS)                                                                          \
+  TS_LAUNCH("qk_norm_rope_kvwrite", (qk_norm_rope_kvwrite_vec_kernel<T, STEPS>), grid, warps * 32, 0, stream, \
+            (const T*)qkv, (T*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D, (T*)k_cache,  \
+            (T*)v_cache, slot_mapping, page_size, heads_total, ps)
+  if (vec && (dtype == TS_F32 || dtype == TS_BF16)) {
+    const int steps = (D / 4 + 31) / 32;        // pairs of pairs per lane
+    if (dtype == TS_F32) {
+      if (steps <= 1) TS_ROPE_VEC(float, 1); else if (steps <= 2) TS_ROPE_VEC(float, 2); else TS_ROPE_VEC(float, 4);
+    } else {
+      if (steps <= 1) TS_ROPE_VEC(__nv_bfloat16, 1); else if (steps <= 2) TS_ROPE_VEC(__nv_bfloat16, 2); else TS_ROPE_VEC(__nv_bfloat16, 4);
+    }
+    return 0;
+  }
+#undef TS_ROPE_VEC
   if (dtype == TS_F32)
     TS_LAUNCH("qk_norm_rope_kvwrite", qk_norm_rope_kvwrite_kernel<float>, grid, warps * 32, 0, stream,
               (const float*)qkv, (float*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D,
-              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total);
+              (float*)k_cache, (float*)v_cache, slot_mapping, page_size, heads_total, ps);
   else if (dtype == TS_BF16)
     TS_LAUNCH("qk_norm_rope_kvwrite", qk_norm_rope_kvwrite_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
               (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, positions, rope, qw, kw, has_norm, eps, H,
-              Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total);
+              Hkv, D, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, slot_mapping, page_size, heads_total, ps);
   else
     return ts_fail("qk_norm_rope_kvwrite: unknown dtype %d", dtype);
   return 0;

@@ -280,6 +280,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
       for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = v[i];
     }
+    if (p.out != nullptr) {
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -314,6 +315,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
+    }
     }
   }
   tcgen05_fence_before();
@@ -672,6 +674,8 @@ TS_EXPORT long long ts_gemm_tcgen05_scratch(int M, int N, int splits) {
 
 // x [M, K] (leading dimension ldx), w [N, K] (ldw), out [M, N] (ldc) bfloat16 or float.
 // counters: at least (N / 128 rounded up) * (M tiles) ints, all zero, when splits > 1.
+// out == nullptr (with splits > 1): only the partial tiles are produced, laid out
+// [split][token tile][row tile][token in tile][row in tile]; a consumer kernel adds them up.
 TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                               long long ldw, long long ldc, int out_f32, int splits, float* partials,
                               int* counters, cudaStream_t stream) {
@@ -680,7 +684,8 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
   TS_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
   TS_REQUIRE(splits >= 1 && splits <= 64, "gemm_tcgen05: splits out of range");
-  TS_REQUIRE(splits == 1 || (partials && counters), "gemm_tcgen05: split-K needs scratch and counters");
+  TS_REQUIRE(splits == 1 || (partials && (counters || out == nullptr)), "gemm_tcgen05: split-K needs scratch and counters");
+  TS_REQUIRE(out != nullptr || splits > 1, "gemm_tcgen05: without an output the partial tiles must be asked for (splits > 1)");
   const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap mw, mx;
   TS_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_N), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the weights");

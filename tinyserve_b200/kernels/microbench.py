@@ -52,7 +52,8 @@ def bench_gemm(a):
     form = "tiled" if a.impl == "tcgen05_tiled" else ("persistent" if a.impl == "tcgen05_persistent" else ops.TCGEN05_FORM)
     splits = (a.splits or ops.gemm_splits(a.m, a.n, a.k)) if form == "tiled" else None
     if a.impl.startswith("tcgen05"):
-        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, form=form, blocks=a.blocks or None)
+        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, form=form, blocks=a.blocks or None,
+                                           partials_only=a.partials_only)
     else:
         fn = lambda i: torch.mm(x, ws[i].t())
     us = _time(fn, copies, a.iters, a.graph)
@@ -120,6 +121,8 @@ def main(argv=None):
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--partials-only", action="store_true",
+                    help="gemm: stop after the split-K partial tiles (a consumer kernel adds them up)")
     a = ap.parse_args(argv)
     ops.require_device("cuda:0")
     out = {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm}[a.kernel](a)

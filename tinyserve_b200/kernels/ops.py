@@ -24,6 +24,42 @@ TCGEN05_MAX_TOKENS = int(os.environ.get("TINYSERVE_TCGEN05_MAX_TOKENS", "16"))
 #: bfloat16 attention: "mma" (tensor cores, head sizes up to 256) or "simt" (32-bit FMA kernel)
 BF16_ATTENTION = "mma"
 MMA_MAX_HEAD_DIM = 256
+#: how the key ranges of split-KV decode are merged: "launch" (a second, tiny kernel) or "kernel"
+#: (inside the decode kernel, by the block that finishes last).  Measured on B200 from CUDA graphs,
+#: 8 requests x 640 keys: 14.4 us with the second launch, 18.9 us merged in the kernel.
+DECODE_MERGE = "launch"
+
+
+class SplitPartials:
+    """The result of a matrix product as split-K partial tiles: the product's kernel stopped
+    before adding them up, because the next kernel (residual add + norm, or the q/k norm + rotary
+    kernel) adds them while it loads, which is cheaper than reducing inside the product.
+    ``materialize()`` adds them up into an ordinary [M, N] tensor for any other consumer."""
+
+    def __init__(self, data, splits, M, N, tile_t, dtype):
+        self.data, self.splits, self.M, self.N, self.tile_t, self.dtype = data, splits, M, N, tile_t, dtype
+        self.n_tiles, self.t_tiles = -(-N // 128), -(-M // tile_t)
+        self.shape = (M, N)
+        self.device = data.device
+
+    def args(self):
+        return (_ptr(self.data), c_int(self.splits), c_int(self.n_tiles), c_int(self.t_tiles),
+                c_int(self.tile_t))
+
+    def materialize(self):
+        out = torch.empty(self.M, self.N, dtype=self.dtype, device=self.device)
+        lib = _elementwise()
+        _check(lib, lib.ts_reduce_partials(c_int(_DTYPE[self.dtype]), *self.args(), _ptr(out),
+                                           c_int(self.M), c_int(self.N), _stream()))
+        return out
+
+
+_NO_PARTIALS = (c_void_p(0), c_int(0), c_int(0), c_int(0), c_int(0))
+
+
+def materialize(x):
+    """An ordinary tensor from what a product returned."""
+    return x.materialize() if isinstance(x, SplitPartials) else x
 
 
 def launch_count() -> int:
@@ -129,6 +165,8 @@ def _tcgen05_ok(x, weight, bias):
 #: "persistent" (stream-K: one block per SM takes an equal stretch of the work) or "tiled" (one
 #: block per row tile and K cut)
 TCGEN05_FORM = os.environ.get("TINYSERVE_GEMM_FORM", "tiled")
+#: let a product cut along K hand its partial tiles to the next kernel instead of adding them up
+SPLIT_PARTIALS = os.environ.get("TINYSERVE_SPLIT_PARTIALS", "1") != "0"
 _partials: dict = {}
 
 
@@ -139,11 +177,12 @@ def _persistent_scratch(device):
     return _partials[key]
 
 
-def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None):
+def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False):
     M, K = x.shape
     N = weight.shape[0]
-    out = torch.empty(M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
-    form = form or TCGEN05_FORM
+    out = None if partials_only else torch.empty(
+        M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
+    form = "tiled" if partials_only else (form or TCGEN05_FORM)
     lib = _gemm_tcgen05()
     if form == "persistent":
         blocks = min(blocks or NUM_SMS, NUM_SMS)
@@ -155,15 +194,20 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None)
     lib.ts_gemm_tcgen05_scratch.restype = c_longlong
     if splits is None:
         splits = gemm_splits(M, N, K)
+    if partials_only and splits < 2:
+        raise ValueError("partial tiles need at least two splits")
     partials = counters = None
     if splits > 1:
         need = lib.ts_gemm_tcgen05_scratch(c_int(M), c_int(N), c_int(splits))
         partials = torch.empty(need, dtype=torch.float32, device=x.device)
-        counters = _tile_counters(x.device)
+        counters = None if partials_only else _tile_counters(x.device)
     _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
                                     c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
                                     c_int(1 if out_float32 else 0), c_int(splits), _ptr(partials),
                                     _ptr(counters), _stream()))
+    if partials_only:
+        tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+        return SplitPartials(partials, splits, M, N, tile_t, torch.bfloat16)
     return out
 
 
@@ -205,8 +249,13 @@ def embed_lookup(table, ids):
 
 def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None):
     """residual (float32, in place) += x; returns rmsnorm(residual) * weight as ``out_dtype``.
-    ``x`` None: no add.  With ``rows`` (int32) only those rows are normalised and returned, and
-    the residual is left as it is."""
+    ``x`` None: no add; ``x`` may be the SplitPartials of a product.  With ``rows`` (int32) only
+    those rows are normalised and returned, and the residual is left as it is."""
+    parts = _NO_PARTIALS
+    if isinstance(x, SplitPartials):
+        if x.shape != tuple(residual.shape):
+            raise TypeError("add_rmsnorm: the partial tiles do not have the residual's shape")
+        parts, x = x.args(), None
     _cuda(x, residual, weight, rows)
     if residual.dtype != torch.float32 or not residual.is_contiguous():
         raise TypeError("the residual stream is contiguous float32")
@@ -219,7 +268,7 @@ def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None):
     _check(lib, lib.ts_add_rmsnorm(c_int(_DTYPE[out_dtype]), _ptr(x), _ptr(residual), _ptr(weight),
                                    c_int(_vec_flag(weight, out_dtype)), c_float(eps), _ptr(out),
                                    _ptr(rows), c_int(num_out), c_int(n),
-                                   c_int(0 if rows is not None else 1), _stream()))
+                                   c_int(0 if rows is not None else 1), *parts, _stream()))
     return out
 
 
@@ -238,6 +287,7 @@ def rmsnorm(x, weight, eps, out=None):
 
 def gated_activation(gate_up, activation="silu"):
     """[rows, 2 I] (gate | up) -> act(gate) * up, [rows, I]."""
+    gate_up = materialize(gate_up)
     _cuda(gate_up)
     rows, two_i = gate_up.shape
     out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
@@ -252,26 +302,38 @@ def qk_norm_rope_kvwrite(qkv, positions, num_heads, num_kv_heads, head_dim, rota
                          slot_mapping=None, page_size=0):
     """Per-head norm of q and k, rotary encoding, q to a [T, H, D] tensor (returned), k and v
     to the cache slots of ``slot_mapping`` (None: nothing is written)."""
-    _cuda(qkv, positions, k_cache, v_cache, slot_mapping)
+    parts, dtype = _NO_PARTIALS, qkv.dtype
+    if isinstance(qkv, SplitPartials):
+        if head_dim % 2:
+            qkv = qkv.materialize()
+        else:
+            parts = qkv.args()
     T = qkv.shape[0]
-    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or not qkv.is_contiguous():
-        raise ValueError("qkv must be contiguous [T, (H + 2 Hkv) * D]")
-    q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv must be [T, (H + 2 Hkv) * D]")
+    device = qkv.device
+    if parts is _NO_PARTIALS:
+        if not qkv.is_contiguous():
+            raise ValueError("qkv must be contiguous")
+    else:
+        qkv = None
+    _cuda(qkv, positions, k_cache, v_cache, slot_mapping)
+    q = torch.empty(T, num_heads, head_dim, dtype=dtype, device=device)
     cos = rotary.cos if rotary is not None else None
     sin = rotary.sin if rotary is not None else None
     rot = rotary.rotary_dim if rotary is not None else 0
     inter = int(rotary.interleaved) if rotary is not None else 0
-    if k_cache is not None and k_cache.dtype != qkv.dtype:
+    if k_cache is not None and k_cache.dtype != dtype:
         raise TypeError("cache and activations differ in dtype")
-    flag = _vec_flag(q_weight, qkv.dtype) if q_weight is not None else 0
+    flag = _vec_flag(q_weight, dtype) if q_weight is not None else 0
     if q_weight is not None and k_weight.dtype != q_weight.dtype:
         raise TypeError("q and k norm weights differ in dtype")
     lib = _elementwise()
     _check(lib, lib.ts_qk_norm_rope_kvwrite(
-        c_int(_dt(qkv)), _ptr(qkv), _ptr(q), _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot),
+        c_int(_DTYPE[dtype]), _ptr(qkv), _ptr(q), _ptr(positions), _ptr(cos), _ptr(sin), c_int(rot),
         c_int(inter), _ptr(q_weight), _ptr(k_weight), c_int(flag), c_float(eps), c_int(T),
         c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), _ptr(k_cache), _ptr(v_cache),
-        _ptr(slot_mapping), c_int(page_size), _stream()))
+        _ptr(slot_mapping), c_int(page_size), *parts, _stream()))
     return q
 
 
@@ -326,12 +388,15 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     launches = 2 if num_splits > 1 else 1
     if mma:
         lib = _attention_mma(D)
+        counters = None
+        if num_splits > 1 and DECODE_MERGE == "kernel" and ctx.num_requests * Hkv * -(-(H // Hkv) // 16) <= 16384:
+            counters, launches = _tile_counters(q.device), 1
         _check(lib, lib.ts_paged_attention_mma(
             _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
             _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
-            c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(1 if decode else 0),
-            _stream()), launches)
+            c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+            c_int(1 if decode else 0), _stream()), launches)
         return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention(
@@ -343,17 +408,23 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     return out
 
 
-def linear(x, weight, bias=None, out_float32=False):
+def linear(x, weight, bias=None, out_float32=False, allow_partials=False):
     """x [M, K] @ weight[N, K]^T (+ bias).  float32 operands: this package's 32-bit FMA kernel
     (no tensor cores, no reduced precision).  bfloat16 operands: cuBLAS through torch.mm, or
     the FMA kernel when BF16_GEMM == "simt"; with BF16_GEMM == "tcgen05" products of up to
-    TCGEN05_MAX_TOKENS rows run on this package's TMA + tcgen05 kernel."""
+    TCGEN05_MAX_TOKENS rows run on this package's TMA + tcgen05 kernel.  With ``allow_partials``
+    the result may be a SplitPartials (the caller hands it to add_rmsnorm, qk_norm_rope_kvwrite,
+    or calls materialize)."""
     _cuda(x, weight, bias)
     M, K = x.shape
     N = weight.shape[0]
     if weight.shape[1] != K or x.dtype != weight.dtype:
         raise ValueError(f"linear: x {tuple(x.shape)} {x.dtype} does not fit weight {tuple(weight.shape)} {weight.dtype}")
+    x = materialize(x)
     if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias):
+        if allow_partials and SPLIT_PARTIALS and not out_float32 and TCGEN05_FORM == "tiled" \
+                and gemm_splits(x.shape[0], weight.shape[0], x.shape[1]) > 1:
+            return _linear_tcgen05(x, weight, False, partials_only=True)
         return _linear_tcgen05(x, weight, out_float32)
     if x.dtype == torch.bfloat16 and BF16_GEMM in ("cublas", "tcgen05"):
         if out_float32:

@@ -56,7 +56,7 @@ class Attention(Mixer):
         return CacheSpec(kind, self.num_kv_heads, self.head_dim, self.window)
 
     def forward(self, h, ctx, call):
-        qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"))
+        qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"), allow_partials=True)
         cache = ctx.cache(call.cache)
         view = ctx.group(cache.group)
         q = ops.qk_norm_rope_kvwrite(
@@ -69,7 +69,7 @@ class Attention(Mixer):
             slot_mapping=view.slot_mapping if call.writes_cache else None,
             page_size=view.page_size)
         out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window)
-        return ops.linear(out.view(out.shape[0], self.q_size), self.w["o_proj.weight"])
+        return ops.linear(out.view(out.shape[0], self.q_size), self.w["o_proj.weight"], allow_partials=True)
 
 
 register_mixer("attention", Attention)

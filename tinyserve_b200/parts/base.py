@@ -103,7 +103,9 @@ class Norm(Part):
         raise NotImplementedError
 
     def add_forward(self, x, residual, rows=None):
-        """residual += x (x may be None), return norm(residual) in the compute dtype."""
+        """residual += x (x may be None), return norm(residual) in the compute dtype.  x is what
+        a mixer or feed-forward returned: a tensor, or a ``kernels.ops.SplitPartials`` (pass it to
+        ops.add_rmsnorm as it is, or turn it into a tensor with ops.materialize)."""
         raise NotImplementedError
 
 
@@ -121,7 +123,8 @@ class Mixer(Part):
         return None
 
     def forward(self, h, ctx, call):
-        """h [T, hidden] in the compute dtype -> [T, hidden].  ``call`` is the
+        """h [T, hidden] in the compute dtype -> [T, hidden] (a tensor, or what ops.linear
+        returned with allow_partials=True).  ``call`` is the
         ``BoundCall`` of the run order: its cache entry, state entry and
         ``writes_cache``."""
         raise NotImplementedError

@@ -27,7 +27,7 @@ class GatedMLP(FeedForward):
     def forward(self, h, ctx):
         gate_up = ops.linear(h, self.w["gate_up_proj.weight"])
         act = ops.gated_activation(gate_up, self.activation)
-        return ops.linear(act, self.w["down_proj.weight"])
+        return ops.linear(act, self.w["down_proj.weight"], allow_partials=True)
 
 
 register_feed_forward("gated_mlp", GatedMLP)
