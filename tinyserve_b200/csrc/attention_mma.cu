@@ -4,6 +4,7 @@
 // Two kernels share the tile code:
 //   prefill: a block of 4 warps handles 64 rows = (query, head of one KV group) pairs and walks
 //            the visible keys in tiles of 64, K and V double-buffered in shared memory by cp.async;
+//            tiles that lie wholly below a warp's rows skip the mask;
 //   decode : requests that bring one token.  A block handles the heads of one KV group (up to 16
 //            rows) and one of `num_splits` key ranges; its 4 warps take 16 keys each of every
 //            64-key tile (3 stages in flight) and merge their partial softmax at the end.  The
@@ -29,9 +30,13 @@ constexpr int D = TS_HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 up to 256");
 constexpr int CH = D / 8;                 // 16-byte chunks of a row
 constexpr int ROW_BYTES = D * 2 + 16;     // rows are padded by one chunk: ldmatrix without conflicts
-constexpr int THREADS = 128;
+constexpr int THREADS = 128;              // decode block
+#ifndef TS_PREFILL_WARPS
+#define TS_PREFILL_WARPS 4
+#endif
+constexpr int PRE_THREADS = 32 * TS_PREFILL_WARPS;   // prefill block: warps of 16 rows each
 constexpr int BN = 64;                    // keys of a tile
-constexpr int BM = 64;                    // rows of a prefill block
+constexpr int BM = 16 * TS_PREFILL_WARPS; // rows of a prefill block
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr bool Q_IN_REGS = D <= 128;
 
@@ -77,16 +82,22 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special function unit; -inf gives 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // NKEYS keys from j0 on -> shared memory (keys and values); keys outside [j_lo, j_hi) become zeros
-template <int NKEYS>
+template <int NKEYS, int NTHREADS>
 __device__ __forceinline__ void load_kv_tile(char* ks, char* vs, const MmaAttnParams& p, const int* bt,
                                              int kvh, int j0, int j_lo, int j_hi) {
-  for (int i = threadIdx.x; i < NKEYS * CH; i += THREADS) {
+  for (int i = threadIdx.x; i < NKEYS * CH; i += NTHREADS) {
     const int key = i / CH, c = i % CH;
     const int j = j0 + key;
     const bool valid = j >= j_lo && j < j_hi;
@@ -153,7 +164,8 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[N
 // s holds raw scores on entry and probabilities on exit.  `jbase` is the position of column 0.
 // pos[h] is the position of row h's query, lo[h] the lowest visible key; a row with pos < 0 sees
 // nothing.
-template <int NT>
+// MASK false: every key of the tile is visible to both rows (no comparisons).
+template <int NT, bool MASK = true>
 __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8][4], float (&m)[2],
                                              float (&l)[2], const int (&pos)[2], const int (&lo)[2],
                                              int jbase, float scale_log2, int lane) {
@@ -166,7 +178,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
         const int j = jbase + nt * 8 + 2 * t + e;
-        const bool visible = j <= pos[h] && j >= lo[h];
+        const bool visible = !MASK || (j <= pos[h] && j >= lo[h]);
         const float v = visible ? s[nt][2 * h + e] * scale_log2 : -INFINITY;
         s[nt][2 * h + e] = v;
         mx = fmaxf(mx, v);
@@ -175,13 +187,13 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
     mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
     const float m_new = fmaxf(m[h], mx);
     const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-    const float alpha = exp2f(m[h] - m_safe);          // m[h] = -inf gives 0
+    const float alpha = fast_exp2(m[h] - m_safe);      // m[h] = -inf gives 0
     float sum = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const float pr = exp2f(s[nt][2 * h + e] - m_safe);
+        const float pr = fast_exp2(s[nt][2 * h + e] - m_safe);
         s[nt][2 * h + e] = pr;
         sum += pr;
       }
@@ -196,7 +208,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NT][4], float (&o)[D / 8
 }
 
 // ------------------------------------------------------------------ prefill (any q_len)
-__global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) {
+__global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams p) {
   extern __shared__ __align__(16) char smem[];
   char* Qs = smem;                           // [BM][ROW_BYTES]
   char* Ks = Qs + BM * ROW_BYTES;            // [2][BN][ROW_BYTES]
@@ -207,7 +219,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   const int b = blockIdx.z;
   const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  const int q0 = blockIdx.x * p.queries_per_tile;
+  // the last queries see the most keys: their blocks go first
+  const int q0 = (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;
   if (q0 >= q_len) return;
   const int kv_len = p.kv_lens[b];
   const int G = p.H / p.Hkv, GT = p.heads_per_tile, QPT = p.queries_per_tile;
@@ -218,7 +231,7 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int* bt = p.block_table + (size_t)b * p.max_blocks;
 
-  for (int i = threadIdx.x; i < BM * CH; i += THREADS) {
+  for (int i = threadIdx.x; i < BM * CH; i += PRE_THREADS) {
     const int r = i / CH, c = i % CH;
     const bool valid = r < n_valid;
     const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
@@ -228,11 +241,11 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   const int j_hi = min(kv_len, pos0 + nq);
   const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
   const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
-  load_kv_tile<BN>(Ks, Vs, p, bt, kvh, first_tile * BN, j_lo, j_hi);
+  load_kv_tile<BN, PRE_THREADS>(Ks, Vs, p, bt, kvh, first_tile * BN, j_lo, j_hi);
   cp_async_commit();
 
   int pos[2], lo[2];
-  int warp_max_pos = -1;
+  int warp_max_pos = -1, warp_min_pos = -1, warp_max_lo = 0;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + g + 8 * h;
@@ -241,7 +254,12 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   }
   {
     const int last = min(warp * 16 + 15, n_valid - 1);
-    if (last >= warp * 16) warp_max_pos = pos0 + (QPT > 1 ? last / GT : 0);
+    if (last >= warp * 16) {
+      warp_max_pos = pos0 + (QPT > 1 ? last / GT : 0);
+      // a tile needs no mask if all 16 rows of the warp are valid and see all of its keys
+      if (last == warp * 16 + 15) warp_min_pos = pos0 + (QPT > 1 ? (warp * 16) / GT : 0);
+      warp_max_lo = p.window > 0 ? max(0, warp_max_pos - p.window + 1) : 0;
+    }
   }
   float o[D / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
@@ -254,8 +272,8 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
   for (int tile = first_tile; tile < end_tile; ++tile) {
     const int buf = (tile - first_tile) & 1;
     if (tile + 1 < end_tile)
-      load_kv_tile<BN>(Ks + (buf ^ 1) * BN * ROW_BYTES, Vs + (buf ^ 1) * BN * ROW_BYTES, p, bt, kvh,
-                       (tile + 1) * BN, j_lo, j_hi);
+      load_kv_tile<BN, PRE_THREADS>(Ks + (buf ^ 1) * BN * ROW_BYTES, Vs + (buf ^ 1) * BN * ROW_BYTES, p, bt,
+                                    kvh, (tile + 1) * BN, j_lo, j_hi);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -272,7 +290,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(MmaAttnParams p) 
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
       qk_tile<BN / 8>(s, my_q, qf, Ks + buf * BN * ROW_BYTES, 0, lane);
-      softmax_tile<BN / 8>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
+      if (tile * BN + BN - 1 <= warp_min_pos && tile * BN >= warp_max_lo)
+        softmax_tile<BN / 8, false>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
+      else
+        softmax_tile<BN / 8, true>(s, o, m, l, pos, lo, tile * BN, p.scale_log2, lane);
       pv_tile<BN / 8>(o, s, Vs + buf * BN * ROW_BYTES, 0, lane);
     }
     __syncthreads();
@@ -331,7 +352,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
     if (s < n_tiles)
-      load_kv_tile<BN>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
     cp_async_commit();
   }
   int pos[2], lo[2];
@@ -351,7 +372,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < n_tiles) {
       const int nb = nxt % DEC_STAGES;
-      load_kv_tile<BN>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_hi);
+      load_kv_tile<BN, THREADS>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_hi);
     }
     cp_async_commit();
     cp_async_wait<DEC_STAGES - 1>();
@@ -543,6 +564,6 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
     configured_prefill = true;
   }
   dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
-  TS_LAUNCH("attn_prefill", attn_prefill_kernel, grid, THREADS, smem, stream, p);
+  TS_LAUNCH("attn_prefill", attn_prefill_kernel, grid, PRE_THREADS, smem, stream, p);
   return 0;
 }

@@ -139,16 +139,25 @@ def _tile_counters(device):
     return _counters[key]
 
 
-def gemm_splits(M, N, K):
-    """Cuts along K so that a product with few 128-row tiles still fills the SMs (about 160
-    blocks), with at least four 64-wide slices per cut; wide token tiles are cut at most in
-    two, because their partial tiles are large."""
+def gemm_splits(M, N, K, partials=False):
+    """Cuts along K of the tiled product, so that a product with few 128-row tiles still fills
+    the SMs.  When the product reduces its own partial tiles: about 160 blocks, at least four
+    64-wide slices per cut, wide token tiles cut at most in two (their partial tiles are large).
+    When it hands the partial tiles on (``partials``): all 2 x 148 block slots, at most 8 cuts
+    (measured on B200 at 8 tokens: 6144x4096 best at 6, 4096x4096 and 4096x12288 at 8)."""
     tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = -(-N // 128) * -(-M // tile_t)
+    slices = -(-K // 64)
     if tiles >= NUM_SMS:
         return 1
-    splits = max(1, min(-(-160 // tiles), -(-K // 64) // 4, 16))
-    return min(splits, 2) if tile_t >= 64 else splits
+    if partials:
+        splits = max(1, min(2 * NUM_SMS // tiles, slices // 4, 8))
+    else:
+        splits = max(1, min(-(-160 // tiles), slices // 4, 16))
+        if tile_t >= 64:
+            splits = min(splits, 2)
+    per = -(-slices // splits)
+    return -(-slices // per)           # no cut without a slice
 
 
 def gemm_tcgen05_error() -> int:
@@ -193,7 +202,7 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None,
         return out
     lib.ts_gemm_tcgen05_scratch.restype = c_longlong
     if splits is None:
-        splits = gemm_splits(M, N, K)
+        splits = gemm_splits(M, N, K, partials=partials_only)
     if partials_only and splits < 2:
         raise ValueError("partial tiles need at least two splits")
     partials = counters = None
@@ -219,7 +228,10 @@ def _attention(head_dim: int):
 
 
 def _attention_mma(head_dim: int):
-    return build.load_unit("attention_mma.cu", {"TS_HEAD_DIM": head_dim})
+    defines = {"TS_HEAD_DIM": head_dim}
+    if os.environ.get("TINYSERVE_PREFILL_WARPS"):
+        defines["TS_PREFILL_WARPS"] = int(os.environ["TINYSERVE_PREFILL_WARPS"])
+    return build.load_unit("attention_mma.cu", defines)
 
 
 def _sampler():
@@ -353,11 +365,10 @@ def attention_splits(num_requests, max_q_len, max_kv_len, num_heads, num_kv_head
 
 
 def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
-    """Key ranges for the tensor-core decode kernel: enough blocks for two per SM, at least two
-    tiles of 64 keys per range."""
+    """Key ranges for the tensor-core decode kernel: as many as fit in one wave of blocks (two
+    per SM), with at least two tiles of 64 keys per range."""
     blocks = num_kv_heads * -(-(num_heads // num_kv_heads) // 16) * num_requests
-    want = -(-2 * NUM_SMS // blocks)
-    return max(1, min(want, max_kv_len // 128, 32))
+    return max(1, min(2 * NUM_SMS // blocks, max_kv_len // 128, 32))
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
@@ -423,7 +434,7 @@ def linear(x, weight, bias=None, out_float32=False, allow_partials=False):
     x = materialize(x)
     if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias):
         if allow_partials and SPLIT_PARTIALS and not out_float32 and TCGEN05_FORM == "tiled" \
-                and gemm_splits(x.shape[0], weight.shape[0], x.shape[1]) > 1:
+                and gemm_splits(x.shape[0], weight.shape[0], x.shape[1], partials=True) > 1:
             return _linear_tcgen05(x, weight, False, partials_only=True)
         return _linear_tcgen05(x, weight, out_float32)
     if x.dtype == torch.bfloat16 and BF16_GEMM in ("cublas", "tcgen05"):
