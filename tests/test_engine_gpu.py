@@ -72,16 +72,42 @@ def test_temperature_generation_tiny_b_with_chunked_prefill(tmp_path):
     assert alone.token_ids == outs[3].token_ids
 
 
-def test_preemption_recomputes_the_same_tokens(tmp_path):
+@pytest.mark.parametrize("async_scheduling", [True, False])
+def test_preemption_recomputes_the_same_tokens(tmp_path, async_scheduling):
     folder = make_model_dir(tmp_path, "A", seed=33)
     prompts = [random_ids(256, n, seed=n) for n in (30, 28, 26)]
-    roomy = llm_for(folder, "float32").generate(prompts, greedy(40))
-    tight = llm_for(folder, "float32", num_blocks=9)       # 144 tokens of cache for 3 x ~70
+    roomy = llm_for(folder, "float32", async_scheduling=False).generate(prompts, greedy(40))
+    tight = llm_for(folder, "float32", num_blocks=9, async_scheduling=async_scheduling)   # 144 tokens for 3 x ~70
     outs = tight.generate(prompts, greedy(40))
     assert any(o.was_preempted for o in outs)
     assert [o.token_ids for o in outs] == [o.token_ids for o in roomy]
     tight.runner.manager.check_invariants()
     assert tight.runner.manager.num_free_pages() == 9
+
+
+def test_host_one_step_ahead_gives_the_same_tokens(tmp_path):
+    """The loop that schedules step n+1 while step n runs (tokens fed back on the device) and the
+    one-step-at-a-time loop produce the same tokens, with mixed sampling settings, chunked
+    prompts, a stop token and graphs."""
+    from tinyserve_b200 import SamplingParams
+    folder = make_model_dir(tmp_path, "B", seed=35)
+    prompts = [random_ids(384, n, seed=n) for n in (3, 50, 17, 90, 8, 33)]
+    params = [SamplingParams(temperature=t, max_tokens=m, repetition_penalty=rp, top_k=k, top_p=p, seed=i)
+              for i, (t, m, rp, k, p) in enumerate([(0.0, 30, 1.0, -1, 1.0), (0.8, 25, 1.0, -1, 1.0),
+                                                     (0.0, 12, 1.3, -1, 1.0), (1.0, 40, 1.0, 20, 0.9),
+                                                     (0.0, 1, 1.0, -1, 1.0), (0.7, 33, 1.1, -1, 0.95)])]
+    results = []
+    for async_scheduling, graphs in ((False, False), (True, False), (True, True)):
+        llm = llm_for(folder, "float32", async_scheduling=async_scheduling, use_cuda_graphs=graphs,
+                      max_num_batched_tokens=48, max_num_seqs=4, block_size=8, num_blocks=96)
+        first = llm_for(folder, "float32", async_scheduling=False).generate([prompts[0]], greedy(5))[0].token_ids
+        llm.stop_ids = {first[3]}             # request 0 stops at its fourth token
+        outs = llm.generate(prompts, params)
+        results.append([(o.token_ids, o.finish_reason) for o in outs])
+        assert outs[0].finish_reason == "stop" and outs[0].token_ids == first[:4]
+        assert not llm.has_work() and llm.runner.manager.num_free_pages() == 96
+        llm.runner.manager.check_invariants()
+    assert results[0] == results[1] == results[2]
 
 
 def test_entry_point_options(tmp_path):

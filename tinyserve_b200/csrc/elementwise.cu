@@ -9,13 +9,17 @@
 TS_DEFINE_LAST_ERROR()
 
 // ------------------------------------------------------------------ embedding
+// An id < 0 stands for a token that is still on the device: -1 - slot names the state slot of the
+// request, whose last sampled token the sampler left in slot_tokens[slot].
 template <typename T>
 __global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int n, int vocab) {
+                                    float* __restrict__ out, int n, int vocab,
+                                    const int* __restrict__ slot_tokens) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const int id = ids[t];
+  int id = ids[t];
+  if (id < 0 && slot_tokens) id = slot_tokens[-1 - id];
   float* dst = out + (size_t)t * n;
   if (id < 0 || id >= vocab) {
     for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = 0.f;
@@ -26,13 +30,14 @@ __global__ void embed_lookup_kernel(const T* __restrict__ table, const int* __re
 }
 
 TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, float* out,
-                              int num_tokens, int n, int vocab, cudaStream_t stream) {
+                              int num_tokens, int n, int vocab, const int* slot_tokens,
+                              cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && n > 0 && vocab > 0, "embed_lookup: empty input");
   const int threads = n >= 1024 ? 256 : 128;
   if (dtype == TS_F32)
-    TS_LAUNCH("embed_lookup", embed_lookup_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, n, vocab);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, ids, out, n, vocab, slot_tokens);
   else if (dtype == TS_BF16)
-    TS_LAUNCH("embed_lookup", embed_lookup_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n, vocab);
+    TS_LAUNCH("embed_lookup", embed_lookup_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n, vocab, slot_tokens);
   else
     return ts_fail("embed_lookup: unknown dtype %d", dtype);
   return 0;

@@ -105,6 +105,8 @@ struct SampleArgs {
   const unsigned int* step;           // [rows] position counter of the noise
   unsigned long long seed;
   int* out;                 // [rows]
+  int* slot_tokens;         // optional: the token also goes to slot_tokens[slots[row]]
+  const int* slots;
 };
 
 __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
@@ -126,7 +128,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
     Best b{-INFINITY, 0x7fffffff};
     for (int v = threadIdx.x; v < V; v += THREADS) b = better(b, Best{x[v], v});
     b = block_best(b, best_scratch);
-    if (threadIdx.x == 0) a.out[row] = b.index;
+    if (threadIdx.x == 0) {
+      a.out[row] = b.index;
+      if (a.slot_tokens) a.slot_tokens[a.slots[row]] = b.index;
+    }
     return;
   }
   const float inv_temp = 1.f / temp;
@@ -228,7 +233,10 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(SampleArgs a) {
     }
   }
   b = block_best(b, best_scratch);
-  if (threadIdx.x == 0) a.out[row] = b.index;
+  if (threadIdx.x == 0) {
+    a.out[row] = b.index;
+    if (a.slot_tokens) a.slot_tokens[a.slots[row]] = b.index;
+  }
 }
 
 // logits[row, id] = logit > 0 ? logit / penalty : logit * penalty for every listed id (>= 0);
@@ -255,11 +263,13 @@ __global__ void repetition_penalty_kernel(float* logits, long long row_stride, i
 TS_EXPORT int ts_sample(const float* logits, long long row_stride, int num_rows, int vocab,
                         const float* temperature, const int* top_k, const float* top_p,
                         const unsigned long long* stream_ids, const unsigned int* steps,
-                        unsigned long long seed, int* out, cudaStream_t stream) {
+                        unsigned long long seed, int* out, int* slot_tokens, const int* slots,
+                        cudaStream_t stream) {
   TS_REQUIRE(num_rows > 0 && vocab > 0, "sample: empty input");
   TS_REQUIRE(row_stride >= vocab, "sample: row stride smaller than the vocabulary");
   TS_REQUIRE(temperature && stream_ids && steps && out, "sample: missing argument");
-  SampleArgs a{logits, row_stride, vocab, temperature, top_k, top_p, stream_ids, steps, seed, out};
+  TS_REQUIRE((slot_tokens == nullptr) == (slots == nullptr), "sample: slot_tokens and slots come together");
+  SampleArgs a{logits, row_stride, vocab, temperature, top_k, top_p, stream_ids, steps, seed, out, slot_tokens, slots};
   TS_LAUNCH("sample", sample_kernel, num_rows, THREADS, 0, stream, a);
   return 0;
 }

@@ -48,6 +48,7 @@ class StepContext:
         self.host: dict = {}
         self.dtype = None
         self.workspace = None
+        self.slot_tokens = None      # int32 [slots + 1]: last sampled token of every state slot
 
     def cache(self, index: int):
         return self.device_cache.entries[index]

@@ -4,8 +4,12 @@ The surface is tinyserve's ``Engine`` (serve.py:2381-2712): ``add_request``, ``s
 ``abort``, ``has_work`` and ``generate``, which adds every prompt and steps until all are
 done, returning ``Output`` objects in request order (serve.py:2703-2712).  A step here is
 schedule -> run the batch -> sample -> read the tokens back -> finish or go on; tinyserve
-runs the host one step ahead of the device (serve.py:2509-2601), which this loop does not.
-A prompt is a string (needs the tokenizer files in the model folder) or a list of ids."""
+runs the host one step ahead of the device (serve.py:2509-2601); so does this engine with
+``async_scheduling`` (the default): while step n runs, the tokens of step n-1 are read back and
+checked, and step n+1 is scheduled and packed with placeholders for the tokens that the device
+still holds (the sampler leaves each request's token at its state slot, and the embedding lookup
+reads it from there).  A prompt is a string (needs the tokenizer files in the model folder) or a
+list of ids."""
 from __future__ import annotations
 
 import json
@@ -20,7 +24,7 @@ import torch
 from ..config.engine_config import EngineConfig
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
-from .runner import ModelRunner
+from .runner import PENDING, ModelRunner
 from .scheduler import Request, Scheduler
 from .text import Detokenizer, apply_stop_strings, load_tokenizer
 
@@ -58,7 +62,7 @@ def _stop_ids(model_dir, tokenizer) -> set:
 
 class LLM:
     def __init__(self, model: str = "", *, model_config=None, random_weights: bool = False,
-                 verbose: bool = False, **engine_options):
+                 verbose: bool = False, async_scheduling: bool = True, **engine_options):
         """``model``: a folder with config.json and safetensors.  ``engine_options`` are the
         fields of ``EngineConfig`` (dtype, max_model_len, block_size, max_num_seqs,
         max_num_batched_tokens, gpu_memory_utilization, num_blocks, use_cuda_graphs, seed).
@@ -81,6 +85,12 @@ class LLM:
         self.num_generated_tokens = 0
         self.num_steps = 0
         self._tokens_host = torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory()
+        self.async_scheduling = async_scheduling
+        self._token_bufs = [torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._flip = 0
+        self._next = None          # (batch, wants, prepared step) scheduled and packed, not launched
+        self._in_flight = None     # (live rows, host buffer, event, logits) sampled, not read back
+        self._spare_slot = self.cfg.max_num_seqs
         if verbose:
             print(f"[tinyserve_b200] engine ready in {time.time() - t0:.1f}s", flush=True)
 
@@ -116,13 +126,107 @@ class LLM:
         if req is not None and not req.finished:
             self.scheduler.finish(req, "abort")
             self.detok.pop(request_id, None)
+        # a packed step, or tokens on their way, that only concern ended requests are dropped
+        if self._next is not None and all(s.req.finished for s in self._next[0]):
+            self._next = None
+        if self._in_flight is not None and all(r.request_id not in self.requests for _, r, _ in self._in_flight[0]):
+            self._in_flight = None
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._next is not None or self._in_flight is not None
 
     # ------------------------------------------------------------------ one step
-    @torch.inference_mode()
     def step(self) -> list:
+        """One engine step; returns the outputs of the requests that got a token."""
+        return self._step_async() if self.async_scheduling else self._step_sync()
+
+    # ------------------------------------------------------------------ the host runs one step ahead
+    def _entries(self, batch):
+        entries, wants = [], []
+        for s in batch:
+            req = s.req
+            tokens = req.token_ids[s.num_computed:s.num_computed + s.num_new]
+            want = s.completes_prompt
+            if not want:
+                req.was_chunked_prefill = True
+            if s.num_computed < req.prompt_len:
+                self.num_prompt_tokens_run += min(s.num_new, req.prompt_len - s.num_computed)
+            entries.append(StepEntry(req.request_id, tokens, [s.num_new - 1] if want else []))
+            wants.append(want)
+        return entries, wants
+
+    @torch.inference_mode()
+    def _step_async(self) -> list:
+        """The four stages of serve.py:2509-2601: launch the step packed last call; finish the
+        step before it (its tokens have arrived or are waited for); sample this step's logits and
+        give its requests placeholders; schedule and pack the next step while the device works."""
+        cur, self._next = self._next, None
+        logits = None
+        if cur is not None:
+            logits = self.runner.launch(cur[2])
+            self.num_steps += 1
+        outputs = []
+        if self._in_flight is not None:
+            outputs = self._finish_async(*self._in_flight)
+            self._in_flight = None
+        outputs += [self._output(r) for r in self._take_dropped()]
+        if cur is not None and logits is not None:
+            batch, wants, prep = cur
+            rows = [s.req for s, w in zip(batch, wants) if w]          # one per row of logits
+            n = len(rows)
+            if n == len(batch):
+                slots = self.runner.state_slots_on_device(n)
+            else:
+                slots = torch.tensor([self.runner.manager.slot(r.request_id)
+                                      if self.runner.manager.is_live(r.request_id) else self._spare_slot
+                                      for r in rows], dtype=torch.int32, device=self.runner.device)
+            raw = logits.clone() if any(r.params.return_logprobs for r in rows) else None
+            tokens_dev = self.sampler(logits, rows, slot_tokens=self.runner.slot_tokens, slots=slots)
+            host = self._token_bufs[self._flip]
+            self._flip ^= 1
+            host[:n].copy_(tokens_dev, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record()
+            live = []
+            for i, req in enumerate(rows):
+                if req.finished:
+                    continue           # ended (stop, abort) while this step was already packed
+                forced = req.params.forced_token_ids
+                req.token_ids.append(int(forced[len(req.output_ids)]) if forced is not None else PENDING)
+                self.num_generated_tokens += 1
+                if len(req.output_ids) >= req.params.max_tokens or req.num_tokens >= self.cfg.max_model_len:
+                    self.scheduler.finish(req, "length")
+                live.append((i, req, len(req.token_ids) - 1))
+            self._in_flight = (live, host, event, raw)
+        batch = self.scheduler.schedule()
+        if batch:
+            entries, wants = self._entries(batch)
+            self._next = (batch, wants, self.runner.prepare(entries))
+        return outputs
+
+    def _finish_async(self, live, host, event, raw) -> list:
+        event.synchronize()
+        tokens = host.tolist()
+        outputs = []
+        for i, req, at in live:
+            if req.request_id not in self.requests:
+                continue               # aborted meanwhile
+            if req.token_ids[at] == PENDING:
+                req.token_ids[at] = tokens[i]
+            tok = req.token_ids[at]
+            if req.params.return_logprobs:
+                req.logprobs.append(raw[i].log_softmax(-1).cpu())
+            if tok in self.stop_ids and not req.params.ignore_eos:
+                if req.finished:
+                    req.finish_reason = "stop"
+                else:
+                    self.scheduler.finish(req, "stop")
+            outputs.append(self._output(req))
+        return outputs
+
+    # ------------------------------------------------------------------ one step at a time
+    @torch.inference_mode()
+    def _step_sync(self) -> list:
         batch = self.scheduler.schedule()
         outputs = [self._output(r) for r in self._take_dropped()]
         if not batch:

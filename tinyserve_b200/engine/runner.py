@@ -29,6 +29,16 @@ from .build import build_model
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
 
+PENDING = -1     # a token id that is still on the device (see ModelRunner.slot_tokens)
+
+
+class Prepared:
+    """A packed step that waits for its launch."""
+
+    def __init__(self, entries, ctx, graph, buf):
+        self.entries, self.ctx, self.graph, self.buf = entries, ctx, graph, buf
+
+
 class _Runtime:
     def __init__(self, device, max_positions, dtype):
         self.device, self.max_positions, self.dtype = device, max_positions, dtype
@@ -107,18 +117,22 @@ class ModelRunner:
         for name, n in sizes:
             self._offsets[name] = (total, n)
             total += (n + 3) // 4 * 4
-        self._host = torch.zeros(total, dtype=torch.int32).pin_memory() \
-            if self.device.type == "cuda" else torch.zeros(total, dtype=torch.int32)
-        self._host_np = self._host.numpy()
+        # two staging buffers: a step is packed while the copy of the one before may be pending
+        self._hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() if self.device.type == "cuda"
+                       else torch.zeros(total, dtype=torch.int32) for _ in range(2)]
+        self._hosts_np = [h.numpy() for h in self._hosts]
+        self._next_buf = 0
         self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        # last sampled token of every state slot (one spare entry for rows nobody waits for)
+        self.slot_tokens = torch.zeros(S + 1, dtype=torch.int32, device=self.device)
 
     def _seg(self, buf, name, n=None):
         off, cap = self._offsets[name]
         return buf[off:off + (cap if n is None else n)]
 
     # ------------------------------------------------------------------ packing
-    def _pack(self, entries, pad_requests=0, pad_tokens=0):
-        """Fill the host staging buffer; returns a StepContext without device work."""
+    def _pack(self, entries, buf=0, pad_requests=0, pad_tokens=0):
+        """Fill host staging buffer ``buf``; returns a StepContext without device work."""
         cfg, mgr, ps = self.cfg, self.manager, self.page_size
         B = len(entries)
         T = sum(len(e.tokens) for e in entries)
@@ -129,7 +143,7 @@ class ModelRunner:
             raise ValueError(f"{Tp} tokens in one step, max_num_batched_tokens is {cfg.max_num_batched_tokens}")
         if Bp > cfg.max_num_seqs:
             raise ValueError(f"{Bp} requests in one step, max_num_seqs is {cfg.max_num_seqs}")
-        h = self._host_np
+        h = self._hosts_np[buf]
         seg = lambda name, n=None: self._seg(h, name, n)
         ids, pos, rows = seg("token_ids"), seg("positions"), seg("logit_rows")
         cu_q, kv_lens, slots, fresh = seg("cu_q"), seg("kv_lens"), seg("state_slots"), seg("fresh")
@@ -148,15 +162,29 @@ class ModelRunner:
                 raise ValueError(f"request {e.rid!r} would hold {start + n} tokens, max_model_len is {cfg.max_model_len}")
             if any(mgr.pages_needed(e.rid, n)) and not mgr.allocate(e.rid, n):
                 raise CacheError(f"no cache pages left for request {e.rid!r}")
-            ids[t:t + n] = e.tokens
-            pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
-            for g in range(G):
-                pages = mgr.block_table(e.rid, g)
-                row = tables[g][b]
-                row[:len(pages)] = pages
-                row[len(pages):] = 0
-                p = np.arange(start, start + n)
-                slot_maps[g][t:t + n] = np.asarray(pages, dtype=np.int64)[p // ps] * ps + p % ps
+            if n == 1:
+                # a decoded token: scalars, no temporaries
+                tok = e.tokens[0]
+                ids[t] = tok if tok >= 0 else -1 - mgr.slot(e.rid)     # pending: read on the device
+                pos[t] = start
+                for g in range(G):
+                    pages = mgr.block_table(e.rid, g)
+                    row = tables[g][b]
+                    row[:len(pages)] = pages
+                    row[len(pages):] = 0
+                    slot_maps[g][t] = pages[start // ps] * ps + start % ps
+            else:
+                if min(e.tokens) < 0:
+                    raise ValueError(f"request {e.rid!r}: only a single decoded token may be pending")
+                ids[t:t + n] = e.tokens
+                pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+                for g in range(G):
+                    pages = mgr.block_table(e.rid, g)
+                    row = tables[g][b]
+                    row[:len(pages)] = pages
+                    row[len(pages):] = 0
+                    p = np.arange(start, start + n)
+                    slot_maps[g][t:t + n] = np.asarray(pages, dtype=np.int64)[p // ps] * ps + p % ps
             for j in e.want:
                 if not 0 <= j < n:
                     raise ValueError(f"request {e.rid!r} wants place {j} of {n} tokens")
@@ -208,27 +236,51 @@ class ModelRunner:
                                         self._seg(d, f"slot_mapping{g}", T), table[:B]))
         ctx.device_cache = self.device_cache
         ctx.dtype = self.dtype
+        ctx.slot_tokens = self.slot_tokens
         return ctx
 
-    def _upload(self):
-        self._dev.copy_(self._host, non_blocking=True)
+    def _upload(self, buf=0):
+        self._dev.copy_(self._hosts[buf], non_blocking=True)
 
     # ------------------------------------------------------------------ stepping
+    def prepare(self, entries) -> Prepared:
+        """Pack a step on the host (no device work).  A token id of PENDING stands for the
+        request's last sampled token, which the device still holds."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        graph = self._graph_for(entries)
+        buf, self._next_buf = self._next_buf, self._next_buf ^ 1
+        if graph is not None:
+            size = graph[2]
+            ctx = self._pack(entries, buf, pad_requests=size, pad_tokens=size)
+            self._seg(self._hosts_np[buf], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
+        else:
+            ctx = self._pack(entries, buf)
+        return Prepared(entries, ctx, graph, buf)
+
     @torch.inference_mode()
+    def launch(self, prep: Prepared):
+        """Upload and run a prepared step; its tokens are computed afterwards."""
+        self._upload(prep.buf)
+        if prep.graph is not None:
+            graph, out, size, launches = prep.graph
+            graph.replay()
+            ops.count_launches(launches)
+            logits = out[:len(prep.entries)]
+        else:
+            logits = self.model.forward(self._bind_device_views(prep.ctx))
+        for e in prep.entries:
+            if self.manager.is_live(e.rid):      # a request may have ended since it was packed
+                self.manager.commit(e.rid, len(e.tokens))
+        return logits
+
     def step(self, entries):
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the
         device (None if nothing is wanted).  The entries' tokens are computed afterwards."""
-        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
-        graph = self._graph_for(entries)
-        if graph is not None:
-            logits = self._replay(graph, entries)
-        else:
-            ctx = self._bind_device_views(self._pack(entries))
-            self._upload()
-            logits = self.model.forward(ctx)
-        for e in entries:
-            self.manager.commit(e.rid, len(e.tokens))
-        return logits
+        return self.launch(self.prepare(entries))
+
+    def state_slots_on_device(self, n):
+        """int32 [n] view of the state slots of the step that was launched last."""
+        return self._seg(self._dev, "state_slots", n)
 
     # ------------------------------------------------------------------ decode graphs
     def decode_buckets(self):
@@ -259,10 +311,10 @@ class ModelRunner:
         try:
             for size in sizes:
                 entries = [StepEntry(dummy, [0], [0])]
-                ctx = self._pack(entries, pad_requests=size, pad_tokens=size)
+                ctx = self._pack(entries, 0, pad_requests=size, pad_tokens=size)
                 # captured shape: `size` requests of one token, all rows wanted
                 ctx.num_logit_rows = size
-                self._seg(self._host_np, "logit_rows")[:size] = np.arange(size, dtype=np.int32)
+                self._seg(self._hosts_np[0], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
                 ctx.max_kv_len = self.cfg.max_model_len
                 self._bind_device_views(ctx)
                 self._upload()
@@ -283,12 +335,3 @@ class ModelRunner:
         self._graph_sizes = sorted(self.graphs)
         return len(self.graphs)
 
-    def _replay(self, graph_entry, entries):
-        graph, out, size, launches = graph_entry
-        ctx = self._pack(entries, pad_requests=size, pad_tokens=size)
-        rows = self._seg(self._host_np, "logit_rows")
-        rows[:size] = np.arange(size, dtype=np.int32)
-        self._upload()
-        graph.replay()
-        ops.count_launches(launches)
-        return out[:len(entries)]

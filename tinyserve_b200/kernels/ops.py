@@ -248,14 +248,15 @@ def units_for(head_dims) -> list:
 
 
 # ----------------------------------------------------------------------------- ops
-def embed_lookup(table, ids):
-    """float32 [T, n] = table[ids]; ids int32."""
-    _cuda(table, ids)
+def embed_lookup(table, ids, slot_tokens=None):
+    """float32 [T, n] = table[ids]; ids int32.  An id < 0 names a state slot (-1 - slot) whose
+    last sampled token is read from ``slot_tokens`` on the device."""
+    _cuda(table, ids, slot_tokens)
     T, n = ids.shape[0], table.shape[1]
     out = torch.empty(T, n, dtype=torch.float32, device=table.device)
     lib = _elementwise()
     _check(lib, lib.ts_embed_lookup(c_int(_dt(table)), _ptr(table), _ptr(ids), _ptr(out), c_int(T),
-                                    c_int(n), c_int(table.shape[0]), _stream()))
+                                    c_int(n), c_int(table.shape[0]), _ptr(slot_tokens), _stream()))
     return out
 
 
@@ -457,10 +458,13 @@ def linear(x, weight, bias=None, out_float32=False, allow_partials=False):
     return out
 
 
-def sample(logits, temperature, stream_ids, steps, seed, top_k=None, top_p=None):
+def sample(logits, temperature, stream_ids, steps, seed, top_k=None, top_p=None, slot_tokens=None,
+           slots=None):
     """One token per row of float32 logits.  temperature float32 [B] (0 = argmax); stream_ids
-    int64 [B] and steps int32 [B] select the noise; top_k int32 [B], top_p float32 [B] optional."""
-    _cuda(logits, temperature, stream_ids, steps, top_k, top_p)
+    int64 [B] and steps int32 [B] select the noise; top_k int32 [B], top_p float32 [B] optional.
+    With ``slot_tokens`` (int32 [slots]) and ``slots`` (int32 [B]) row i's token is also stored
+    at slot_tokens[slots[i]], for the next step's embedding lookup."""
+    _cuda(logits, temperature, stream_ids, steps, top_k, top_p, slot_tokens, slots)
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise TypeError("sample: logits must be float32 rows")
     B, V = logits.shape
@@ -468,7 +472,8 @@ def sample(logits, temperature, stream_ids, steps, seed, top_k=None, top_p=None)
     lib = _sampler()
     _check(lib, lib.ts_sample(_ptr(logits), c_longlong(logits.stride(0)), c_int(B), c_int(V),
                               _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(stream_ids),
-                              _ptr(steps), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(out), _stream()))
+                              _ptr(steps), c_ulonglong(seed & (2 ** 64 - 1)), _ptr(out),
+                              _ptr(slot_tokens), _ptr(slots), _stream()))
     return out
 
 

@@ -133,7 +133,7 @@ class DecoderModel(Part):
     # ------------------------------------------------------------------ forward
     def forward(self, ctx):
         """Run this step's tokens; returns 32-bit logits [len(ctx.logit_rows), vocab]."""
-        residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids)
+        residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids, ctx.slot_tokens)
         x = None
         for call in self.calls:
             x = self.blocks[call.layer].forward(x, residual, ctx, call)

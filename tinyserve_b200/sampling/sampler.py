@@ -32,11 +32,27 @@ class Sampler:
     def __init__(self, seed: int, device):
         self.seed = int(seed)
         self.device = device
+        self._zeros: dict = {}
 
-    def __call__(self, logits, requests):
+    def _greedy_args(self, n):
+        """Device tensors for an all-greedy batch (temperature 0 ignores the noise arguments)."""
+        if n not in self._zeros:
+            self._zeros[n] = (torch.zeros(n, dtype=torch.float32, device=self.device),
+                              torch.zeros(n, dtype=torch.int64, device=self.device),
+                              torch.zeros(n, dtype=torch.int32, device=self.device))
+        return self._zeros[n]
+
+    def __call__(self, logits, requests, slot_tokens=None, slots=None):
         """logits float32 [B, V] (modified in place by the penalty); ``requests``: objects with
-        request_id, params, token_ids, prompt_len.  Returns int32 [B] on the device."""
+        request_id, params, token_ids, prompt_len.  Returns int32 [B] on the device.  With
+        ``slot_tokens`` and ``slots`` (int32 [B], device) every token is also left at its request's
+        state slot for the next step."""
         B = logits.shape[0]
+        feedback = dict(slot_tokens=slot_tokens, slots=slots)
+        if all(r.params.temperature == 0 and (r.params.repetition_penalty == 1.0 or r.params.repeat_last_n == 0)
+               for r in requests):
+            temps, streams, steps = self._greedy_args(B)
+            return ops.sample(logits, temps, streams, steps, self.seed, **feedback)
         temps, ks, ps, streams, steps = [], [], [], [], []
         pen_rows, pen_ids, pen_vals = [], [], []
         for i, r in enumerate(requests):
@@ -68,4 +84,4 @@ class Sampler:
             torch.tensor(steps, dtype=torch.int32, device=dev),
             self.seed,
             top_k=torch.tensor(ks, dtype=torch.int32, device=dev) if need_k else None,
-            top_p=torch.tensor(ps, dtype=torch.float32, device=dev) if need_p else None)
+            top_p=torch.tensor(ps, dtype=torch.float32, device=dev) if need_p else None, **feedback)
