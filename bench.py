@@ -5,7 +5,8 @@
 
 A step is one decode step of the whole batch.  Prints ONE JSON line:
   value     decoded tokens per second over K steps, timed on the device with CUDA events;
-            each step uploads the batch, runs the model and samples greedily on the device
+            each step uploads the batch, runs the model and samples greedily on the device;
+            tokens are fed back on the device and the host packs one step ahead
   e2e       the same through the Python entry point (LLM.add_request / LLM.step): host
             token ids in, sampled tokens out, scheduler and cache manager included
   prefill   one 2,048-token prompt in one step
@@ -121,15 +122,28 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None):
         logits = runner.step([StepEntry(r, p, [PROMPT_LEN - 1]) for r, p in zip(group, prompts)])
         last += logits.argmax(-1).tolist()
 
-    def one_step(tokens):
-        logits = runner.step([StepEntry(r, [t], [0]) for r, t in zip(rids, tokens)])
-        out = ops.sample(logits, temps, streams, counters, 0)
+    # Tokens stay on the device: the sampler leaves each request's token at its state slot and the
+    # next step's embedding lookup reads it there.  The host packs step n+1 while step n runs and
+    # never lags more than one step (it waits for the event of step n-1 before it reuses a buffer).
+    from tinyserve_b200.engine.runner import PENDING
+    slots = torch.tensor([runner.manager.slot(r) for r in rids], dtype=torch.int64, device=runner.device)
+    runner.slot_tokens[slots] = torch.tensor(last, dtype=torch.int32, device=runner.device)
+    entries = [StepEntry(r, [PENDING], [0]) for r in rids]
+    events = []
+
+    def one_step():
+        if len(events) >= 2:
+            events[-2].synchronize()
+        logits = runner.step(entries)
+        out = ops.sample(logits, temps, streams, counters, 0, slot_tokens=runner.slot_tokens,
+                         slots=runner.state_slots_on_device(batch))
         host.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return host.tolist()
+        ev = torch.cuda.Event()
+        ev.record()
+        events.append(ev)
 
     for _ in range(warmup):
-        last = one_step(last)
+        one_step()
     torch.cuda.synchronize()
     if clock:
         clock.start()
@@ -137,7 +151,7 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None):
     launches0 = ops.launch_count()
     start.record()
     for _ in range(steps):
-        last = one_step(last)
+        one_step()
     end.record()
     torch.cuda.synchronize()
     clocks = clock.stop() if clock else None
