@@ -56,7 +56,7 @@ def causal_attention(q, k, v, scale, window=0):
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("thd,shd->hts", q, k) * scale
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window > 0:
         visible &= pos[None, :] > pos[:, None] - window
@@ -141,9 +141,10 @@ def load_folder(model_dir, dtype=torch.float64):
 
 def hidden_states(cfg, w, token_ids, dtype=torch.float64):
     """serve.py:1253-1258: embed, the layers, last residual add + final norm. Returns [T, h]."""
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
+    device = w["model.embed_tokens.weight"].device       # CPU in most tests; a GPU for large shapes
+    ids = torch.as_tensor(token_ids, dtype=torch.long).to(device)
     T = ids.shape[0]
-    cos, sin = rope_tables(cfg["head_dim"], cfg["rope_theta"], T, dtype)
+    cos, sin = (t.to(device) for t in rope_tables(cfg["head_dim"], cfg["rope_theta"], T, dtype))
     r = w["model.embed_tokens.weight"][ids]                       # serve.py:1239
     for i in range(cfg["num_hidden_layers"]):
         r = decoder_layer(r, w, i, cfg, cos, sin, layer_window(cfg, i))

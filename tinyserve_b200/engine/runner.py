@@ -121,6 +121,7 @@ class ModelRunner:
         self._hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() if self.device.type == "cuda"
                        else torch.zeros(total, dtype=torch.int32) for _ in range(2)]
         self._hosts_np = [h.numpy() for h in self._hosts]
+        self._copied = [None, None]      # event after the last copy out of each staging buffer
         self._next_buf = 0
         self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
         # last sampled token of every state slot (one spare entry for rows nobody waits for)
@@ -249,6 +250,10 @@ class ModelRunner:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         graph = self._graph_for(entries)
         buf, self._next_buf = self._next_buf, self._next_buf ^ 1
+        if self._copied[buf] is not None:
+            # the host may run several steps ahead of the device (nobody has to read a result
+            # between steps): this buffer's last copy must have left it before it is packed again
+            self._copied[buf].synchronize()
         if graph is not None:
             size = graph[2]
             ctx = self._pack(entries, buf, pad_requests=size, pad_tokens=size)
@@ -261,6 +266,10 @@ class ModelRunner:
     def launch(self, prep: Prepared):
         """Upload and run a prepared step; its tokens are computed afterwards."""
         self._upload(prep.buf)
+        if self.device.type == "cuda":
+            if self._copied[prep.buf] is None:
+                self._copied[prep.buf] = torch.cuda.Event()
+            self._copied[prep.buf].record()
         if prep.graph is not None:
             graph, out, size, launches = prep.graph
             graph.replay()
