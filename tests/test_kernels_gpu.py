@@ -217,9 +217,9 @@ def _run_attention(q, kc, vc, table, q_lens, kv_lens, page, scale, window, split
     return ops().paged_attention(q, kc, vc, view, ctx, scale, window, num_splits=splits)
 
 
-@pytest.fixture(params=["mma", "simt"])
+@pytest.fixture(params=["tcgen05", "mma", "simt"])
 def bf16_attention(request):
-    """Both bfloat16 attention back ends: tensor cores and the 32-bit FMA kernel."""
+    """The bfloat16 attention back ends: tcgen05 prefill (+ mma.sync decode), mma.sync, 32-bit FMA."""
     o = ops()
     old, o.BF16_ATTENTION = o.BF16_ATTENTION, request.param
     yield request.param
@@ -228,11 +228,14 @@ def bf16_attention(request):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(6, 2, 48, 8), (4, 4, 16, 16), (8, 1, 64, 4), (40, 1, 32, 16),
-                                           (5, 5, 80, 32), (16, 2, 128, 16), (80, 1, 16, 8), (4, 2, 256, 16)])
+                                           (5, 5, 80, 32), (16, 2, 128, 16), (80, 1, 16, 8), (4, 2, 256, 16),
+                                           (32, 8, 128, 16), (6, 2, 64, 8), (3, 1, 128, 128), (200, 1, 64, 16)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 3), (23, 1), (23, 4)])
 def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention):
-    if dtype == torch.float32 and bf16_attention == "simt":
+    if dtype == torch.float32 and bf16_attention != "mma":
         pytest.skip("float32 has one back end")
+    if bf16_attention == "tcgen05" and (D not in (64, 128) or page < 8 or splits > 1):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128, pages of 8 and more, no splits")
     # a whole prompt, a decode token, a portion after a prefix, two tokens, a long decode
     kv_lens, q_lens = [70, 133, 97, 2, 300], [70, 1, 29, 2, 1]
     k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
@@ -241,6 +244,8 @@ def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf1
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=1)
     out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
     close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "attention")
+    if bf16_attention == "tcgen05" and dtype == torch.bfloat16:
+        assert ops().attention_tcgen05_error(D) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -249,8 +254,8 @@ def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf1
 @pytest.mark.parametrize("merge", ["launch", "kernel"])
 def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention, merge, monkeypatch):
     """Every request brings one token: the decode kernels."""
-    if dtype == torch.float32 and bf16_attention == "simt":
-        pytest.skip("float32 has one back end")
+    if (dtype == torch.float32 and bf16_attention != "mma") or bf16_attention == "tcgen05":
+        pytest.skip("float32 has one back end; decode has no tcgen05 kernel")
     if merge == "kernel" and (dtype == torch.float32 or bf16_attention == "simt" or splits == 1):
         pytest.skip("only the tensor-core decode kernel merges its key ranges itself")
     monkeypatch.setattr(ops(), "DECODE_MERGE", merge)
@@ -267,6 +272,8 @@ def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("splits", [1, 5])
 def test_attention_finds_one_far_key(dtype, splits, bf16_attention):
+    if bf16_attention == "tcgen05":
+        pytest.skip("decode has no tcgen05 kernel")
     """Among 700 keys one, on a page of its own early in the sequence, matches the query: the
     output must be that key's value."""
     H, Hkv, D, page, n, far = 4, 2, 32, 16, 700, 37

@@ -17,9 +17,7 @@
 // Every mbarrier wait is bounded: if a wait runs out, the block raises the library's error flag
 // (ts_gemm_tcgen05_error), lets its copies land, frees its tensor memory and returns.
 // tinyserve leaves these products to cuBLAS (serve.py:847, 883, 916, 919, 1263).
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 TS_DEFINE_LAST_ERROR()
 
@@ -30,9 +28,6 @@ constexpr int TILE_N = 128;          // weight rows of a block (MMA M)
 constexpr int BK = 64;               // K elements of a stage: 128 bytes, one swizzle row
 constexpr int THREADS = 128;
 constexpr int W_STAGE_BYTES = TILE_N * BK * 2;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-
-__device__ int g_error_flag = 0;
 
 struct GemmParams {
   void* out;            // [M, ldc] bfloat16 or float
@@ -42,78 +37,11 @@ struct GemmParams {
   int splits, out_f32;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}\n"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// false if the wait ran out (or another thread of the block already gave up)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-  }
-  *abort_flag = 1;
-  atomicExch(&g_error_flag, 1);
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-
-// shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte swizzle;
-// groups of 8 rows are 1024 bytes apart
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);     // start address, 16-byte units
-  d |= static_cast<uint64_t>(1) << 16;                   // leading byte offset (unused with swizzle)
-  d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride byte offset
-  d |= static_cast<uint64_t>(1) << 46;                   // descriptor version of sm_100
-  d |= static_cast<uint64_t>(2) << 61;                   // 128-byte swizzle
-  return d;
-}
 // instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = tile_t
 __host__ __device__ constexpr uint32_t instr_desc(int tile_t) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(tile_t >> 3) << 17) |
          (static_cast<uint32_t>(TILE_N >> 4) << 24);
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tmem_load8(uint32_t addr, float (&v)[8]) {
-  uint32_t r[8];
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(addr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-
 // Consecutive MMAs into one accumulator depend on each other, and an MMA of 16 tokens is all
 // latency; the four K steps of a stage therefore go to ACCS independent accumulators, which the
 // epilogue adds up.
@@ -393,10 +321,6 @@ struct UnitIter {
   }
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-
 template <int TILE_T>
 __global__ void __launch_bounds__(P_THREADS)
 gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -600,22 +524,6 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 }
 
 // ---------------------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
-  return fn;
-}
-
 // rows x K bfloat16 matrix with leading dimension ld; boxes of box_rows x 64 elements
 bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
   EncodeTiledFn fn = encode_tiled();

@@ -1,7 +1,7 @@
 """Compile the CUDA sources for sm_100a with nvcc, on first use, into shared libraries.
 
 Each source (plus its -D definitions) is one *unit*; its library is named after a hash of
-the source text, of ``common.cuh`` and of the flags, so that a changed source is rebuilt
+the source text, of the headers beside it and of the flags, so that a changed source is rebuilt
 and an unchanged one is loaded as it is.  Libraries go to ``kernels/_build`` inside the
 package, or to a per-user folder under the temporary directory when the package is
 read-only.  Only what is asked for is compiled: a model compiles the attention unit of
@@ -66,7 +66,8 @@ def build_dir() -> str:
 def unit_path(source: str, defines: dict) -> tuple:
     src = os.path.join(CSRC, source)
     h = hashlib.sha1()
-    for path in (src, os.path.join(CSRC, "common.cuh")):
+    headers = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
+    for path in [src] + [os.path.join(CSRC, f) for f in headers]:
         with open(path, "rb") as fh:
             h.update(fh.read())
     flags = [f"-D{k}={v}" for k, v in sorted(defines.items())]

@@ -21,8 +21,10 @@ _launches = 0
 #: TCGEN05_MAX_TOKENS rows, cuBLAS above), "cublas" (torch.mm) or "simt" (the FMA kernel)
 BF16_GEMM = "tcgen05"
 TCGEN05_MAX_TOKENS = int(os.environ.get("TINYSERVE_TCGEN05_MAX_TOKENS", "16"))
-#: bfloat16 attention: "mma" (tensor cores, head sizes up to 256) or "simt" (32-bit FMA kernel)
-BF16_ATTENTION = "mma"
+#: bfloat16 attention: "tcgen05" (prefill of head sizes 64 and 128 on the tcgen05 kernel, the rest
+#: as "mma"), "mma" (mma.sync kernels, head sizes up to 256) or "simt" (32-bit FMA kernel)
+BF16_ATTENTION = os.environ.get("TINYSERVE_BF16_ATTENTION", "tcgen05")
+TCGEN05_HEAD_DIMS = (64, 128)
 MMA_MAX_HEAD_DIM = 256
 #: how the key ranges of split-KV decode are merged: "launch" (a second, tiny kernel) or "kernel"
 #: (inside the decode kernel, by the block that finishes last).  Measured on B200 from CUDA graphs,
@@ -234,6 +236,15 @@ def _attention_mma(head_dim: int):
     return build.load_unit("attention_mma.cu", defines)
 
 
+def _attention_tcgen05(head_dim: int):
+    return build.load_unit("attention_tcgen05.cu", {"TS_HEAD_DIM": head_dim})
+
+
+def attention_tcgen05_error(head_dim: int) -> int:
+    """1 if a block of the tcgen05 attention kernel ever gave up on a wait (synchronises)."""
+    return _attention_tcgen05(head_dim).ts_attention_tcgen05_error()
+
+
 def _sampler():
     return build.load_unit("sampler.cu")
 
@@ -244,6 +255,8 @@ def units_for(head_dims) -> list:
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
     units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
+    units += [("attention_tcgen05.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
+              if d in TCGEN05_HEAD_DIMS]
     return units
 
 
@@ -380,9 +393,20 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     _cuda(q, k_cache, v_cache)
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
-    mma = q.dtype == torch.bfloat16 and BF16_ATTENTION == "mma" and D <= MMA_MAX_HEAD_DIM \
+    mma = q.dtype == torch.bfloat16 and BF16_ATTENTION in ("mma", "tcgen05") and D <= MMA_MAX_HEAD_DIM \
         and D in SUPPORTED_HEAD_DIMS
     decode = mma and ctx.max_q_len == 1
+    page = view.page_size
+    if (mma and not decode and BF16_ATTENTION == "tcgen05" and D in TCGEN05_HEAD_DIMS
+            and 8 <= page <= 128 and page & (page - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
+        out = torch.empty_like(q)
+        lib = _attention_tcgen05(D)
+        _check(lib, lib.ts_paged_attention_tcgen05(
+            _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
+            _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
+            c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
+            c_int(window), _stream()))
+        return out
     if num_splits is None:
         if decode:
             num_splits = decode_splits(ctx.num_requests, ctx.max_kv_len, H, Hkv)
