@@ -167,7 +167,10 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
   T* op = static_cast<T*>(out);
   if (aligned && n <= 4 * 4 * 1024) {
     const int quads = n / 4;
-    const int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
+    // few rows (decode): one element group per thread, the shortest chain; many rows (prefill):
+    // smaller blocks with four groups per thread, more rows in flight per SM
+    int items = quads <= 1024 ? 1 : (quads <= 2048 ? 2 : 4);
+    if (num_out_rows >= 512 && quads >= 256) items = 4;
     int threads = ((quads + items - 1) / items + 31) / 32 * 32;
     if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
     else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
@@ -336,19 +339,13 @@ struct RopeArgs {
 };
 
 template <typename T>
-__global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+__device__ __forceinline__ void rope_one_head(int t, int head, int lane, const T* __restrict__ qkv, T* __restrict__ q_out,
                                             const int* __restrict__ positions, RopeArgs rope,
                                             VecParam qw, VecParam kw, int has_norm, float eps,
                                             int H, int Hkv, int D, T* __restrict__ k_cache,
                                             T* __restrict__ v_cache,
                                             const int* __restrict__ slot_mapping, int page_size,
                                             int heads_total, PartialSrc ps) {
-  pdl_trigger();
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (head >= heads_total) return;
-  const int t = blockIdx.x;
   const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
   const int n0 = head * D;
   auto in = [&](int i) { return ps.base ? ps.load1(t, n0 + i) : to_f32<T>(src[i]); };
@@ -400,6 +397,23 @@ __global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __rest
     dst[i] = from_f32<T>(a);
   }
 }
+// one warp per (token, head); with gridDim.y smaller than the number of head groups the warps
+// walk the heads, so that many tokens need few, fatter blocks
+template <typename T>
+__global__ void qk_norm_rope_kvwrite_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                            const int* __restrict__ positions, RopeArgs rope,
+                                            VecParam qw, VecParam kw, int has_norm, float eps,
+                                            int H, int Hkv, int D, T* __restrict__ k_cache,
+                                            T* __restrict__ v_cache,
+                                            const int* __restrict__ slot_mapping, int page_size,
+                                            int heads_total, PartialSrc ps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int head = blockIdx.y * warps + warp; head < heads_total; head += gridDim.y * warps)
+    rope_one_head<T>(blockIdx.x, head, lane, qkv, q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D,
+                     k_cache, v_cache, slot_mapping, page_size, heads_total, ps);
+}
 
 // Two neighbouring pairs per lane and step, for the pairing (j, j + D/2) over the whole head
 // with D / 2 even: 4- or 8-byte accesses, one cache line per warp and step.
@@ -418,19 +432,13 @@ template <> struct Duo<__nv_bfloat16> {
 };
 
 template <typename T, int STEPS>
-__global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+__device__ __forceinline__ void rope_one_head_vec(int t, int head, int lane, const T* __restrict__ qkv, T* __restrict__ q_out,
                                                 const int* __restrict__ positions, RopeArgs rope,
                                                 VecParam qw, VecParam kw, int has_norm, float eps,
                                                 int H, int Hkv, int D, T* __restrict__ k_cache,
                                                 T* __restrict__ v_cache,
                                                 const int* __restrict__ slot_mapping, int page_size,
                                                 int heads_total, PartialSrc ps) {
-  pdl_trigger();
-  pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y * (blockDim.x >> 5) + warp;
-  if (head >= heads_total) return;
-  const int t = blockIdx.x;
   const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
   T* dst;
   bool is_v = false;
@@ -488,6 +496,22 @@ __global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __
   }
 }
 
+template <typename T, int STEPS>
+__global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                                const int* __restrict__ positions, RopeArgs rope,
+                                                VecParam qw, VecParam kw, int has_norm, float eps,
+                                                int H, int Hkv, int D, T* __restrict__ k_cache,
+                                                T* __restrict__ v_cache,
+                                                const int* __restrict__ slot_mapping, int page_size,
+                                                int heads_total, PartialSrc ps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int head = blockIdx.y * warps + warp; head < heads_total; head += gridDim.y * warps)
+    rope_one_head_vec<T, STEPS>(blockIdx.x, head, lane, qkv, q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv,
+                                D, k_cache, v_cache, slot_mapping, page_size, heads_total, ps);
+}
+
 TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, const int* positions,
                                       const float* cos, const float* sin, int rotary_dim,
                                       int interleaved, const void* q_weight, const void* k_weight,
@@ -507,8 +531,9 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
   TS_REQUIRE(slot_mapping == nullptr || (k_cache && v_cache && page_size > 0),
              "qk_norm_rope_kvwrite: cache write without a cache");
   const int heads_total = slot_mapping ? H + 2 * Hkv : H;
-  const int warps = 4;
-  dim3 grid(num_tokens, (heads_total + warps - 1) / warps);
+  // few tokens: a warp per head (most blocks); many tokens: 8 warps walk a token's heads
+  const int warps = num_tokens >= 256 ? 8 : 4;
+  dim3 grid(num_tokens, num_tokens >= 256 ? 1 : (heads_total + warps - 1) / warps);
   RopeArgs rope{cos, sin, rotary_dim, interleaved};
   VecParam qw{q_weight, weight_is_f32}, kw{k_weight, weight_is_f32};
   const int has_norm = q_weight != nullptr;
