@@ -248,6 +248,29 @@ def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf1
         assert ops().attention_tcgen05_error(D) == 0
 
 
+@pytest.mark.parametrize("H,Hkv,D,page", [(16, 8, 128, 16), (6, 2, 64, 8), (10, 2, 48, 16)])
+@pytest.mark.parametrize("window", [0, 200])
+def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window, bf16_attention):
+    """A serving step in the middle of a run: many requests decode, two bring portions of their
+    prompts.  The one-token requests go to the decode kernel by a request list (long ones in
+    several key ranges), the portions to the prefill kernel by a work list of blocks."""
+    if bf16_attention == "tcgen05" and D not in (64, 128):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
+    dtype = torch.bfloat16
+    gen = torch.Generator().manual_seed(5)
+    q_lens = [1, 1, 150, 1, 1, 1, 37, 1, 1, 2, 1]
+    kv_lens = [int(torch.randint(1, 900, (1,), generator=gen)) + n for n in q_lens]
+    kv_lens[3], kv_lens[7] = 1, 1500         # a first token; a context long enough for key ranges
+    k = [rnd(n, Hkv, D, seed=40 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    v = [rnd(n, Hkv, D, seed=60 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
+    q = rnd(sum(q_lens), H, D, seed=31, dtype=dtype)
+    kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 5, seed=2)
+    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None)
+    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "attention")
+    if bf16_attention == "tcgen05":
+        assert ops().attention_tcgen05_error(D) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])

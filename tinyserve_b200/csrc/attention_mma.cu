@@ -48,6 +48,8 @@ struct MmaAttnParams {
   const int* block_table;   // [B, max_blocks]
   const int* cu_q;          // [B + 1]
   const int* kv_lens;       // [B]
+  const int* tile_req;      // optional work list: request and first query of every block
+  const int* tile_q0;
   float* part_o;            // [T, H, splits, D]
   float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
   int* counters;            // [requests * gridDim.x] zeros: the block that arrives last merges the key ranges
@@ -216,11 +218,12 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
 
   pdl_trigger();
   pdl_wait();
-  const int b = blockIdx.z;
+  // with a work list block x handles tile x; else blocks (tile, request) cover max_q_len and exit
+  // where a request has fewer queries (the last queries see the most keys: their blocks go first)
+  const int b = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.z;
   const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  // the last queries see the most keys: their blocks go first
-  const int q0 = (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;
+  const int q0 = p.tile_req ? p.tile_q0[blockIdx.x] : (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;
   if (q0 >= q_len) return;
   const int kv_len = p.kv_lens[b];
   const int G = p.H / p.Hkv, GT = p.heads_per_tile, QPT = p.queries_per_tile;
@@ -328,7 +331,8 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
 
   pdl_trigger();
   pdl_wait();
-  const int b = blockIdx.z, split = blockIdx.y;
+  // with a request list block z handles its entry z (the one-token requests of a mixed batch)
+  const int b = p.tile_req ? p.tile_req[blockIdx.z] : blockIdx.z, split = blockIdx.y;
   const int kvh = blockIdx.x / p.head_tiles, head_tile = blockIdx.x % p.head_tiles;
   const int q_begin = p.cu_q[b];
   if (p.cu_q[b + 1] - q_begin != 1) return;
@@ -429,10 +433,12 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
       num = fmaf(wgt, sm_o[(w * 16 + r) * D + d], num);
       den = fmaf(wgt, sm_ml[(w * 16 + r) * 2 + 1], den);
     }
-    const size_t row = (size_t)q_begin * p.H + kvh * G + g0 + r;
+    const int head = kvh * G + g0 + r;
     if (p.num_splits == 1) {
-      p.out[row * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      p.out[((size_t)q_begin * p.H + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     } else {
+      // partial rows go by token, or by the entry of the request list when there is one
+      const size_t row = (size_t)(p.tile_req ? (int)blockIdx.z : q_begin) * p.H + head;
       p.part_o[(row * p.num_splits + split) * D + d] = num;
       if (d == 0) {
         p.part_ml[(row * p.num_splits + split) * 2] = mx;
@@ -482,11 +488,14 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
 }
 
 // out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
+// (block x merges partial row x into output row x, or into head x % H of token tokens[x / H])
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         bf16* __restrict__ out, int num_splits, int H) {
+                                         bf16* __restrict__ out, int num_splits, int H,
+                                         const int* __restrict__ tokens) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
+  const size_t out_row = tokens ? (size_t)tokens[blockIdx.x / H] * H + blockIdx.x % H : row;
   const float* ml = part_ml + row * num_splits * 2;
   float mx = -INFINITY;
   for (int s = 0; s < num_splits; ++s) mx = fmaxf(mx, ml[2 * s]);
@@ -499,7 +508,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
       const float w = ml[2 * s] == -INFINITY ? 0.f : exp2f(ml[2 * s] - mx);
       v = fmaf(w, part_o[(row * num_splits + s) * D + d], v);
     }
-    out[row * D + d] = __float2bfloat16_rn(v * inv);
+    out[out_row * D + d] = __float2bfloat16_rn(v * inv);
   }
 }
 
@@ -509,6 +518,9 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 
 // decode_only != 0: every request brings one token (requests with another count are skipped);
 // num_splits > 1 needs scratch: part_o T*H*splits*D floats, part_ml T*H*splits*2 floats.
+// tile_req / tile_q0 (optional, num_tiles ints each): for the prefill kernel the request and the
+// first query of every block of tile_queries queries; with decode_only the one-token requests of
+// a mixed batch and their tokens (the scratch then has num_tiles rows in place of T).
 // counters: num_requests * Hkv * ceil(group / 16) zeroed ints (they return to zero); with them the
 // key ranges are merged inside the decode kernel, without them by a second launch.
 TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
@@ -516,7 +528,8 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                      int page_size, int max_blocks, float scale, int window,
                                      int num_splits, float* part_o, float* part_ml, int* counters,
-                                     int decode_only, cudaStream_t stream) {
+                                     int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
+                                     int tile_queries, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
@@ -527,6 +540,10 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.counters = counters;
+  p.tile_req = tile_req;
+  p.tile_q0 = tile_q0;
+  TS_REQUIRE((tile_req == nullptr) == (tile_q0 == nullptr) && (tile_req == nullptr || num_tiles > 0),
+             "paged_attention_mma: the work list is incomplete");
   p.H = H; p.Hkv = Hkv; p.max_blocks = max_blocks;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -543,11 +560,15 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
       if (e != cudaSuccess) return ts_fail("paged_attention_mma: %s", cudaGetErrorString(e));
       configured = true;
     }
-    dim3 grid(Hkv * p.head_tiles, num_splits, num_requests);
+    // tile_req / tile_q0 here: the one-token requests of a mixed batch and their tokens
+    TS_REQUIRE(tile_req == nullptr || counters == nullptr, "paged_attention_mma: a request list merges by its own launch");
+    const int count = tile_req ? num_tiles : num_requests;
+    dim3 grid(Hkv * p.head_tiles, num_splits, count);
     TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
     if (num_splits > 1 && counters == nullptr) {
-      TS_LAUNCH("attention_combine", attention_combine_kernel, num_tokens * H, D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,
-                (const float*)part_o, (const float*)part_ml, p.out, num_splits, H);
+      TS_LAUNCH("attention_combine", attention_combine_kernel, (tile_req ? count : num_tokens) * H,
+                D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,
+                (const float*)part_o, (const float*)part_ml, p.out, num_splits, H, tile_q0);
     }
     return 0;
   }
@@ -564,6 +585,10 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
     configured_prefill = true;
   }
   dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
+  TS_REQUIRE(p.tile_req == nullptr || tile_queries == p.queries_per_tile,
+             "paged_attention_mma: the work list was cut for %d queries a block, the kernel takes %d",
+             tile_queries, p.queries_per_tile);
+  if (p.tile_req) grid = dim3(num_tiles, (unsigned)gy, 1);
   TS_LAUNCH("attn_prefill", attn_prefill_kernel, grid, PRE_THREADS, smem, stream, p);
   return 0;
 }

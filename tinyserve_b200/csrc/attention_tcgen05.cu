@@ -45,6 +45,8 @@ struct TcAttnParams {
   const int* block_table;   // [B, max_blocks]
   const int* cu_q;          // [B + 1]
   const int* kv_lens;       // [B]
+  const int* tile_req;      // optional work list: request and first query of every block
+  const int* tile_q0;
   int H, Hkv, page_shift, page_size, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
   int window;
@@ -83,10 +85,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   pdl_trigger();
   pdl_wait();
-  const int b = blockIdx.z;
+  // with a work list block x handles tile x; else blocks (tile, request) cover max_q_len and exit
+  // where a request has fewer queries
+  const int b = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.z;
   const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  const int q0 = (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;     // heavy blocks first
+  const int q0 = p.tile_req ? p.tile_q0[blockIdx.x]
+                            : (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;     // heavy blocks first
   if (q0 >= q_len) return;
   const int kv_len = p.kv_lens[b];
   const int G = p.H / p.Hkv, GT = p.heads_per_tile, QPT = p.queries_per_tile;
@@ -319,12 +324,14 @@ TS_EXPORT int ts_attention_tcgen05_error() {
   return flag;
 }
 
-// q, out [T, H, D]; caches [num_pages, Hkv, page_size, D]; bfloat16.
+// q, out [T, H, D]; caches [num_pages, Hkv, page_size, D]; bfloat16.  tile_req / tile_q0 (optional,
+// num_tiles ints each): the request and the first query of every block of 128 / group queries.
 TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k_cache, const void* v_cache,
                                          const int* block_table, const int* cu_q, const int* kv_lens,
                                          int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                          int num_pages, int page_size, int max_blocks, float scale, int window,
-                                         cudaStream_t stream) {
+                                         const int* tile_req, const int* tile_q0, int num_tiles,
+                                         int tile_queries, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_tcgen05: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_tcgen05: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size >= 8 && page_size <= BN && (page_size & (page_size - 1)) == 0,
@@ -335,6 +342,7 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   const int G = H / Hkv;
   TcAttnParams p;
   p.out = (bf16*)out; p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens;
+  p.tile_req = tile_req; p.tile_q0 = tile_q0;
   p.H = H; p.Hkv = Hkv; p.page_size = page_size; p.max_blocks = max_blocks; p.window = window;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
@@ -365,7 +373,13 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
     if (e != cudaSuccess) return ts_fail("paged_attention_tcgen05: %s", cudaGetErrorString(e));
     configured = true;
   }
+  TS_REQUIRE((tile_req == nullptr) == (tile_q0 == nullptr) && (tile_req == nullptr || num_tiles > 0),
+             "paged_attention_tcgen05: the work list is incomplete");
+  TS_REQUIRE(tile_req == nullptr || tile_queries == p.queries_per_tile,
+             "paged_attention_tcgen05: the work list was cut for %d queries a block, the kernel takes %d",
+             tile_queries, p.queries_per_tile);
   dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
+  if (tile_req) grid = dim3(num_tiles, (unsigned)gy, 1);
   TS_LAUNCH("attn_prefill_tcgen05", attn_prefill_tc_kernel, grid, THREADS, SMEM, stream, mq, mk, mv, p);
   return 0;
 }

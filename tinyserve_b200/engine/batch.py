@@ -49,6 +49,7 @@ class StepContext:
         self.dtype = None
         self.workspace = None
         self.slot_tokens = None      # int32 [slots + 1]: last sampled token of every state slot
+        self.tile_cache: dict = {}   # attention work lists of this step, by queries per block
 
     def cache(self, index: int):
         return self.device_cache.entries[index]

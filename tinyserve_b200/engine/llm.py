@@ -87,6 +87,11 @@ class LLM:
         self._tokens_host = torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory()
         self.async_scheduling = async_scheduling
         self._token_bufs = [torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        # the slots of a step's wanted rows, when not every request of the step wants logits: staged
+        # in pinned memory like the tokens, and reused only after that step's tokens have arrived
+        self._slot_bufs = [torch.empty(self.cfg.max_num_seqs, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._slot_devs = [torch.empty(self.cfg.max_num_seqs, dtype=torch.int32, device=self.runner.device)
+                           for _ in range(2)]
         self._flip = 0
         self._next = None          # (batch, wants, prepared step) scheduled and packed, not launched
         self._in_flight = None     # (live rows, host buffer, event, logits) sampled, not read back
@@ -177,9 +182,12 @@ class LLM:
             if n == len(batch):
                 slots = self.runner.state_slots_on_device(n)
             else:
-                slots = torch.tensor([self.runner.manager.slot(r.request_id)
-                                      if self.runner.manager.is_live(r.request_id) else self._spare_slot
-                                      for r in rows], dtype=torch.int32, device=self.runner.device)
+                manager = self.runner.manager
+                staged = self._slot_bufs[self._flip]
+                staged[:n] = torch.tensor([manager.slot(r.request_id) if manager.is_live(r.request_id)
+                                           else self._spare_slot for r in rows], dtype=torch.int32)
+                slots = self._slot_devs[self._flip][:n]
+                slots.copy_(staged[:n], non_blocking=True)
             raw = logits.clone() if any(r.params.return_logprobs for r in rows) else None
             tokens_dev = self.sampler(logits, rows, slot_tokens=self.runner.slot_tokens, slots=slots)
             host = self._token_bufs[self._flip]

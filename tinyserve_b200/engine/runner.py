@@ -276,7 +276,8 @@ class ModelRunner:
             ops.count_launches(launches)
             logits = out[:len(prep.entries)]
         else:
-            logits = self.model.forward(self._bind_device_views(prep.ctx))
+            with ops.stream_scope():
+                logits = self.model.forward(self._bind_device_views(prep.ctx))
         for e in prep.entries:
             if self.manager.is_live(e.rid):      # a request may have ended since it was packed
                 self.manager.commit(e.rid, len(e.tokens))
@@ -329,13 +330,13 @@ class ModelRunner:
                 self._upload()
                 stream = torch.cuda.Stream(self.device)
                 stream.wait_stream(torch.cuda.current_stream(self.device))
-                with torch.cuda.stream(stream):
+                with torch.cuda.stream(stream), ops.stream_scope():
                     self.model.forward(ctx)           # warm-up outside capture
                 torch.cuda.current_stream(self.device).wait_stream(stream)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
-                with torch.cuda.graph(graph, pool=pool):
+                with torch.cuda.graph(graph, pool=pool), ops.stream_scope():
                     out = self.model.forward(ctx)
                 pool = pool or graph.pool()
                 self.graphs[size] = (graph, out, size, ops.launch_count() - before)

@@ -26,6 +26,7 @@ TCGEN05_MAX_TOKENS = int(os.environ.get("TINYSERVE_TCGEN05_MAX_TOKENS", "16"))
 BF16_ATTENTION = os.environ.get("TINYSERVE_BF16_ATTENTION", "tcgen05")
 TCGEN05_HEAD_DIMS = (64, 128)
 MMA_MAX_HEAD_DIM = 256
+MMA_PREFILL_ROWS = 64           # query rows of a block of the mma prefill kernel (4 warps of 16)
 #: how the key ranges of split-KV decode are merged: "launch" (a second, tiny kernel) or "kernel"
 #: (inside the decode kernel, by the block that finishes last).  Measured on B200 from CUDA graphs,
 #: 8 requests x 640 keys: 14.4 us with the second launch, 18.9 us merged in the kernel.
@@ -81,8 +82,29 @@ def require_device(device) -> None:
         raise RuntimeError(f"tinyserve_b200 runs on CUDA devices only, got {device!r}")
 
 
+_STREAM = None
+
+
 def _stream():
+    if _STREAM is not None:
+        return _STREAM
     return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Looks the current CUDA stream up once for all ops launched inside the scope (the lookup
+    costs more than a kernel launch).  The current stream must not change inside the scope."""
+
+    def __enter__(self):
+        global _STREAM
+        self._outer = _STREAM
+        _STREAM = c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _STREAM
+        _STREAM = self._outer
+        return False
 
 
 def _ptr(t):
@@ -378,11 +400,73 @@ def attention_splits(num_requests, max_q_len, max_kv_len, num_heads, num_kv_head
     return max(1, min(want, max_kv_len // 128, 32))
 
 
+class AttentionWork:
+    """The work lists of a step's attention launches, built once per step on the host."""
+    __slots__ = ("tile_req", "tile_q0", "num_tiles", "dec_req", "dec_tok", "num_decode", "max_decode_kv")
+
+
+def attention_work(ctx, queries_per_tile, device, split_decodes=True):
+    """Cuts a step's attention into work lists (int32 device tensors).  Requests with several
+    tokens are cut into blocks of ``queries_per_tile`` queries, (request, first query) each,
+    heaviest (most keys) first, so that a long portion beside many short requests launches no
+    block for nothing.  With ``split_decodes``, requests of one token are listed apart, (request,
+    token) each: they go to the decode kernel, which does not spend a block of rows on one query."""
+    cache = getattr(ctx, "tile_cache", None)
+    key = (queries_per_tile, split_decodes)
+    if cache is not None and key in cache:
+        return cache[key]
+    host = getattr(ctx, "host", None) or {}
+    cu = host.get("cu_q") or ctx.cu_q.tolist()
+    kv = host.get("kv_lens") or ctx.kv_lens.tolist()
+    tiles, decodes = [], []
+    for b in range(ctx.num_requests):
+        n = cu[b + 1] - cu[b]
+        if n == 1 and split_decodes:
+            decodes.append((kv[b], b, cu[b]))
+            continue
+        for q0 in range(0, n, queries_per_tile):
+            tiles.append((kv[b] - n + q0, b, q0))
+    tiles.sort(reverse=True)
+    decodes.sort(reverse=True)               # the longest contexts start first
+    dec_req, dec_tok = [d[1] for d in decodes], [d[2] for d in decodes]
+    max_decode_kv = decodes[0][0] if decodes else 0
+    work = AttentionWork()
+    work.num_tiles, work.num_decode, work.max_decode_kv = len(tiles), len(dec_req), max_decode_kv
+    packed = torch.tensor([t[1] for t in tiles] + [t[2] for t in tiles] + dec_req + dec_tok, dtype=torch.int32)
+    if device.type == "cuda":
+        packed = packed.pin_memory().to(device, non_blocking=True)
+    nt, nd = work.num_tiles, work.num_decode
+    work.tile_req, work.tile_q0 = packed[:nt], packed[nt:2 * nt]
+    work.dec_req, work.dec_tok = packed[2 * nt:2 * nt + nd], packed[2 * nt + nd:]
+    if cache is not None:
+        cache[key] = work
+    return work
+
+
 def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     """Key ranges for the tensor-core decode kernel: as many as fit in one wave of blocks (two
     per SM), with at least two tiles of 64 keys per range."""
     blocks = num_kv_heads * -(-(num_heads // num_kv_heads) // 16) * num_requests
     return max(1, min(2 * NUM_SMS // blocks, max_kv_len // 128, 32))
+
+
+def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
+    """The one-token requests of a mixed batch, by the tensor-core decode kernel."""
+    T, H, D = q.shape
+    Hkv = k_cache.shape[1]
+    n = work.num_decode
+    num_splits = decode_splits(n, work.max_decode_kv, H, Hkv)
+    part_o = part_ml = None
+    if num_splits > 1:
+        part_o = torch.empty(n * H * num_splits * D, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n * H * num_splits * 2, dtype=torch.float32, device=q.device)
+    lib = _attention_mma(D)
+    _check(lib, lib.ts_paged_attention_mma(
+        _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
+        _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(1), c_int(H), c_int(Hkv),
+        c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
+        c_int(num_splits), _ptr(part_o), _ptr(part_ml), None, c_int(1), _ptr(work.dec_req), _ptr(work.dec_tok),
+        c_int(n), c_int(0), _stream()), 2 if num_splits > 1 else 1)
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
@@ -401,11 +485,18 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             and 8 <= page <= 128 and page & (page - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
         out = torch.empty_like(q)
         lib = _attention_tcgen05(D)
-        _check(lib, lib.ts_paged_attention_tcgen05(
-            _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
-            _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
-            c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
-            c_int(window), _stream()))
+        group = H // Hkv
+        tile_queries = 128 // group if group < 128 else 1
+        work = attention_work(ctx, tile_queries, q.device)
+        if work.num_decode:
+            _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
+        if work.num_tiles:
+            _check(lib, lib.ts_paged_attention_tcgen05(
+                _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
+                _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H), c_int(Hkv),
+                c_int(k_cache.shape[0]), c_int(page), c_int(view.block_table.stride(0)), c_float(scale),
+                c_int(window), _ptr(work.tile_req), _ptr(work.tile_q0), c_int(work.num_tiles),
+                c_int(tile_queries), _stream()))
         return out
     if num_splits is None:
         if decode:
@@ -427,12 +518,24 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         counters = None
         if num_splits > 1 and DECODE_MERGE == "kernel" and ctx.num_requests * Hkv * -(-(H // Hkv) // 16) <= 16384:
             counters, launches = _tile_counters(q.device), 1
+        tile_req = tile_q0 = None
+        num_tiles = tile_queries = 0
+        if not decode:
+            group = H // Hkv
+            tile_queries = MMA_PREFILL_ROWS // group if group < MMA_PREFILL_ROWS else 1
+            work = attention_work(ctx, tile_queries, q.device)
+            if work.num_decode:
+                _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
+            if not work.num_tiles:
+                return out
+            tile_req, tile_q0, num_tiles = work.tile_req, work.tile_q0, work.num_tiles
         _check(lib, lib.ts_paged_attention_mma(
             _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
             _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
-            c_int(1 if decode else 0), _stream()), launches)
+            c_int(1 if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
+            _stream()), launches)
         return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention(
