@@ -41,7 +41,7 @@ def test_embed_lookup(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("n", [72, 100, 1000, 4104])
+@pytest.mark.parametrize("n", [72, 100, 1000, 1028, 4104, 8192])
 @pytest.mark.parametrize("wdtype", ["same", "f32"])
 def test_add_rmsnorm(dtype, n, wdtype):
     rows, eps = 7, 3e-6
@@ -274,12 +274,12 @@ def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window, b
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])
-@pytest.mark.parametrize("merge", ["launch", "kernel"])
+@pytest.mark.parametrize("merge", ["cluster", "launch", "kernel"])
 def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention, merge, monkeypatch):
     """Every request brings one token: the decode kernels."""
     if (dtype == torch.float32 and bf16_attention != "mma") or bf16_attention == "tcgen05":
         pytest.skip("float32 has one back end; decode has no tcgen05 kernel")
-    if merge == "kernel" and (dtype == torch.float32 or bf16_attention == "simt" or splits == 1):
+    if merge != "launch" and (dtype == torch.float32 or bf16_attention == "simt" or splits == 1):
         pytest.skip("only the tensor-core decode kernel merges its key ranges itself")
     monkeypatch.setattr(ops(), "DECODE_MERGE", merge)
     kv_lens = [1, 64, 65, 300, 129, 1000, 17]
@@ -428,6 +428,47 @@ def test_linear_picks_tcgen05_and_falls_back():
     assert o.TCGEN05_MAX_TOKENS < 300
     x3 = rnd(300, 256, seed=5, dtype=torch.bfloat16)
     close(o.linear(x3, w[:64, :256].contiguous()), x3.double() @ w[:64, :256].double().T, torch.bfloat16, "many rows")
+    assert o.gemm_tcgen05_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (1, 256, 512), (13, 328, 1024), (16, 1024, 12288), (5, 136, 72)])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_product_with_residual_add_and_scaled_rows(M, N, K, wdtype):
+    """The residual form of the tcgen05 product (its K cuts are a cluster that adds the partial
+    sums, adds the residual and leaves rows without their norm factor) and the product that reads
+    such rows and scales its result: together they are product + residual add + RMSNorm + product."""
+    o = ops()
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
+    res = rnd(M, N, seed=3, scale=2.0)
+    wn = rnd(N, seed=4, dtype=wdtype) + 1
+    eps = 1e-5
+    pending = o.linear(x, w, allow_pending=True)
+    assert isinstance(pending, o.PendingProduct) and pending.shape == (M, N)
+    close(pending.materialize(), x.double() @ w.double().T, torch.bfloat16, "materialize")
+    r1 = res.clone()
+    rows = o.add_rmsnorm(pending, r1, wn, eps, torch.bfloat16, scaled_ok=True)
+    assert isinstance(rows, o.ScaledRows) and rows.shape == (M, N)
+    v = res.double().cpu() + x.double().cpu() @ w.double().cpu().T
+    assert (r1.double().cpu() - v).abs().max().item() < 1e-5 * max(1.0, v.abs().max().item()), "32-bit residual"
+    want = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * wn.double().cpu()
+    close(rows.materialize(), want, torch.bfloat16, "normalised rows")
+    # without scaled_ok the same call gives the normalised rows themselves, by the ordinary kernels
+    r2 = res.clone()
+    plain = o.add_rmsnorm(o.linear(x, w, allow_pending=True), r2, wn, eps, torch.bfloat16)
+    assert isinstance(plain, torch.Tensor)
+    close(plain, want, torch.bfloat16, "unfused")
+    # (a product that was not cut along K arrives rounded to bfloat16 on this path)
+    assert (r2 - r1).abs().max().item() <= 2.0 ** -8 * (v - res.double().cpu()).abs().max().item()
+    # the next product reads the rows without their factor and scales its result
+    for N2, partials in ((384, False), (1152, True)):
+        w2 = rnd(N2, N, seed=7, dtype=torch.bfloat16, scale=0.1)
+        ref = rows.materialize().double().cpu() @ w2.double().cpu().T
+        got = o.linear(rows, w2, allow_partials=partials)
+        close(o.materialize(got), ref, torch.bfloat16, "scaled product")
+        if wdtype == torch.float32:
+            out32 = o.linear(rows, w2, out_float32=True)
+            assert out32.dtype == torch.float32
+            close(out32, ref, torch.bfloat16, "scaled product, 32-bit out")
     assert o.gemm_tcgen05_error() == 0
 
 

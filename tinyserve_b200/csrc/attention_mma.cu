@@ -53,6 +53,7 @@ struct MmaAttnParams {
   float* part_o;            // [T, H, splits, D]
   float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
   int* counters;            // [requests * gridDim.x] zeros: the block that arrives last merges the key ranges
+  int cluster_merge;        // the key ranges of a (request, KV group) form a cluster and merge in shared memory
   int H, Hkv, page_shift, page_mask, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
@@ -330,7 +331,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   char* Vs = Ks + DEC_STAGES * BN * ROW_BYTES;       // [DEC_STAGES][BN][ROW_BYTES]
 
   pdl_trigger();
-  pdl_wait();
+  // The lengths, the block table and every cached key but the newest were written before this
+  // step's kernels began: the first tiles are fetched before pdl_wait(), while the kernels that
+  // make this token's query, key and value still run.  The tile with the newest key and the
+  // query follow after it.
   // with a request list block z handles its entry z (the one-token requests of a mixed batch)
   const int b = p.tile_req ? p.tile_req[blockIdx.z] : blockIdx.z, split = blockIdx.y;
   const int kvh = blockIdx.x / p.head_tiles, head_tile = blockIdx.x % p.head_tiles;
@@ -346,7 +350,13 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   const int per_split = (total + p.num_splits - 1) / p.num_splits;
   const int tile_begin = first_tile + split * per_split;
   const int n_tiles = max(0, min(first_tile + total, tile_begin + per_split) - tile_begin);
+  const int newest_tile = qpos / BN;
 
+#pragma unroll
+  for (int s = 0; s < DEC_STAGES - 1; ++s)
+    if (s < n_tiles && tile_begin + s != newest_tile)
+      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+  pdl_wait();
   for (int i = threadIdx.x; i < 16 * CH; i += THREADS) {
     const int r = i / CH, c = i % CH;
     const bool valid = r < ng;
@@ -355,8 +365,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   }
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles)
+    if (s < n_tiles && tile_begin + s == newest_tile)
       load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+    // the first group holds the query and all of these tiles; the others stay empty, so that the
+    // loop below finds as many groups as it counts on
     cp_async_commit();
   }
   int pos[2], lo[2];
@@ -403,6 +415,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   // merge the four warps' partial softmax through shared memory (the K buffers are free now)
   float* sm_o = reinterpret_cast<float*>(Ks);                  // [4][16][D]
   float* sm_ml = sm_o + 4 * 16 * D;                            // [4][16][2]
+  float* cl_ml = sm_ml + 4 * 16 * 2;                           // [16][2] of the block, for its cluster
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     float sum = l[h];
@@ -436,6 +449,13 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     const int head = kvh * G + g0 + r;
     if (p.num_splits == 1) {
       p.out[((size_t)q_begin * p.H + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else if (p.cluster_merge) {
+      // this thread has read its four values of (r, d); the first warp's place now holds their sum
+      sm_o[r * D + d] = num;
+      if (d == 0) {
+        cl_ml[r * 2] = mx;
+        cl_ml[r * 2 + 1] = den;
+      }
     } else {
       // partial rows go by token, or by the entry of the request list when there is one
       const size_t row = (size_t)(p.tile_req ? (int)blockIdx.z : q_begin) * p.H + head;
@@ -445,6 +465,42 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
         p.part_ml[(row * p.num_splits + split) * 2 + 1] = den;
       }
     }
+  }
+  if (p.cluster_merge) {
+    // The blocks of a (request, KV group) are one cluster, rank = key range.  Each block merges
+    // its share of the (head, dimension) pairs from all ranks' shared memory, in rank order.
+    cluster_arrive();
+    cluster_wait();
+    const int per_rank = (ng * D + p.num_splits - 1) / p.num_splits;
+    const int i_end = min(ng * D, (split + 1) * per_rank);
+    for (int i = split * per_rank + threadIdx.x; i < i_end; i += THREADS) {
+      const int r = i / D, d = i % D;
+      float ms[8], ls[8], os[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < p.num_splits) {
+          ms[s] = cluster_load_f32(cl_ml + r * 2, s);
+          ls[s] = cluster_load_f32(cl_ml + r * 2 + 1, s);
+          os[s] = cluster_load_f32(sm_o + r * D + d, s);
+        }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < p.num_splits) mx = fmaxf(mx, ms[s]);
+      float num = 0.f, den = 0.f;
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < p.num_splits) {
+          const float wgt = ms[s] == -INFINITY ? 0.f : exp2f(ms[s] - mx);
+          num = fmaf(wgt, os[s], num);
+          den = fmaf(wgt, ls[s], den);
+        }
+      p.out[((size_t)q_begin * p.H + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+    // no block leaves while a peer may still read its shared memory
+    cluster_arrive();
+    cluster_wait();
+    return;
   }
   if (p.num_splits == 1 || p.counters == nullptr) return;
 
@@ -517,6 +573,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 
 // decode_only != 0: every request brings one token (requests with another count are skipped);
+// decode_only == 2: up to 8 key ranges without counters are merged through the distributed shared
+// memory of a cluster (no scratch is touched, no second launch);
 // num_splits > 1 needs scratch: part_o T*H*splits*D floats, part_ml T*H*splits*2 floats.
 // tile_req / tile_q0 (optional, num_tiles ints each): for the prefill kernel the request and the
 // first query of every block of tile_queries queries; with decode_only the one-token requests of
@@ -534,12 +592,14 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
   TS_REQUIRE(num_splits >= 1 && num_splits <= 64, "paged_attention_mma: num_splits %d out of range", num_splits);
-  TS_REQUIRE(num_splits == 1 || (decode_only && part_o && part_ml), "paged_attention_mma: splits are for decode and need scratch");
+  TS_REQUIRE(num_splits == 1 || (decode_only && ((part_o && part_ml) || (decode_only == 2 && num_splits <= 8 && !counters))),
+             "paged_attention_mma: splits are for decode and need scratch");
   TS_REQUIRE(num_requests <= 65535, "paged_attention_mma: more than 65535 requests");
   MmaAttnParams p;
   p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.counters = counters;
+  p.cluster_merge = 0;
   p.tile_req = tile_req;
   p.tile_q0 = tile_q0;
   TS_REQUIRE((tile_req == nullptr) == (tile_q0 == nullptr) && (tile_req == nullptr || num_tiles > 0),
@@ -564,6 +624,12 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
     TS_REQUIRE(tile_req == nullptr || counters == nullptr, "paged_attention_mma: a request list merges by its own launch");
     const int count = tile_req ? num_tiles : num_requests;
     dim3 grid(Hkv * p.head_tiles, num_splits, count);
+    if (decode_only == 2 && num_splits > 1 && num_splits <= 8 && counters == nullptr) {
+      p.cluster_merge = 1;
+      e = ts_launch_cluster(attn_decode_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), p);
+      if (e != cudaSuccess) return ts_fail("attn_decode (clusters of %d): %s", num_splits, cudaGetErrorString(e));
+      return 0;
+    }
     TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
     if (num_splits > 1 && counters == nullptr) {
       TS_LAUNCH("attention_combine", attention_combine_kernel, (tile_req ? count : num_tokens) * H,

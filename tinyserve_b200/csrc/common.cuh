@@ -35,7 +35,49 @@ static inline int ts_fail(const char* fmt, ...) {
     if (e_ != cudaSuccess) return ts_fail("%s: %s", name, cudaGetErrorString(e_)); \
   } while (0)
 
+#ifdef TS_TIMELINE
+// A build for looking at how the kernels of a step overlap: thread 0 of every block records the
+// GPU's global timer when the block starts (tag 0), when its wait for the predecessor returns
+// (tag 1) and wherever a kernel calls timeline_mark itself.  ts_timeline_read copies the records
+// out.  Product builds compile none of it.
+struct TimelineRecord {
+  unsigned long long ns;
+  int sm, tag, grid_x, grid_y, grid_z, block_x, block_y, block_z, threads, pad;
+};
+constexpr unsigned TIMELINE_CAPACITY = 1u << 17;
+static __device__ TimelineRecord g_timeline[TIMELINE_CAPACITY];
+static __device__ unsigned g_timeline_count;
+__device__ __forceinline__ void timeline_mark(int tag) {
+  if (threadIdx.x | threadIdx.y | threadIdx.z) return;
+  unsigned long long ns;
+  unsigned sm;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  const unsigned i = atomicAdd(&g_timeline_count, 1u);
+  if (i < TIMELINE_CAPACITY)
+    g_timeline[i] = TimelineRecord{ns, (int)sm, tag, (int)gridDim.x, (int)gridDim.y, (int)gridDim.z,
+                                   (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z,
+                                   (int)(blockDim.x * blockDim.y * blockDim.z), 0};
+}
+#define TS_DEFINE_TIMELINE()                                                                       \
+  TS_EXPORT int ts_timeline_read(void* out, int capacity, int reset) {                             \
+    unsigned n = 0;                                                                                \
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;                                         \
+    if (cudaMemcpyFromSymbol(&n, g_timeline_count, sizeof(n)) != cudaSuccess) return -1;           \
+    if (n > TIMELINE_CAPACITY) n = TIMELINE_CAPACITY;                                              \
+    if ((int)n > capacity) n = capacity;                                                           \
+    if (n && cudaMemcpyFromSymbol(out, g_timeline, n * sizeof(TimelineRecord)) != cudaSuccess) return -1; \
+    const unsigned zero = 0;                                                                       \
+    if (reset && cudaMemcpyToSymbol(g_timeline_count, &zero, sizeof(zero)) != cudaSuccess) return -1;     \
+    return (int)n;                                                                                 \
+  }
+#else
+__device__ __forceinline__ void timeline_mark(int) {}
+#define TS_DEFINE_TIMELINE()
+#endif
+
 #define TS_DEFINE_LAST_ERROR() \
+  TS_DEFINE_TIMELINE()         \
   TS_EXPORT const char* ts_last_error() { return ts_error_message; }
 
 // ---------------------------------------------------------------- programmatic dependent launch
@@ -45,8 +87,14 @@ static inline int ts_fail(const char* fmt, ...) {
 // predecessor wrote and before it writes global memory at all; pdl_wait() returns when the
 // predecessor has completed and its writes are visible.  What a kernel does before pdl_wait()
 // (set-up, fetching weights) overlaps the predecessor.  Set TINYSERVE_PDL=0 to launch plainly.
-__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() {
+  timeline_mark(0);
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  timeline_mark(1);
+}
 
 static inline bool ts_pdl_enabled() {
   static int enabled = -1;
@@ -71,6 +119,44 @@ static inline cudaError_t ts_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   cfg.attrs = attr;
   cfg.numAttrs = ts_pdl_enabled() ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// the same with thread-block clusters (the grid a multiple of the cluster in every dimension)
+template <typename... KArgs, typename... Args>
+static inline cudaError_t ts_launch_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, dim3 cluster, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster.x;
+  attr[0].val.clusterDim.y = cluster.y;
+  attr[0].val.clusterDim.z = cluster.z;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ts_pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// distributed shared memory of a cluster: rank, barrier, and a load from a peer block's copy of
+// a shared variable
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ float cluster_load_f32(const float* own_shared, uint32_t rank) {
+  uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(own_shared)), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 #define TS_LAUNCH(name, kernel, grid, block, smem, stream, ...)                          \

@@ -158,6 +158,78 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
   }
 }
 
+// Few rows (decode): a row is spread over a cluster of NORM_CLUSTER blocks, so that its partial
+// sums of a split-K product, which are many times the row itself, come in through that many SMs.
+// Each block adds up the squares of its columns, the blocks read one another's sums from
+// distributed shared memory in rank order (every block gets the same total, the same every run)
+// and each normalises its own columns.  Blocks of a cluster are (rank, row).
+constexpr int NORM_CLUSTER = 8;
+constexpr int PARTIAL_BATCH = 8;      // loads of partial sums in flight per thread
+
+template <typename T>
+__global__ void add_rmsnorm_cluster_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
+                                           float eps, T* __restrict__ out, const int* __restrict__ rows,
+                                           int n, int quads_per_block, int write_residual, PartialSrc ps) {
+  __shared__ float scratch[33];
+  __shared__ float cluster_part;
+  pdl_trigger();
+  const uint32_t rank = cluster_rank();
+  const int c = ((int)rank * quads_per_block + (int)threadIdx.x) * 4;
+  const bool active = (int)threadIdx.x < quads_per_block && c < n;
+  float wv[4] = {0.f, 0.f, 0.f, 0.f};
+  if (active) {      // the weights are constants: fetch them while the predecessor still runs
+    if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv);
+    else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv);
+  }
+  pdl_wait();
+  const int i = blockIdx.y;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  float acc = 0.f;
+  if (active) {
+    Quad<float>::load(residual + r * n + c, v);
+    if (ps.base) {
+      // all loads of a batch are issued before the first is used; the sum runs in split order
+      float xs[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int s0 = 0; s0 < ps.splits; s0 += PARTIAL_BATCH) {
+        float4 q[PARTIAL_BATCH];
+#pragma unroll
+        for (int s = 0; s < PARTIAL_BATCH; ++s)
+          if (s0 + s < ps.splits) q[s] = __ldcg(reinterpret_cast<const float4*>(ps.base + ps.offset(s0 + s, (int)r, c)));
+#pragma unroll
+        for (int s = 0; s < PARTIAL_BATCH; ++s)
+          if (s0 + s < ps.splits) { xs[0] += q[s].x; xs[1] += q[s].y; xs[2] += q[s].z; xs[3] += q[s].w; }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += xs[e];
+    } else if (x) {
+      float xv[4];
+      Quad<T>::load(x + r * n + c, xv);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] += xv[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc += v[e] * v[e];
+  }
+  const float mine = block_sum(acc, scratch);
+  if (threadIdx.x == 0) cluster_part = mine;
+  cluster_arrive();
+  cluster_wait();
+  float total = 0.f;
+#pragma unroll
+  for (int k = 0; k < NORM_CLUSTER; ++k) total += cluster_load_f32(&cluster_part, k);
+  cluster_arrive();        // this block has read its peers; it may not leave before they have read it
+  const float rstd = rsqrtf(total / (float)n + eps);
+  if (active) {
+    if (write_residual) Quad<float>::store(residual + r * n + c, v);
+    float o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = v[e] * rstd * wv[e];
+    Quad<T>::store(out + (size_t)i * n + c, o);
+  }
+  cluster_wait();
+}
+
 template <typename T>
 int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, void* out, const int* rows,
                        int num_out_rows, int n, int write_residual, PartialSrc ps, cudaStream_t stream) {
@@ -165,6 +237,15 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
                                       reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(w.ptr)) % 16 == 0;
   const T* xp = static_cast<const T*>(x);
   T* op = static_cast<T*>(out);
+  if (aligned && num_out_rows <= 32 && n >= 1024 && n <= NORM_CLUSTER * 4 * 1024) {
+    const int quads_per_block = (n / 4 + NORM_CLUSTER - 1) / NORM_CLUSTER;
+    const int threads = (quads_per_block + 31) / 32 * 32;
+    cudaError_t e = ts_launch_cluster(add_rmsnorm_cluster_kernel<T>, dim3(NORM_CLUSTER, num_out_rows), dim3(threads), 0,
+                                      stream, dim3(NORM_CLUSTER), xp, residual, w, eps, op, rows, n, quads_per_block,
+                                      write_residual, ps);
+    if (e != cudaSuccess) return ts_fail("add_rmsnorm: %s", cudaGetErrorString(e));
+    return 0;
+  }
   if (aligned && n <= 4 * 4 * 1024) {
     const int quads = n / 4;
     // few rows (decode): one element group per thread, the shortest chain; many rows (prefill):
@@ -229,6 +310,29 @@ TS_EXPORT int ts_rmsnorm(int dtype, const void* x, const void* weight, int weigh
     TS_LAUNCH("rmsnorm", rmsnorm_kernel<__nv_bfloat16>, num_rows, threads, 0, stream, (const __nv_bfloat16*)x, w, eps, (__nv_bfloat16*)out, n);
   else
     return ts_fail("rmsnorm: unknown dtype %d", dtype);
+  return 0;
+}
+
+// ------------------------------------------------------------------ rows without their norm factor -> rows
+// out[m, :] = x[m, :] * rsqrt(sum_t sumsq[t][m] / n + eps): the normalised rows of what the residual
+// form of the tcgen05 product leaves (x = residual * norm_weight, sums of residual^2 per 128 columns)
+__global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ sumsq, int tiles,
+                                  float eps, __nv_bfloat16* __restrict__ out, int n) {
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x;
+  float sum = 0.f;
+  for (int t = 0; t < tiles; ++t) sum += sumsq[(size_t)t * 16 + m];
+  const float rstd = rsqrtf(sum / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    out[(size_t)m * n + c] = __float2bfloat16_rn(__bfloat162float(x[(size_t)m * n + c]) * rstd);
+}
+
+TS_EXPORT int ts_scale_rows(const void* x, const float* sumsq, int tiles, float eps, void* out, int M, int n,
+                            cudaStream_t stream) {
+  TS_REQUIRE(M > 0 && M <= 16 && n > 0 && tiles > 0, "scale_rows: up to 16 rows with their sums of squares");
+  TS_LAUNCH("scale_rows", scale_rows_kernel, M, 256, 0, stream, (const __nv_bfloat16*)x, sumsq, tiles, eps,
+            (__nv_bfloat16*)out, n);
   return 0;
 }
 
@@ -431,67 +535,128 @@ template <> struct Duo<__nv_bfloat16> {
   }
 };
 
+// What a (token, head) needs besides the head's values: where the result goes, the norm's weights
+// and the angles of the token's position.  None of it is written by this step's kernels, so it is
+// fetched before pdl_wait().
 template <typename T, int STEPS>
-__device__ __forceinline__ void rope_one_head_vec(int t, int head, int lane, const T* __restrict__ qkv, T* __restrict__ q_out,
-                                                const int* __restrict__ positions, RopeArgs rope,
-                                                VecParam qw, VecParam kw, int has_norm, float eps,
-                                                int H, int Hkv, int D, T* __restrict__ k_cache,
-                                                T* __restrict__ v_cache,
-                                                const int* __restrict__ slot_mapping, int page_size,
-                                                int heads_total, PartialSrc ps) {
-  const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
+struct RopeHead {
   T* dst;
-  bool is_v = false;
+  bool skip, is_v;
+  float2 wa[STEPS], wb[STEPS], c[STEPS], sn[STEPS];
+};
+
+template <typename T, int STEPS>
+__device__ __forceinline__ RopeHead<T, STEPS> rope_prepare_vec(int t, int head, int lane, T* __restrict__ q_out,
+                                                               const int* __restrict__ positions, RopeArgs rope,
+                                                               VecParam qw, VecParam kw, int has_norm, int H, int Hkv,
+                                                               int D, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                                               const int* __restrict__ slot_mapping, int page_size) {
+  RopeHead<T, STEPS> h;
+  h.skip = false;
+  h.is_v = false;
   VecParam w = qw;
   if (head < H) {
-    dst = q_out + ((size_t)t * H + head) * D;
+    h.dst = q_out + ((size_t)t * H + head) * D;
   } else {
     const int slot = slot_mapping[t];
-    if (slot < 0) return;
+    h.skip = slot < 0;
     const int kvh = head < H + Hkv ? head - H : head - H - Hkv;
-    is_v = head >= H + Hkv;
-    const size_t page = slot / page_size, in_page = slot % page_size;
-    dst = (is_v ? v_cache : k_cache) + ((page * Hkv + kvh) * page_size + in_page) * D;
+    h.is_v = head >= H + Hkv;
+    const size_t page = h.skip ? 0 : slot / page_size, in_page = h.skip ? 0 : slot % page_size;
+    h.dst = (h.is_v ? v_cache : k_cache) + ((page * Hkv + kvh) * page_size + in_page) * D;
     w = kw;
   }
+  if (h.skip || h.is_v) return h;
   const int half = D >> 1;
-  float2 a[STEPS], b[STEPS];
-  float acc = 0.f;
+  const int pos = positions[t];
 #pragma unroll
   for (int s = 0; s < STEPS; ++s) {
     const int j = 2 * (lane + 32 * s);
     if (j < half) {
-      a[s] = ps.base ? ps.load2(t, head * D + j) : Duo<T>::load(src + j);
-      b[s] = ps.base ? ps.load2(t, head * D + half + j) : Duo<T>::load(src + half + j);
-      acc += a[s].x * a[s].x + a[s].y * a[s].y + b[s].x * b[s].x + b[s].y * b[s].y;
+      h.wa[s] = has_norm ? make_float2(w[j], w[j + 1]) : make_float2(1.f, 1.f);
+      h.wb[s] = has_norm ? make_float2(w[half + j], w[half + j + 1]) : make_float2(1.f, 1.f);
+      h.c[s] = *reinterpret_cast<const float2*>(rope.cos + (size_t)pos * half + j);
+      h.sn[s] = *reinterpret_cast<const float2*>(rope.sin + (size_t)pos * half + j);
     }
   }
-  if (is_v) {
+  return h;
+}
+
+template <typename T, int STEPS>
+__device__ __forceinline__ void rope_apply_vec(const RopeHead<T, STEPS>& h, int t, int head, int lane,
+                                               const T* __restrict__ qkv, int has_norm, float eps, int H, int Hkv,
+                                               int D, PartialSrc ps) {
+  if (h.skip) return;
+  const T* src = qkv + (size_t)t * (H + 2 * Hkv) * D + (size_t)head * D;
+  const int half = D >> 1;
+  float2 a[STEPS], b[STEPS];
+  float acc = 0.f;
+  if (ps.base) {
+    // the loads of all splits are issued before the first is used; the sum runs in split order
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) a[s] = b[s] = make_float2(0.f, 0.f);
+    for (int k0 = 0; k0 < ps.splits; k0 += 4) {
+      float2 qa[4][STEPS], qb[4][STEPS];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (k0 + k < ps.splits && j < half) {
+            qa[k][s] = __ldcg(reinterpret_cast<const float2*>(ps.base + ps.offset(k0 + k, t, head * D + j)));
+            qb[k][s] = __ldcg(reinterpret_cast<const float2*>(ps.base + ps.offset(k0 + k, t, head * D + half + j)));
+          }
+        }
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (k0 + k < ps.splits && j < half) {
+            a[s].x += qa[k][s].x; a[s].y += qa[k][s].y;
+            b[s].x += qb[k][s].x; b[s].y += qb[k][s].y;
+          }
+        }
+    }
+  } else {
 #pragma unroll
     for (int s = 0; s < STEPS; ++s) {
       const int j = 2 * (lane + 32 * s);
       if (j < half) {
-        Duo<T>::store(dst + j, a[s].x, a[s].y);
-        Duo<T>::store(dst + half + j, b[s].x, b[s].y);
+        a[s] = Duo<T>::load(src + j);
+        b[s] = Duo<T>::load(src + half + j);
+      }
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < half) acc += a[s].x * a[s].x + a[s].y * a[s].y + b[s].x * b[s].x + b[s].y * b[s].y;
+  }
+  if (h.is_v) {
+#pragma unroll
+    for (int s = 0; s < STEPS; ++s) {
+      const int j = 2 * (lane + 32 * s);
+      if (j < half) {
+        Duo<T>::store(h.dst + j, a[s].x, a[s].y);
+        Duo<T>::store(h.dst + half + j, b[s].x, b[s].y);
       }
     }
     return;
   }
   const float rstd = has_norm ? rsqrtf(warp_sum(acc) / (float)D + eps) : 1.f;
-  const int pos = positions[t];
 #pragma unroll
   for (int s = 0; s < STEPS; ++s) {
     const int j = 2 * (lane + 32 * s);
     if (j < half) {
       float a0 = a[s].x, a1 = a[s].y, b0 = b[s].x, b1 = b[s].y;
       if (has_norm) {
-        a0 *= rstd * w[j]; a1 *= rstd * w[j + 1];
-        b0 *= rstd * w[half + j]; b1 *= rstd * w[half + j + 1];
+        a0 *= rstd * h.wa[s].x; a1 *= rstd * h.wa[s].y;
+        b0 *= rstd * h.wb[s].x; b1 *= rstd * h.wb[s].y;
       }
-      const float2 c = *reinterpret_cast<const float2*>(rope.cos + (size_t)pos * half + j);
-      const float2 sn = *reinterpret_cast<const float2*>(rope.sin + (size_t)pos * half + j);
-      Duo<T>::store(dst + j, a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
-      Duo<T>::store(dst + half + j, b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+      const float2 c = h.c[s], sn = h.sn[s];
+      Duo<T>::store(h.dst + j, a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+      Duo<T>::store(h.dst + half + j, b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
     }
   }
 }
@@ -505,11 +670,19 @@ __global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __
                                                 const int* __restrict__ slot_mapping, int page_size,
                                                 int heads_total, PartialSrc ps) {
   pdl_trigger();
-  pdl_wait();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int head = blockIdx.y * warps + warp; head < heads_total; head += gridDim.y * warps)
-    rope_one_head_vec<T, STEPS>(blockIdx.x, head, lane, qkv, q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv,
-                                D, k_cache, v_cache, slot_mapping, page_size, heads_total, ps);
+  const int t = blockIdx.x, first = blockIdx.y * warps + warp;
+  RopeHead<T, STEPS> h;
+  if (first < heads_total)
+    h = rope_prepare_vec<T, STEPS>(t, first, lane, q_out, positions, rope, qw, kw, has_norm, H, Hkv, D, k_cache,
+                                   v_cache, slot_mapping, page_size);
+  pdl_wait();
+  for (int head = first; head < heads_total; head += gridDim.y * warps) {
+    if (head != first)
+      h = rope_prepare_vec<T, STEPS>(t, head, lane, q_out, positions, rope, qw, kw, has_norm, H, Hkv, D, k_cache,
+                                     v_cache, slot_mapping, page_size);
+    rope_apply_vec<T, STEPS>(h, t, head, lane, qkv, has_norm, eps, H, Hkv, D, ps);
+  }
 }
 
 TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, const int* positions,

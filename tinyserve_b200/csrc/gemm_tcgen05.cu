@@ -23,6 +23,10 @@ TS_DEFINE_LAST_ERROR()
 
 namespace {
 
+#ifndef TS_GEMM_RING_KB
+#define TS_GEMM_RING_KB 110          // shared memory of a block's ring of stages
+#endif
+
 using bf16 = __nv_bfloat16;
 constexpr int TILE_N = 128;          // weight rows of a block (MMA M)
 constexpr int BK = 64;               // K elements of a stage: 128 bytes, one swizzle row
@@ -35,7 +39,21 @@ struct GemmParams {
   int* counters;        // [row tiles * token tiles], zero between calls
   int M, N, K, ldc;
   int splits, out_f32;
+  // Rows of x that still lack their RMSNorm factor: x holds v * norm_weight, and the sums of v^2
+  // lie in x_sumsq [x_tiles][SUMSQ_STRIDE] (one partial sum per 128 columns of v).  The factor
+  // rsqrt(sum / K + x_eps) of a token scales its column of the result.
+  const float* x_sumsq;
+  int x_tiles;
+  float x_eps;
+  // The residual form (the K cuts of a row tile are one cluster): residual [M, N] += result;
+  // hprime [M, N] = bfloat16(residual * norm_w); sumsq_out [row tile][SUMSQ_STRIDE] = sums of
+  // residual^2 over the tile's 128 columns, for the product that reads hprime.
+  float* residual;
+  VecParam norm_w;
+  bf16* hprime;
+  float* sumsq_out;
 };
+constexpr int SUMSQ_STRIDE = 16;     // tokens of the residual form (one token tile of 16)
 
 // instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = tile_t
 __host__ __device__ constexpr uint32_t instr_desc(int tile_t) {
@@ -63,7 +81,8 @@ template <int TILE_T> struct Cfg {
   static constexpr int X_STAGE_BYTES = TILE_T * BK * 2;
   static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_STAGE_BYTES;
   // two blocks share an SM: stay below ~100 KB of stages
-  static constexpr int STAGES = (96 * 1024) / STAGE_BYTES < 2 ? 2 : ((96 * 1024) / STAGE_BYTES > 8 ? 8 : (96 * 1024) / STAGE_BYTES);
+  static constexpr int RING = TS_GEMM_RING_KB * 1024;
+  static constexpr int STAGES = RING / STAGE_BYTES < 2 ? 2 : (RING / STAGE_BYTES > 8 ? 8 : RING / STAGE_BYTES);
   static constexpr int TMEM_COLS = Accs<TILE_T>::N * TILE_T < 32 ? 32 : Accs<TILE_T>::N * TILE_T;
   static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
 };
@@ -81,6 +100,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* is_last = const_cast<int*>(abort_flag) + 1;
+
+  __shared__ float row_scale[TILE_T];
+  __shared__ float sum_scratch[33];
 
   pdl_trigger();
   const int n_tile = blockIdx.x, t_tile = blockIdx.y, split = blockIdx.z;
@@ -135,6 +157,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       tma_load_2d(smem_u32(stage + W_STAGE_BYTES), &map_x, bar, (kb0 + i) * BK, t_tile * TILE_T);
       armed = i + 1;
     }
+    timeline_mark(2);      // all loads issued
     if (*abort_flag) {
       // let the copies that are still in flight land before the block goes away
       for (int i = max(0, armed - C::STAGES); i < armed; ++i) {
@@ -163,8 +186,16 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (ok && nkb > 0) tcgen05_commit(smem_u32(accum));
   } else {
     pdl_wait();
+    if (p.x_sumsq != nullptr && threadIdx.x >= 64 && threadIdx.x < 64 + TILE_T) {
+      const int j = threadIdx.x - 64, m = t_tile * TILE_T + j;
+      float sum = 0.f;
+      if (m < p.M)
+        for (int t = 0; t < p.x_tiles; ++t) sum += __ldcg(p.x_sumsq + (size_t)t * SUMSQ_STRIDE + m);
+      row_scale[j] = rsqrtf(sum / (float)p.K + p.x_eps);
+    }
   }
-  __syncwarp();
+  __syncthreads();
+  const bool scaled = p.x_sumsq != nullptr;
 
   // epilogue: lane = weight row, columns = tokens
   bool have = nkb > 0;
@@ -174,7 +205,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int n = n_tile * TILE_N + warp * 32 + lane;
   const int t0 = t_tile * TILE_T;
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
-  if (p.splits == 1) {
+  if (p.residual != nullptr) {
+    // residual form.  Every block of the cluster leaves its partial tile in its shared memory
+    // (the ring is idle: all MMAs have completed); rank r then owns the tokens r, r + splits, ...:
+    // it adds the ranks' partial sums in rank order, adds the residual, and writes the new
+    // residual, its product with the norm's weight and the tile's sum of squares.
+    float* red = reinterpret_cast<float*>(smem);               // [TILE_T][TILE_N]
 #pragma unroll 1
     for (int c = 0; c < TILE_T; c += 8) {
       float v[8];
@@ -182,6 +218,48 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) red[(c + i) * TILE_N + threadIdx.x] = scaled ? v[i] * row_scale[c + i] : v[i];
+    }
+    const float wn = n < p.N ? p.norm_w[n] : 0.f;
+    cluster_arrive();
+    cluster_wait();
+    for (int j = split; j < TILE_T && t0 + j < p.M; j += p.splits) {
+      const int m = t0 + j;
+      float part[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (s < p.splits) part[s] = cluster_load_f32(red + j * TILE_N + threadIdx.x, s);
+      float sq = 0.f;
+      if (n < p.N) {
+        float sum = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; ++s)
+          if (s < p.splits) sum += part[s];
+        const float v = p.residual[(size_t)m * p.N + n] + sum;
+        p.residual[(size_t)m * p.N + n] = v;
+        p.hprime[(size_t)m * p.N + n] = __float2bfloat16_rn(v * wn);
+        sq = v * v;
+      }
+      const float total = block_sum(sq, sum_scratch);
+      if (threadIdx.x == 0) p.sumsq_out[(size_t)n_tile * SUMSQ_STRIDE + m] = total;
+    }
+    // no block leaves while a peer may still read its shared memory
+    cluster_arrive();
+    cluster_wait();
+  } else if (p.splits == 1) {
+#pragma unroll 1
+    for (int c = 0; c < TILE_T; c += 8) {
+      float v[8];
+      if (have) tmem_load8_sum<TILE_T>(taddr + c, v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = 0.f;
+      }
+      if (scaled) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= row_scale[c + i];
       }
       if (n < p.N) {
 #pragma unroll
@@ -206,7 +284,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = v[i];
+      for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = scaled ? v[i] * row_scale[c + i] : v[i];
     }
     if (p.out != nullptr) {
     __threadfence();
@@ -248,6 +326,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
   tcgen05_fence_before();
   __syncthreads();
+  timeline_mark(3);        // results stored
   if (warp == 0) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
   }
@@ -546,6 +625,13 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, di
     if (e != cudaSuccess) return ts_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
     configured = true;
   }
+  if (p.residual != nullptr) {
+    // the K cuts of a row tile are the blocks of one cluster
+    cudaError_t e = ts_launch_cluster(gemm_wx_kernel<TILE_T>, grid, dim3(THREADS), Cfg<TILE_T>::SMEM, stream,
+                                      dim3(1, 1, p.splits), mw, mx, p);
+    if (e != cudaSuccess) return ts_fail("gemm_tcgen05 (clusters of %d): %s", p.splits, cudaGetErrorString(e));
+    return 0;
+  }
   TS_LAUNCH("gemm_tcgen05", gemm_wx_kernel<TILE_T>, grid, THREADS, Cfg<TILE_T>::SMEM, stream, mw, mx, p);
   return 0;
 }
@@ -584,16 +670,53 @@ TS_EXPORT long long ts_gemm_tcgen05_scratch(int M, int N, int splits) {
 // counters: at least (N / 128 rounded up) * (M tiles) ints, all zero, when splits > 1.
 // out == nullptr (with splits > 1): only the partial tiles are produced, laid out
 // [split][token tile][row tile][token in tile][row in tile]; a consumer kernel adds them up.
+namespace {
+int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
+               long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
+               int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
+               float* sumsq_out, cudaStream_t stream);
+}
+
 TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                               long long ldw, long long ldc, int out_f32, int splits, float* partials,
                               int* counters, cudaStream_t stream) {
+  return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, nullptr, 0, 0.f,
+                    nullptr, nullptr, 0, nullptr, nullptr, stream);
+}
+
+// The same product with one or both of two extras, for up to 16 tokens.
+// x_sumsq != nullptr: x holds rows v * norm_weight that still lack their RMSNorm factor, and
+// x_sumsq [x_tiles][16] the sums of v^2 over each 128 columns; every token's result is scaled by
+// rsqrt(sum / K + x_eps).
+// residual != nullptr (out, partials and counters unused; splits <= 8, the cuts of a row tile
+// are one thread-block cluster): residual [M, N] (float, contiguous) += x w^T; hprime [M, N]
+// (bfloat16) = residual * norm_w; sumsq_out [N / 128 rounded up][16] = the sums of residual^2
+// over each 128 columns, for the product that takes hprime as its x.
+TS_EXPORT int ts_gemm_tcgen05_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
+                                    long long ldw, long long ldc, int out_f32, int splits, float* partials,
+                                    int* counters, const float* x_sumsq, int x_tiles, float x_eps,
+                                    float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
+                                    float* sumsq_out, cudaStream_t stream) {
+  TS_REQUIRE(M <= SUMSQ_STRIDE, "gemm_tcgen05: the fused forms take up to %d tokens, got %d", SUMSQ_STRIDE, M);
+  TS_REQUIRE(x_sumsq == nullptr || x_tiles > 0, "gemm_tcgen05: sums of squares without their tile count");
+  TS_REQUIRE(residual == nullptr || (norm_w && hprime && sumsq_out && splits <= 8),
+             "gemm_tcgen05: the residual form needs the norm's weight, both outputs and at most 8 cuts");
+  return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, x_sumsq, x_tiles,
+                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, stream);
+}
+
+namespace {
+int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
+               long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
+               int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
+               float* sumsq_out, cudaStream_t stream) {
   TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
   TS_REQUIRE(M <= 65535 * 128, "gemm_tcgen05: too many rows");
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
   TS_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
   TS_REQUIRE(splits >= 1 && splits <= 64, "gemm_tcgen05: splits out of range");
-  TS_REQUIRE(splits == 1 || (partials && (counters || out == nullptr)), "gemm_tcgen05: split-K needs scratch and counters");
-  TS_REQUIRE(out != nullptr || splits > 1, "gemm_tcgen05: without an output the partial tiles must be asked for (splits > 1)");
+  TS_REQUIRE(residual != nullptr || splits == 1 || (partials && (counters || out == nullptr)), "gemm_tcgen05: split-K needs scratch and counters");
+  TS_REQUIRE(residual != nullptr || out != nullptr || splits > 1, "gemm_tcgen05: without an output the partial tiles must be asked for (splits > 1)");
   const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap mw, mx;
   TS_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_N), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the weights");
@@ -601,6 +724,9 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
   GemmParams p;
   p.out = out; p.partials = partials; p.counters = counters;
   p.M = M; p.N = N; p.K = K; p.ldc = (int)ldc; p.splits = splits; p.out_f32 = out_f32;
+  p.x_sumsq = x_sumsq; p.x_tiles = x_tiles; p.x_eps = x_eps;
+  p.residual = residual; p.norm_w = VecParam{norm_w, norm_w_is_f32};
+  p.hprime = static_cast<bf16*>(hprime); p.sumsq_out = sumsq_out;
   dim3 grid((N + TILE_N - 1) / TILE_N, (M + tile_t - 1) / tile_t, splits);
   switch (tile_t) {
     case 16: return launch<16>(mw, mx, p, grid, stream);
@@ -609,6 +735,7 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
     default: return launch<128>(mw, mx, p, grid, stream);
   }
 }
+}  // namespace
 
 // scratch floats of the persistent form for `blocks` blocks
 TS_EXPORT long long ts_gemm_tcgen05_persistent_scratch(int M, int blocks) {

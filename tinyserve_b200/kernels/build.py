@@ -78,7 +78,9 @@ def unit_path(source: str, defines: dict) -> tuple:
 
 def compile_unit(source: str, defines: dict | None = None) -> str:
     """Build one unit if its library is not there yet; returns the library's path."""
-    defines = defines or {}
+    defines = dict(defines or {})
+    if os.environ.get("TINYSERVE_TIMELINE", "0") == "1":
+        defines["TS_TIMELINE"] = 1         # the build that records when every block starts and waits
     out, src, flags = unit_path(source, defines)
     if os.path.isfile(out):
         return out
@@ -121,6 +123,11 @@ def load_unit(source: str, defines: dict | None = None) -> ctypes.CDLL:
     with _lock:
         _loaded[key] = lib
     return lib
+
+
+def loaded_units() -> list:
+    with _lock:
+        return list(_loaded.values())
 
 
 def compile_many(units) -> list:

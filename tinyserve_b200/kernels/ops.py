@@ -27,10 +27,13 @@ BF16_ATTENTION = os.environ.get("TINYSERVE_BF16_ATTENTION", "tcgen05")
 TCGEN05_HEAD_DIMS = (64, 128)
 MMA_MAX_HEAD_DIM = 256
 MMA_PREFILL_ROWS = 64           # query rows of a block of the mma prefill kernel (4 warps of 16)
-#: how the key ranges of split-KV decode are merged: "launch" (a second, tiny kernel) or "kernel"
-#: (inside the decode kernel, by the block that finishes last).  Measured on B200 from CUDA graphs,
-#: 8 requests x 640 keys: 14.4 us with the second launch, 18.9 us merged in the kernel.
-DECODE_MERGE = "launch"
+#: how the key ranges of split-KV decode are merged: "cluster" (the ranges of a (request, KV group)
+#: are the blocks of a thread-block cluster and merge through distributed shared memory; up to 8
+#: ranges, more fall back to "launch"), "launch" (a second, tiny kernel) or "kernel" (inside the
+#: decode kernel, through global memory, by the block that finishes last).  Measured on B200 from
+#: CUDA graphs, 8 requests x 640 keys: 14.4 us with the second launch, 18.9 us merged in the kernel.
+DECODE_MERGE = os.environ.get("TINYSERVE_DECODE_MERGE", "cluster")
+CLUSTER_MERGE_MAX_SPLITS = 8
 
 
 class SplitPartials:
@@ -59,10 +62,65 @@ class SplitPartials:
 
 _NO_PARTIALS = (c_void_p(0), c_int(0), c_int(0), c_int(0), c_int(0))
 
+#: let the product before a residual add + norm do the add itself (PendingProduct, ScaledRows)
+FUSED_RESIDUAL = os.environ.get("TINYSERVE_FUSED_RESIDUAL", "1") != "0"
+FUSED_MAX_TOKENS = 16
+FUSED_MAX_SPLITS = 8
+
+
+class PendingProduct:
+    """x @ weight^T that has not been launched yet.  ``linear(..., allow_pending=True)`` returns it
+    for a few tokens, because the residual add + norm that usually follows can run in the
+    product's own kernel: ``add_rmsnorm`` then launches the residual form of the tcgen05 kernel
+    (the K cuts of a row tile are a thread-block cluster; they add their partial sums through
+    distributed shared memory, add the residual and leave a ScaledRows).  Any other consumer
+    calls ``partials()`` or ``materialize()`` and gets the ordinary product."""
+
+    def __init__(self, x, weight):
+        self.x, self.weight = x, weight
+        self.shape = (x.shape[0], weight.shape[0])
+        self.dtype, self.device = x.dtype, x.device
+
+    def splits(self):
+        M, K = self.x.shape
+        return min(gemm_splits(M, self.weight.shape[0], K, partials=True), FUSED_MAX_SPLITS)
+
+    def partials(self):
+        if SPLIT_PARTIALS and self.splits() > 1:
+            return _linear_tcgen05(self.x, self.weight, False, partials_only=True)
+        return self.materialize()
+
+    def materialize(self):
+        return _linear_tcgen05(self.x, self.weight, False)
+
+
+class ScaledRows:
+    """Rows that still lack their RMSNorm factor: ``data`` [M, N] holds residual * norm_weight in
+    bfloat16 and ``sumsq`` [tiles, 16] the sums of residual^2 over each 128 columns.  ``linear``
+    takes it as x and scales every token's result by rsqrt(sum / N + eps) in its epilogue, which
+    is the same product as with normalised rows; ``materialize()`` gives the normalised rows."""
+
+    def __init__(self, data, sumsq, tiles, eps):
+        self.data, self.sumsq, self.tiles, self.eps = data, sumsq, tiles, eps
+        self.shape, self.dtype, self.device = tuple(data.shape), data.dtype, data.device
+
+    def args(self):
+        return (_ptr(self.sumsq), c_int(self.tiles), c_float(self.eps))
+
+    def materialize(self):
+        out = torch.empty_like(self.data)
+        lib = _elementwise()
+        _check(lib, lib.ts_scale_rows(_ptr(self.data), *self.args(), _ptr(out), c_int(self.shape[0]),
+                                      c_int(self.shape[1]), _stream()))
+        return out
+
+
+_NO_SCALE = (c_void_p(0), c_int(0), c_float(0.0))
+
 
 def materialize(x):
-    """An ordinary tensor from what a product returned."""
-    return x.materialize() if isinstance(x, SplitPartials) else x
+    """An ordinary tensor from what a product or a norm returned."""
+    return x.materialize() if isinstance(x, (SplitPartials, PendingProduct, ScaledRows)) else x
 
 
 def launch_count() -> int:
@@ -149,7 +207,10 @@ def _gemm():
 
 
 def _gemm_tcgen05():
-    return build.load_unit("gemm_tcgen05.cu")
+    defines = {}
+    if "TINYSERVE_GEMM_RING_KB" in os.environ:
+        defines["TS_GEMM_RING_KB"] = int(os.environ["TINYSERVE_GEMM_RING_KB"])
+    return build.load_unit("gemm_tcgen05.cu", defines)
 
 
 _counters: dict = {}
@@ -210,12 +271,13 @@ def _persistent_scratch(device):
     return _partials[key]
 
 
-def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False):
+def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False, scale=None):
+    """``scale``: the ScaledRows whose ``data`` is ``x`` (tiled form only)."""
     M, K = x.shape
     N = weight.shape[0]
     out = None if partials_only else torch.empty(
         M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
-    form = "tiled" if partials_only else (form or TCGEN05_FORM)
+    form = "tiled" if partials_only or scale is not None else (form or TCGEN05_FORM)
     lib = _gemm_tcgen05()
     if form == "persistent":
         blocks = min(blocks or NUM_SMS, NUM_SMS)
@@ -234,10 +296,16 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None,
         need = lib.ts_gemm_tcgen05_scratch(c_int(M), c_int(N), c_int(splits))
         partials = torch.empty(need, dtype=torch.float32, device=x.device)
         counters = None if partials_only else _tile_counters(x.device)
-    _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
-                                    c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
-                                    c_int(1 if out_float32 else 0), c_int(splits), _ptr(partials),
-                                    _ptr(counters), _stream()))
+    if scale is not None:
+        _check(lib, lib.ts_gemm_tcgen05_fused(
+            _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
+            c_longlong(weight.stride(0)), c_longlong(N), c_int(1 if out_float32 else 0), c_int(splits),
+            _ptr(partials), _ptr(counters), *scale.args(), None, None, c_int(0), None, None, _stream()))
+    else:
+        _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
+                                        c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
+                                        c_int(1 if out_float32 else 0), c_int(splits), _ptr(partials),
+                                        _ptr(counters), _stream()))
     if partials_only:
         tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         return SplitPartials(partials, splits, M, N, tile_t, torch.bfloat16)
@@ -295,10 +363,34 @@ def embed_lookup(table, ids, slot_tokens=None):
     return out
 
 
-def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None):
+def _product_add_residual(pending, residual, weight, eps):
+    """The residual form of the tcgen05 product: residual += x w^T inside the product's kernel;
+    returns the ScaledRows of the new residual for the norm with ``weight``."""
+    x, w = pending.x, pending.weight
+    M, K = x.shape
+    N = w.shape[0]
+    tiles = -(-N // 128)
+    hprime = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    sumsq = torch.empty(tiles, 16, dtype=torch.float32, device=x.device)
+    lib = _gemm_tcgen05()
+    _check(lib, lib.ts_gemm_tcgen05_fused(
+        _ptr(x), _ptr(w), None, c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)), c_longlong(w.stride(0)),
+        c_longlong(N), c_int(0), c_int(pending.splits()), None, None, *_NO_SCALE, _ptr(residual), _ptr(weight),
+        c_int(_vec_flag(weight, torch.bfloat16)), _ptr(hprime), _ptr(sumsq), _stream()))
+    return ScaledRows(hprime, sumsq, tiles, eps)
+
+
+def add_rmsnorm(x, residual, weight, eps, out_dtype, rows=None, scaled_ok=False):
     """residual (float32, in place) += x; returns rmsnorm(residual) * weight as ``out_dtype``.
-    ``x`` None: no add; ``x`` may be the SplitPartials of a product.  With ``rows`` (int32) only
-    those rows are normalised and returned, and the residual is left as it is."""
+    ``x`` None: no add; ``x`` may be the SplitPartials or the PendingProduct of a product.  With
+    ``rows`` (int32) only those rows are normalised and returned, and the residual is left as it
+    is.  With ``scaled_ok`` the caller takes a ScaledRows as well (it hands it to ``linear``)."""
+    if isinstance(x, PendingProduct):
+        if (scaled_ok and rows is None and out_dtype == torch.bfloat16 and x.shape == tuple(residual.shape)
+                and residual.dtype == torch.float32 and residual.is_contiguous()):
+            _cuda(residual, weight)
+            return _product_add_residual(x, residual, weight, eps)
+        x = x.partials()
     parts = _NO_PARTIALS
     if isinstance(x, SplitPartials):
         if x.shape != tuple(residual.shape):
@@ -443,6 +535,28 @@ def attention_work(ctx, queries_per_tile, device, split_decodes=True):
     return work
 
 
+def timeline_read(reset=True):
+    """The records of a TINYSERVE_TIMELINE=1 build, from every loaded library, as a numpy structured
+    array sorted by time: ns, sm, tag (0 block started, 1 its wait for the predecessor returned,
+    2 and 3 marks of the kernel itself), grid and block indices, threads per block."""
+    import numpy as np
+    dtype = np.dtype([("ns", "<u8"), ("sm", "<i4"), ("tag", "<i4"), ("grid", "<i4", 3), ("block", "<i4", 3),
+                      ("threads", "<i4"), ("pad", "<i4")])
+    chunks = []
+    for lib in build.loaded_units():
+        if not hasattr(lib, "ts_timeline_read"):
+            continue
+        buf = np.zeros(1 << 17, dtype=dtype)
+        n = lib.ts_timeline_read(ctypes.c_void_p(buf.ctypes.data), c_int(len(buf)), c_int(1 if reset else 0))
+        if n < 0:
+            raise RuntimeError("reading the kernel timeline failed")
+        chunks.append(buf[:n])
+    if not chunks:
+        raise RuntimeError("no loaded library records a timeline: set TINYSERVE_TIMELINE=1 before the first kernel is built")
+    out = np.concatenate(chunks)
+    return out[np.argsort(out["ns"], kind="stable")]
+
+
 def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     """Key ranges for the tensor-core decode kernel: as many as fit in one wave of blocks (two
     per SM), with at least two tiles of 64 keys per range."""
@@ -457,7 +571,8 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
     n = work.num_decode
     num_splits = decode_splits(n, work.max_decode_kv, H, Hkv)
     part_o = part_ml = None
-    if num_splits > 1:
+    cluster = DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    if num_splits > 1 and not cluster:
         part_o = torch.empty(n * H * num_splits * D, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n * H * num_splits * 2, dtype=torch.float32, device=q.device)
     lib = _attention_mma(D)
@@ -465,8 +580,8 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
         _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(1), c_int(H), c_int(Hkv),
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
-        c_int(num_splits), _ptr(part_o), _ptr(part_ml), None, c_int(1), _ptr(work.dec_req), _ptr(work.dec_tok),
-        c_int(n), c_int(0), _stream()), 2 if num_splits > 1 else 1)
+        c_int(num_splits), _ptr(part_o), _ptr(part_ml), None, c_int(2 if cluster else 1), _ptr(work.dec_req),
+        _ptr(work.dec_tok), c_int(n), c_int(0), _stream()), 2 if num_splits > 1 and not cluster else 1)
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
@@ -509,10 +624,11 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         num_splits = 1
     out = torch.empty_like(q)
     part_o = part_ml = None
-    if num_splits > 1:
+    cluster = mma and decode and DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    if num_splits > 1 and not cluster:
         part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(T * H * num_splits * 2, dtype=torch.float32, device=q.device)
-    launches = 2 if num_splits > 1 else 1
+    launches = 2 if num_splits > 1 and not cluster else 1
     if mma:
         lib = _attention_mma(D)
         counters = None
@@ -534,7 +650,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
-            c_int(1 if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
+            c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
             _stream()), launches)
         return out
     lib = _attention(D)
@@ -547,24 +663,34 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     return out
 
 
-def linear(x, weight, bias=None, out_float32=False, allow_partials=False):
+def linear(x, weight, bias=None, out_float32=False, allow_partials=False, allow_pending=False):
     """x [M, K] @ weight[N, K]^T (+ bias).  float32 operands: this package's 32-bit FMA kernel
     (no tensor cores, no reduced precision).  bfloat16 operands: cuBLAS through torch.mm, or
     the FMA kernel when BF16_GEMM == "simt"; with BF16_GEMM == "tcgen05" products of up to
     TCGEN05_MAX_TOKENS rows run on this package's TMA + tcgen05 kernel.  With ``allow_partials``
     the result may be a SplitPartials (the caller hands it to add_rmsnorm, qk_norm_rope_kvwrite,
-    or calls materialize)."""
+    or calls materialize); with ``allow_pending`` a PendingProduct (for add_rmsnorm, or
+    materialize).  x may be the ScaledRows that add_rmsnorm returned."""
+    scale = None
+    if isinstance(x, ScaledRows):
+        scale, x = x, x.data
     _cuda(x, weight, bias)
     M, K = x.shape
     N = weight.shape[0]
     if weight.shape[1] != K or x.dtype != weight.dtype:
         raise ValueError(f"linear: x {tuple(x.shape)} {x.dtype} does not fit weight {tuple(weight.shape)} {weight.dtype}")
     x = materialize(x)
-    if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias):
-        if allow_partials and SPLIT_PARTIALS and not out_float32 and TCGEN05_FORM == "tiled" \
+    tiled = TCGEN05_FORM == "tiled"
+    if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias) \
+            and (scale is None or M <= FUSED_MAX_TOKENS):
+        if allow_pending and FUSED_RESIDUAL and scale is None and tiled and not out_float32 and M <= FUSED_MAX_TOKENS:
+            return PendingProduct(x, weight)
+        if (allow_partials or allow_pending) and SPLIT_PARTIALS and not out_float32 and tiled \
                 and gemm_splits(x.shape[0], weight.shape[0], x.shape[1], partials=True) > 1:
-            return _linear_tcgen05(x, weight, False, partials_only=True)
-        return _linear_tcgen05(x, weight, out_float32)
+            return _linear_tcgen05(x, weight, False, partials_only=True, scale=scale)
+        return _linear_tcgen05(x, weight, out_float32, scale=scale)
+    if scale is not None:
+        x = scale.materialize()
     if x.dtype == torch.bfloat16 and BF16_GEMM in ("cublas", "tcgen05"):
         if out_float32:
             out = torch.mm(x, weight.t(), out_dtype=torch.float32)

@@ -55,6 +55,8 @@ class Attention(Mixer):
         kind = "window" if self.window > 0 else "full"
         return CacheSpec(kind, self.num_kv_heads, self.head_dim, self.window)
 
+    accepts_scaled_rows = True
+
     def forward(self, h, ctx, call):
         qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"), allow_partials=True)
         cache = ctx.cache(call.cache)
@@ -69,7 +71,7 @@ class Attention(Mixer):
             slot_mapping=view.slot_mapping if call.writes_cache else None,
             page_size=view.page_size)
         out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window)
-        return ops.linear(out.view(out.shape[0], self.q_size), self.w["o_proj.weight"], allow_partials=True)
+        return ops.linear(out.view(out.shape[0], self.q_size), self.w["o_proj.weight"], allow_pending=True)
 
 
 register_mixer("attention", Attention)

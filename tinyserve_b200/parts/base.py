@@ -102,10 +102,16 @@ class Norm(Part):
     def forward(self, x, out=None):
         raise NotImplementedError
 
+    #: add_forward takes ``scaled_ok`` (see there); a norm without it is never asked for it
+    supports_scaled_rows = False
+
     def add_forward(self, x, residual, rows=None):
         """residual += x (x may be None), return norm(residual) in the compute dtype.  x is what
-        a mixer or feed-forward returned: a tensor, or a ``kernels.ops.SplitPartials`` (pass it to
-        ops.add_rmsnorm as it is, or turn it into a tensor with ops.materialize)."""
+        a mixer or feed-forward returned: a tensor, or a ``kernels.ops.SplitPartials`` or
+        ``PendingProduct`` (pass it to ops.add_rmsnorm as it is, or turn it into a tensor with
+        ops.materialize).  A norm with ``supports_scaled_rows`` also takes ``scaled_ok``: when the
+        block sets it, the part that reads the result hands it to ops.linear only, and the norm may
+        return a ``kernels.ops.ScaledRows`` in place of a tensor."""
         raise NotImplementedError
 
 
@@ -115,6 +121,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     tree_name = "mixer"
+    #: forward hands h to ops.linear only (never reads it itself), so h may be a ScaledRows
+    accepts_scaled_rows = False
 
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
@@ -132,6 +140,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     tree_name = "mlp"
+    accepts_scaled_rows = False       # as for a Mixer
 
     def forward(self, h, ctx):
         raise NotImplementedError

@@ -26,9 +26,16 @@ class PreNormBlock(Part):
     def forward(self, x, residual, ctx, call):
         """(x, residual) -> x of the next block; ``residual`` (32-bit) is updated in place.
         x is None for the first block: the residual then already holds the embeddings."""
-        h = self.input_norm.add_forward(x, residual)
-        h = self.post_mixer_norm.add_forward(self.mixer.forward(h, ctx, call), residual)
+        h = self._norm(self.input_norm, x, residual, self.mixer)
+        h = self._norm(self.post_mixer_norm, self.mixer.forward(h, ctx, call), residual, self.ffn)
         return self.ffn.forward(h, ctx)
+
+    @staticmethod
+    def _norm(norm, x, residual, reader):
+        # a reader that only multiplies h by a matrix may get rows without their norm factor
+        if norm.supports_scaled_rows and reader.accepts_scaled_rows:
+            return norm.add_forward(x, residual, scaled_ok=True)
+        return norm.add_forward(x, residual)
 
 
 ARRANGEMENTS = {"pre_norm": PreNormBlock}

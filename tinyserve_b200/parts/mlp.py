@@ -24,10 +24,12 @@ class GatedMLP(FeedForward):
             "down_proj.weight": ParamSpec((self.hidden_size, i)),
         }
 
+    accepts_scaled_rows = True
+
     def forward(self, h, ctx):
         gate_up = ops.linear(h, self.w["gate_up_proj.weight"])
         act = ops.gated_activation(gate_up, self.activation)
-        return ops.linear(act, self.w["down_proj.weight"], allow_partials=True)
+        return ops.linear(act, self.w["down_proj.weight"], allow_pending=True)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

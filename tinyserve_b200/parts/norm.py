@@ -24,8 +24,11 @@ class RMSNorm(Norm):
     def forward(self, x, out=None):
         return ops.rmsnorm(x, self.w["weight"], self.eps, out=out)
 
-    def add_forward(self, x, residual, rows=None):
-        return ops.add_rmsnorm(x, residual, self.w["weight"], self.eps, self.compute_dtype, rows=rows)
+    supports_scaled_rows = True
+
+    def add_forward(self, x, residual, rows=None, scaled_ok=False):
+        return ops.add_rmsnorm(x, residual, self.w["weight"], self.eps, self.compute_dtype, rows=rows,
+                               scaled_ok=scaled_ok)
 
 
 register_norm("rmsnorm", RMSNorm)
