@@ -98,12 +98,15 @@ def _rope_ref(x, pos, cos, sin, R, interleaved):
 @pytest.mark.parametrize("H,Hkv,D,R,inter,norm,page", [
     (6, 3, 48, 48, False, True, 8), (8, 2, 128, 128, False, True, 16), (5, 5, 16, 16, False, False, 4),
     (4, 1, 80, 32, False, True, 16), (3, 3, 64, 64, True, True, 8), (2, 2, 96, 0, False, True, 16),
+    (5, 2, 64, 64, False, True, 16), (3, 1, 256, 256, False, False, 8),
 ])
-def test_qk_norm_rope_kvwrite(dtype, H, Hkv, D, R, inter, norm, page):
+@pytest.mark.parametrize("T", [11, 300])        # few tokens: a warp per head; many: a block per token
+def test_qk_norm_rope_kvwrite(dtype, H, Hkv, D, R, inter, norm, page, T):
     from tinyserve_b200.parts.rotary import Rotary
-    T, pages, eps = 11, 6, 1e-5
+    pages, eps = -(-T // page) + 5, 1e-5
     qkv = rnd(T, (H + 2 * Hkv) * D, seed=7, dtype=dtype)
-    pos = torch.tensor([0, 1, 2, 30, 31, 32, 5, 6, 7, 63, 9], dtype=torch.int32).cuda()
+    pos = (torch.tensor([0, 1, 2, 30, 31, 32, 5, 6, 7, 63, 9] * (T // 11 + 1))[:T] +
+           torch.arange(T) // 11 % 2).clamp(max=63).int().cuda()
     slots = torch.randperm(pages * page, generator=torch.Generator().manual_seed(3))[:T].int().cuda()
     slots[5] = -1                       # this token writes nothing
     rot = None

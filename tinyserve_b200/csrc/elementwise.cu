@@ -107,20 +107,27 @@ template <> struct Quad<__nv_bfloat16> {
   }
 };
 
-template <typename T, int ITEMS>
-__global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
+// MAX_THREADS / MIN_BLOCKS bound the registers: with many rows (prefill) the kernel lives on the
+// number of rows in flight per SM, and four element groups per thread would otherwise leave room
+// for two blocks only.
+template <typename T, int ITEMS, int MAX_THREADS = 1024, int MIN_BLOCKS = 1>
+__global__ void __launch_bounds__(MAX_THREADS, MIN_BLOCKS) add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restrict__ residual, VecParam w,
                                        float eps, T* __restrict__ out, const int* __restrict__ rows,
                                        int n, int write_residual, PartialSrc ps) {
   __shared__ float scratch[33];
   pdl_trigger();
-  // the weights are constants: fetch them while the predecessor still runs
-  float wv[ITEMS][4];
+  // the weights are constants: fetch them while the predecessor still runs (few rows: the
+  // shortest chain), or where they are used (many rows: fewer registers, more rows in flight)
+  constexpr bool PRELOAD = MIN_BLOCKS == 1;
+  float wv[PRELOAD ? ITEMS : 1][4];
+  if (PRELOAD) {
 #pragma unroll
-  for (int it = 0; it < ITEMS; ++it) {
-    const int c = (threadIdx.x + it * blockDim.x) * 4;
-    if (c < n) {
-      if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv[it]);
-      else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv[it]);
+    for (int it = 0; it < ITEMS; ++it) {
+      const int c = (threadIdx.x + it * blockDim.x) * 4;
+      if (c < n) {
+        if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv[it]);
+        else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv[it]);
+      }
     }
   }
   pdl_wait();
@@ -150,9 +157,13 @@ __global__ void add_rmsnorm_vec_kernel(const T* __restrict__ x, float* __restric
     const int c = (threadIdx.x + it * blockDim.x) * 4;
     if (c < n) {
       if (write_residual) Quad<float>::store(residual + r * n + c, v[it]);
+      if (!PRELOAD) {
+        if (w.is_f32) Quad<float>::load(static_cast<const float*>(w.ptr) + c, wv[0]);
+        else Quad<__nv_bfloat16>::load(static_cast<const __nv_bfloat16*>(w.ptr) + c, wv[0]);
+      }
       float o[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = v[it][e] * rstd * wv[it][e];
+      for (int e = 0; e < 4; ++e) o[e] = v[it][e] * rstd * wv[PRELOAD ? it : 0][e];
       Quad<T>::store(out + (size_t)i * n + c, o);
     }
   }
@@ -255,6 +266,7 @@ int launch_add_rmsnorm(const void* x, float* residual, VecParam w, float eps, vo
     int threads = ((quads + items - 1) / items + 31) / 32 * 32;
     if (items == 1) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 1>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
     else if (items == 2) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 2>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
+    else if (threads <= 256) TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4, 256, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
     else TS_LAUNCH("add_rmsnorm", (add_rmsnorm_vec_kernel<T, 4>), num_out_rows, threads, 0, stream, xp, residual, w, eps, op, rows, n, write_residual, ps);
     return 0;
   }
@@ -685,6 +697,181 @@ __global__ void qk_norm_rope_kvwrite_vec_kernel(const T* __restrict__ qkv, T* __
   }
 }
 
+// Many tokens (prefill): a block per token whose warps walk the token's heads, ROPE_UNROLL heads
+// at a time, so that each warp has that many heads' loads in flight; the token's angles and the
+// norms' weights are fetched once per lane, not once per head.
+constexpr int ROPE_UNROLL = 3;
+
+template <typename T, int STEPS>
+__global__ void qk_norm_rope_kvwrite_rows_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                                 const int* __restrict__ positions, RopeArgs rope,
+                                                 VecParam qw, VecParam kw, int has_norm, float eps,
+                                                 int H, int Hkv, int D, T* __restrict__ k_cache,
+                                                 T* __restrict__ v_cache,
+                                                 const int* __restrict__ slot_mapping, int page_size,
+                                                 int heads_total) {
+  pdl_trigger();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, half = D >> 1;
+  const int pos = positions[t];
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  float2 c[STEPS], sn[STEPS], wqa[STEPS], wqb[STEPS], wka[STEPS], wkb[STEPS];
+#pragma unroll
+  for (int s = 0; s < STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < half) {
+      c[s] = *reinterpret_cast<const float2*>(rope.cos + (size_t)pos * half + j);
+      sn[s] = *reinterpret_cast<const float2*>(rope.sin + (size_t)pos * half + j);
+      wqa[s] = has_norm ? make_float2(qw[j], qw[j + 1]) : make_float2(1.f, 1.f);
+      wqb[s] = has_norm ? make_float2(qw[half + j], qw[half + j + 1]) : make_float2(1.f, 1.f);
+      wka[s] = has_norm ? make_float2(kw[j], kw[j + 1]) : make_float2(1.f, 1.f);
+      wkb[s] = has_norm ? make_float2(kw[half + j], kw[half + j + 1]) : make_float2(1.f, 1.f);
+    }
+  }
+  pdl_wait();
+  const size_t page = slot >= 0 ? slot / page_size : 0, in_page = slot >= 0 ? slot % page_size : 0;
+  const T* row = qkv + (size_t)t * (H + 2 * Hkv) * D;
+  for (int h0 = warp; h0 < heads_total; h0 += warps * ROPE_UNROLL) {
+    float2 a[ROPE_UNROLL][STEPS], b[ROPE_UNROLL][STEPS];
+#pragma unroll
+    for (int u = 0; u < ROPE_UNROLL; ++u) {
+      const int head = h0 + u * warps;
+      if (head < heads_total) {
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (j < half) {
+            a[u][s] = Duo<T>::load(row + (size_t)head * D + j);
+            b[u][s] = Duo<T>::load(row + (size_t)head * D + half + j);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < ROPE_UNROLL; ++u) {
+      const int head = h0 + u * warps;
+      if (head >= heads_total) break;
+      const bool is_q = head < H, is_v = head >= H + Hkv;
+      if (!is_q && slot < 0) continue;
+      const int kvh = is_q ? 0 : (is_v ? head - H - Hkv : head - H);
+      T* dst = is_q ? q_out + ((size_t)t * H + head) * D
+                    : (is_v ? v_cache : k_cache) + ((page * Hkv + kvh) * page_size + in_page) * D;
+      if (is_v) {
+#pragma unroll
+        for (int s = 0; s < STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (j < half) {
+            Duo<T>::store(dst + j, a[u][s].x, a[u][s].y);
+            Duo<T>::store(dst + half + j, b[u][s].x, b[u][s].y);
+          }
+        }
+        continue;
+      }
+      float acc = 0.f;
+#pragma unroll
+      for (int s = 0; s < STEPS; ++s) {
+        const int j = 2 * (lane + 32 * s);
+        if (j < half) acc += a[u][s].x * a[u][s].x + a[u][s].y * a[u][s].y + b[u][s].x * b[u][s].x + b[u][s].y * b[u][s].y;
+      }
+      const float rstd = has_norm ? rsqrtf(warp_sum(acc) / (float)D + eps) : 1.f;
+#pragma unroll
+      for (int s = 0; s < STEPS; ++s) {
+        const int j = 2 * (lane + 32 * s);
+        if (j < half) {
+          const float2 wa = is_q ? wqa[s] : wka[s], wb = is_q ? wqb[s] : wkb[s];
+          float a0 = a[u][s].x, a1 = a[u][s].y, b0 = b[u][s].x, b1 = b[u][s].y;
+          if (has_norm) {
+            a0 *= rstd * wa.x; a1 *= rstd * wa.y;
+            b0 *= rstd * wb.x; b1 *= rstd * wb.y;
+          }
+          Duo<T>::store(dst + j, a0 * c[s].x - b0 * sn[s].x, a1 * c[s].y - b1 * sn[s].y);
+          Duo<T>::store(dst + half + j, b0 * c[s].x + a0 * sn[s].x, b1 * c[s].y + a1 * sn[s].y);
+        }
+      }
+    }
+  }
+}
+
+// The same for head sizes 64, 128 and 256, with four neighbouring elements of each half per lane
+// (8- or 16-byte accesses): LPH = D / 8 lanes share a head, a warp works on 32 / LPH heads at once.
+template <typename T, int LPH>
+__global__ void qk_norm_rope_kvwrite_rows4_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                                  const int* __restrict__ positions, RopeArgs rope,
+                                                  VecParam qw, VecParam kw, int has_norm, float eps,
+                                                  int H, int Hkv, T* __restrict__ k_cache,
+                                                  T* __restrict__ v_cache,
+                                                  const int* __restrict__ slot_mapping, int page_size,
+                                                  int heads_total) {
+  constexpr int D = LPH * 8, HALF = D / 2, HPW = 32 / LPH, U = 2;
+  pdl_trigger();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPH, j = 4 * (lane % LPH);
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  float c[4], sn[4], wqa[4], wqb[4], wka[4], wkb[4];
+  Quad<float>::load(rope.cos + (size_t)pos * HALF + j, c);
+  Quad<float>::load(rope.sin + (size_t)pos * HALF + j, sn);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    wqa[e] = has_norm ? qw[j + e] : 1.f;
+    wqb[e] = has_norm ? qw[HALF + j + e] : 1.f;
+    wka[e] = has_norm ? kw[j + e] : 1.f;
+    wkb[e] = has_norm ? kw[HALF + j + e] : 1.f;
+  }
+  pdl_wait();
+  const size_t page = slot >= 0 ? slot / page_size : 0, in_page = slot >= 0 ? slot % page_size : 0;
+  const T* row = qkv + (size_t)t * (H + 2 * Hkv) * D;
+  for (int base = warp * HPW; base < heads_total; base += warps * HPW * U) {
+    float a[U][4], b[U][4];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int head = base + sub + u * warps * HPW;
+      if (head < heads_total) {
+        Quad<T>::load(row + (size_t)head * D + j, a[u]);
+        Quad<T>::load(row + (size_t)head * D + HALF + j, b[u]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) a[u][e] = b[u][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int head = base + sub + u * warps * HPW;
+      float acc = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc += a[u][e] * a[u][e] + b[u][e] * b[u][e];
+#pragma unroll
+      for (int o = LPH / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (head >= heads_total) continue;
+      const bool is_q = head < H, is_v = head >= H + Hkv;
+      if (!is_q && slot < 0) continue;
+      const int kvh = is_q ? 0 : (is_v ? head - H - Hkv : head - H);
+      T* dst = is_q ? q_out + ((size_t)t * H + head) * D
+                    : (is_v ? v_cache : k_cache) + ((page * Hkv + kvh) * page_size + in_page) * D;
+      float oa[4], ob[4];
+      if (is_v) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { oa[e] = a[u][e]; ob[e] = b[u][e]; }
+      } else {
+        const float rstd = has_norm ? rsqrtf(acc / (float)D + eps) : 1.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float x0 = a[u][e], x1 = b[u][e];
+          if (has_norm) {
+            x0 *= rstd * (is_q ? wqa[e] : wka[e]);
+            x1 *= rstd * (is_q ? wqb[e] : wkb[e]);
+          }
+          oa[e] = x0 * c[e] - x1 * sn[e];
+          ob[e] = x1 * c[e] + x0 * sn[e];
+        }
+      }
+      Quad<T>::store(dst + j, oa);
+      Quad<T>::store(dst + HALF + j, ob);
+    }
+  }
+}
+
 TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, const int* positions,
                                       const float* cos, const float* sin, int rotary_dim,
                                       int interleaved, const void* q_weight, const void* k_weight,
@@ -718,6 +905,37 @@ TS_EXPORT int ts_qk_norm_rope_kvwrite(int dtype, const void* qkv, void* q_out, c
   TS_LAUNCH("qk_norm_rope_kvwrite", (qk_norm_rope_kvwrite_vec_kernel<T, STEPS>), grid, warps * 32, 0, stream, \
             (const T*)qkv, (T*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D, (T*)k_cache,  \
             (T*)v_cache, slot_mapping, page_size, heads_total, ps)
+#define TS_ROPE_ROWS(T, STEPS)                                                                         \
+  TS_LAUNCH("qk_norm_rope_kvwrite", (qk_norm_rope_kvwrite_rows_kernel<T, STEPS>), dim3(num_tokens), warps * 32, 0, \
+            stream, (const T*)qkv, (T*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, D, (T*)k_cache, \
+            (T*)v_cache, slot_mapping, page_size, heads_total)
+#define TS_ROPE_ROWS4(T, LPH)                                                                         \
+  TS_LAUNCH("qk_norm_rope_kvwrite", (qk_norm_rope_kvwrite_rows4_kernel<T, LPH>), dim3(num_tokens), warps * 32, 0, \
+            stream, (const T*)qkv, (T*)q_out, positions, rope, qw, kw, has_norm, eps, H, Hkv, (T*)k_cache,  \
+            (T*)v_cache, slot_mapping, page_size, heads_total)
+  const bool aligned16 = (reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) |
+                          reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache) |
+                          reinterpret_cast<uintptr_t>(cos) | reinterpret_cast<uintptr_t>(sin)) % 16 == 0;
+  if (vec && aligned16 && num_tokens >= 256 && partials == nullptr && (D == 64 || D == 128 || D == 256) &&
+      (dtype == TS_F32 || dtype == TS_BF16)) {
+    if (dtype == TS_F32) {
+      if (D == 64) TS_ROPE_ROWS4(float, 8); else if (D == 128) TS_ROPE_ROWS4(float, 16); else TS_ROPE_ROWS4(float, 32);
+    } else {
+      if (D == 64) TS_ROPE_ROWS4(__nv_bfloat16, 8); else if (D == 128) TS_ROPE_ROWS4(__nv_bfloat16, 16); else TS_ROPE_ROWS4(__nv_bfloat16, 32);
+    }
+    return 0;
+  }
+#undef TS_ROPE_ROWS4
+  if (vec && num_tokens >= 256 && partials == nullptr && D <= 256 && (dtype == TS_F32 || dtype == TS_BF16)) {
+    const int steps = (D / 4 + 31) / 32;
+    if (dtype == TS_F32) {
+      if (steps <= 1) TS_ROPE_ROWS(float, 1); else TS_ROPE_ROWS(float, 2);
+    } else {
+      if (steps <= 1) TS_ROPE_ROWS(__nv_bfloat16, 1); else TS_ROPE_ROWS(__nv_bfloat16, 2);
+    }
+    return 0;
+  }
+#undef TS_ROPE_ROWS
   if (vec && (dtype == TS_F32 || dtype == TS_BF16)) {
     const int steps = (D / 4 + 31) / 32;        // pairs of pairs per lane
     if (dtype == TS_F32) {

@@ -3,6 +3,7 @@
     python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|tcgen05_tiled|tcgen05_persistent|cublas]
     python -m tinyserve_b200.kernels.microbench attention --batch 8 --q-len 1 --kv-len 640
     python -m tinyserve_b200.kernels.microbench norm --rows 8 --n 4096
+    python -m tinyserve_b200.kernels.microbench rope --rows 2048
 
 Every iteration uses another copy of the operands (``--copies``, sized so that together they
 exceed the 126 MB L2), so the bytes really come from HBM.  ``--graph`` replays the loop from a
@@ -79,7 +80,9 @@ def bench_attention(a):
     q = torch.randn(B * q_len, H, D, device="cuda", dtype=torch.bfloat16)
     cu = torch.arange(0, B * q_len + 1, q_len, dtype=torch.int32).cuda()
     kv = torch.full((B,), kv_len, dtype=torch.int32).cuda()
-    ctx = SimpleNamespace(cu_q=cu, kv_lens=kv, num_requests=B, max_q_len=q_len, max_kv_len=kv_len)
+    # as the engine's step context: the lengths on the host too, and the work lists built once
+    ctx = SimpleNamespace(cu_q=cu, kv_lens=kv, num_requests=B, max_q_len=q_len, max_kv_len=kv_len,
+                          host={"cu_q": cu.tolist(), "kv_lens": kv.tolist()}, tile_cache={})
     views = [SimpleNamespace(block_table=t, page_size=page) for t in tables]
     fn = lambda i: ops.paged_attention(q, kc, vc, views[i], ctx, D ** -0.5, 0, num_splits=a.splits or None)
     us = _time(fn, copies, a.iters, a.graph)
@@ -101,9 +104,30 @@ def bench_norm(a):
             "gbs": round(a.rows * a.n * 12 / us / 1e3, 1)}
 
 
+def bench_rope(a):
+    from ..parts.rotary import Rotary
+    H, Hkv, D, page, T = a.heads, a.kv_heads, a.head_dim, a.page, a.rows
+    copies = a.copies or 4
+    qkvs = [torch.randn(T, (H + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    pages = -(-T // page) + 1
+    caches = [(torch.zeros(pages, Hkv, page, D, device="cuda", dtype=torch.bfloat16),
+               torch.zeros(pages, Hkv, page, D, device="cuda", dtype=torch.bfloat16)) for _ in range(copies)]
+    rot = Rotary(D, 1e6, "half")
+    rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(D, 1e6, max(T, 16)))
+    pos = torch.arange(T, dtype=torch.int32).cuda()
+    slots = torch.arange(page, page + T, dtype=torch.int32).cuda()
+    qw = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    fn = lambda i: ops.qk_norm_rope_kvwrite(qkvs[i], pos, H, Hkv, D, rotary=rot, q_weight=qw, k_weight=qw, eps=1e-6,
+                                            k_cache=caches[i][0], v_cache=caches[i][1], slot_mapping=slots,
+                                            page_size=page)
+    us = _time(fn, copies, a.iters, a.graph)
+    return {"kernel": "qk_norm_rope_kvwrite", "rows": T, "heads": H, "kv_heads": Hkv, "head_dim": D,
+            "us": round(us, 2), "gbs": round(T * (H + 2 * Hkv) * D * 4 / us / 1e3, 1)}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m tinyserve_b200.kernels.microbench")
-    ap.add_argument("kernel", choices=["gemm", "attention", "norm"])
+    ap.add_argument("kernel", choices=["gemm", "attention", "norm", "rope"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
@@ -125,7 +149,7 @@ def main(argv=None):
                     help="gemm: stop after the split-K partial tiles (a consumer kernel adds them up)")
     a = ap.parse_args(argv)
     ops.require_device("cuda:0")
-    out = {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm}[a.kernel](a)
+    out = {"gemm": bench_gemm, "attention": bench_attention, "norm": bench_norm, "rope": bench_rope}[a.kernel](a)
     out["graph"] = a.graph
     print(json.dumps(out))
 
