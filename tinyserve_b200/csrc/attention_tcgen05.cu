@@ -1,18 +1,27 @@
 // Paged, variable-length, causal grouped-query attention for prefill on the 5th-generation tensor
 // cores, bfloat16, head size 64 or 128 (-DTS_HEAD_DIM).
 //
-// A block of 192 threads handles 128 rows = (query, head of one KV group) pairs of one request and
-// walks its visible keys in tiles of 128:
-//   warp 0   loads: the query tile once (3-D TMA over [token, head, dim]), then per key tile the K
+// A block of 320 threads handles two tiles of 128 rows = (query, head of one KV group) pairs of one
+// request, tile 1 the queries right after tile 0's, and walks their visible keys in tiles of 128.
+// Both query tiles use the same keys and values, and one tile's softmax runs while the tensor core
+// works for the other:
+//   warp 0   loads: the query tiles once (3-D TMA over [token, head, dim]), then per key tile the K
 //            and V pages of the request's block table (2-D TMA boxes of one page x 64 columns,
-//            128-byte swizzle) into a ring of two stages;
-//   warp 1   issues tcgen05.mma: S = Q K^T into tensor memory, and, once the probabilities are in
-//            shared memory, O += P V (V as an N-contiguous operand) into tensor memory;
-//   warps 2-5 one thread per row: read the row of S from tensor memory, mask (key j is visible to
-//            the query at position p iff j <= p and, with a window W > 0, j > p - W: serve.py:668-680),
-//            online softmax in 32-bit with exp2 (tinykernels.py:386-413, 993), write P as bfloat16
-//            into swizzled shared memory, rescale the row of O when its maximum moved; at the end
-//            divide O by the row sum and store it.
+//            128-byte swizzle), keys and values in rings of two stages each, the keys one tile
+//            ahead of the values;
+//   warp 1   issues tcgen05.mma: S_g = Q_g K^T into tensor memory, and O_g += P_g V (P_g read from
+//            tensor memory, V as an N-contiguous operand) once the probabilities are there; the
+//            scores of tile g's next key tile follow its P V at once (the tensor pipe runs in order).
+//            One thread issues for both query tiles: that keeps the two tiles half a period apart
+//            (with an issuing thread per tile they fell into step and ran 8 % slower);
+//   warps 2-5 (tile 0) and 6-9 (tile 1), one thread per row: read the row of S from tensor memory,
+//            mask (key j is visible to the query at position p iff j <= p and, with a window
+//            W > 0, j > p - W: serve.py:668-680), online softmax in 32-bit with exp2
+//            (tinykernels.py:386-413, 993), write P as bfloat16 over the first columns of S_g,
+//            rescale the row of O when its maximum moved; at the end divide O by the row sum and
+//            store it.
+// Tensor memory: all 512 columns (S_0 / P_0, S_1 / P_1, O_0, O_1), taken before the dependent
+// kernel may start, so that no block of a successor can sit on columns that this kernel still needs.
 // Row maxima and sums never leave their thread, so there are no shuffles.  Every mbarrier wait is
 // bounded (tcgen05.cuh); a block that gives up raises ts_attention_tcgen05_error.
 #include "tcgen05.cuh"
@@ -28,17 +37,18 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int D = TS_HEAD_DIM;
 static_assert(D == 64 || D == 128, "the tcgen05 prefill kernel takes head sizes 64 and 128");
-constexpr int BM = 128;                      // rows of a block
+constexpr int BM = 128;                      // rows of a query tile
 constexpr int BN = 128;                      // keys of a tile
-constexpr int THREADS = 192;
-constexpr int STAGES = 2;
+constexpr int GROUPS = 2;                    // query tiles of a block
+constexpr int THREADS = 64 + GROUPS * 128;
+constexpr int K_STAGES = 2;
+constexpr int V_STAGES = 2;
 constexpr int DCH = D / 64;                  // 64-column chunks of a head
 constexpr int CHUNK_BYTES = 128 * 128;       // 128 rows of 128 bytes
 constexpr int Q_BYTES = DCH * CHUNK_BYTES;
 constexpr int KV_BYTES = DCH * CHUNK_BYTES;  // one of K or V of a tile
-constexpr int P_BYTES = (BN / 64) * CHUNK_BYTES;
-constexpr int TMEM_COLS = 256;               // S: columns 0..127, O: 128..128+D
-constexpr size_t SMEM = 1024 + Q_BYTES + 2 * STAGES * KV_BYTES + P_BYTES + 256;
+constexpr int TMEM_COLS = 512;               // S_0, S_1: 128 columns each (P_g over the first 64 of S_g); O_0 at 256, O_1 at 384
+constexpr size_t SMEM = 1024 + GROUPS * Q_BYTES + (K_STAGES + V_STAGES) * KV_BYTES + 256;
 
 struct TcAttnParams {
   bf16* out;                // [T, H, D]
@@ -48,7 +58,7 @@ struct TcAttnParams {
   const int* tile_req;      // optional work list: request and first query of every block
   const int* tile_q0;
   int H, Hkv, page_shift, page_size, max_blocks;
-  int heads_per_tile, queries_per_tile, head_tiles;
+  int heads_per_tile, queries_per_tile, head_tiles;     // of one query tile
   int window;
   float scale_log2;
 };
@@ -63,58 +73,43 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// (10 warps take the registers of 12, three per scheduler: 168 registers a thread)
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
   extern __shared__ char smem_raw[];
   char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  char* Qs = smem;
-  char* Ks = Qs + Q_BYTES;                       // [STAGES][KV_BYTES]
-  char* Vs = Ks + STAGES * KV_BYTES;             // [STAGES][KV_BYTES]
-  char* Ps = Vs + STAGES * KV_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(Ps + P_BYTES);
+  char* Qs = smem;                               // [GROUPS][Q_BYTES]
+  char* Ks = Qs + GROUPS * Q_BYTES;              // [K_STAGES][KV_BYTES]
+  char* Vs = Ks + K_STAGES * KV_BYTES;           // [V_STAGES][KV_BYTES]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Vs + V_STAGES * KV_BYTES);
   uint64_t* q_full = bars;                       // 1
-  uint64_t* kv_full = bars + 1;                  // [STAGES]
-  uint64_t* kv_empty = kv_full + STAGES;         // [STAGES]
-  uint64_t* s_full = kv_empty + STAGES;          // S holds the scores of a tile
-  uint64_t* s_free = s_full + 1;                 // the softmax threads have read S
-  uint64_t* p_full = s_free + 1;                 // P is in shared memory, O is rescaled
-  uint64_t* o_ready = p_full + 1;                // O holds the sum over the tiles so far
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + 1);
+  uint64_t* k_full = q_full + 1;                 // [K_STAGES]
+  uint64_t* k_empty = k_full + K_STAGES;         // [K_STAGES] both tiles' scores of the stage's keys are computed
+  uint64_t* v_full = k_empty + K_STAGES;         // [V_STAGES]
+  uint64_t* v_empty = v_full + V_STAGES;         // [V_STAGES] the stage's values are added to both O
+  uint64_t* s_full = v_empty + V_STAGES;         // [GROUPS] S_g holds the scores of a key tile
+  uint64_t* p_full = s_full + GROUPS;            // [GROUPS] P_g is in tensor memory, O_g is rescaled
+  uint64_t* o_ready = p_full + GROUPS;           // [GROUPS] O_g holds the sum over the key tiles so far
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + GROUPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  pdl_trigger();
-  pdl_wait();
-  // with a work list block x handles tile x; else blocks (tile, request) cover max_q_len and exit
-  // where a request has fewer queries
-  const int b = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.z;
-  const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
-  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
-  const int q0 = p.tile_req ? p.tile_q0[blockIdx.x]
-                            : (gridDim.x - 1 - blockIdx.x) * p.queries_per_tile;     // heavy blocks first
-  if (q0 >= q_len) return;
-  const int kv_len = p.kv_lens[b];
-  const int G = p.H / p.Hkv, GT = p.heads_per_tile, QPT = p.queries_per_tile;
-  const int g0 = head_tile * GT;
-  const int nq = min(QPT, q_len - q0);
-  const int n_valid = QPT > 1 ? nq * GT : min(GT, G - g0);
-  const int pos0 = kv_len - q_len + q0;
-  const int j_hi = min(kv_len, pos0 + nq);
-  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
-  const int n_tiles = end_tile - first_tile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&kv_full[s]), 1);
-      mbar_init(smem_u32(&kv_empty[s]), 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), 1);
     }
-    mbar_init(smem_u32(s_full), 1);
-    mbar_init(smem_u32(s_free), 4);
-    mbar_init(smem_u32(p_full), 4);
-    mbar_init(smem_u32(o_ready), 1);
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), 1);
+    }
+    for (int g = 0; g < GROUPS; ++g) {
+      mbar_init(smem_u32(&s_full[g]), 1);
+      mbar_init(smem_u32(&p_full[g]), 4);
+      mbar_init(smem_u32(&o_ready[g]), 1);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -126,138 +121,199 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
-  const uint32_t tmem_s = *tmem_slot, tmem_o = tmem_s + BN;
+  const uint32_t tmem_base = *tmem_slot;
+  // this block holds all of the SM's tensor memory now: only now may a dependent kernel start
+  pdl_trigger();
+  pdl_wait();
+
+  // with a work list block x handles entry x; else blocks (tile pair, request) cover max_q_len and
+  // exit where a request has fewer queries
+  const int QPT = p.queries_per_tile, GT = p.heads_per_tile;
+  const int b = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.z;
+  const int kvh = blockIdx.y / p.head_tiles, head_tile = blockIdx.y % p.head_tiles;
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int q0 = p.tile_req ? p.tile_q0[blockIdx.x]
+                            : (gridDim.x - 1 - blockIdx.x) * GROUPS * QPT;     // heavy blocks first
+  const int kv_len = p.kv_lens[b];
+  const int G = p.H / p.Hkv;
+  const int g0 = head_tile * GT;
+  const int nq_all = max(0, min(GROUPS * QPT, q_len - q0));
+  const int groups = nq_all > QPT ? 2 : 1;       // query tiles of this block that hold queries
+  const int pos0 = kv_len - q_len + q0;
+  const int j_hi = min(kv_len, pos0 + nq_all);
+  const int j_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+  const int first_tile = j_lo / BN, end_tile = (j_hi + BN - 1) / BN;
+  const int n_tiles = nq_all > 0 ? end_tile - first_tile : 0;
+  // the timeline build follows one block through its tiles (marks 10.. by the issuer, 20.. by a
+  // softmax thread of each query tile, 30 by the loader; the value is the key tile)
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (warp == 0) {
-    if (lane == 0) {
-      // queries: rows (query, head) with the head fastest; one box per 64 columns
+    if (lane == 0 && n_tiles > 0) {
+      // queries: rows (query, head) with the head fastest; one box per 64 columns and query tile
       const uint32_t qbar = smem_u32(q_full);
-      mbar_expect_tx(qbar, DCH * 64 * 2 * GT * QPT);
-      for (int c = 0; c < DCH; ++c)
-        tma_load_3d(smem_u32(Qs + c * CHUNK_BYTES), &map_q, qbar, c * 64, kvh * G + g0, q_begin + q0);
+      mbar_expect_tx(qbar, groups * DCH * 64 * 2 * GT * QPT);
+      for (int g = 0; g < groups; ++g)
+        for (int c = 0; c < DCH; ++c)
+          tma_load_3d(smem_u32(Qs + g * Q_BYTES + c * CHUNK_BYTES), &map_q, qbar, c * 64, kvh * G + g0,
+                      q_begin + q0 + g * QPT);
       const int* bt = p.block_table + (size_t)b * p.max_blocks;
       const int pages_per_tile = BN >> p.page_shift;
-      for (int t = 0; t < n_tiles; ++t) {
-        const int s = t % STAGES;
-        if (!mbar_wait(smem_u32(&kv_empty[s]), ((t / STAGES) & 1) ^ 1, abort_flag)) break;
-        const uint32_t bar = smem_u32(&kv_full[s]);
-        mbar_expect_tx(bar, 2 * KV_BYTES);
+      // Keys and values have rings of their own, and the keys run one tile ahead: a stage of keys
+      // is free as soon as both tiles' scores are computed, long before its values have been used.
+      // The pages of a tile are looked up in one go (independent loads), before the wait.
+      auto load = [&](bool keys, int t) -> bool {
+        const int stages = keys ? K_STAGES : V_STAGES, s = t % stages;
         const int j0 = (first_tile + t) * BN;
-        for (int pg = 0; pg < pages_per_tile; ++pg) {
+        int pages[16];
+#pragma unroll
+        for (int pg = 0; pg < 16; ++pg) {
           const int j = j0 + (pg << p.page_shift);
-          const int page = j < j_hi ? bt[j >> p.page_shift] : 0;          // past the end: the null page
-          const int row = (page * p.Hkv + kvh) << p.page_shift;
-          for (int c = 0; c < DCH; ++c) {
-            const int off = s * KV_BYTES + c * CHUNK_BYTES + (pg << p.page_shift) * 128;
-            tma_load_2d(smem_u32(Ks + off), &map_k, bar, c * 64, row);
-            tma_load_2d(smem_u32(Vs + off), &map_v, bar, c * 64, row);
+          pages[pg] = pg < pages_per_tile && j < j_hi ? bt[j >> p.page_shift] : 0;   // past the end: the null page
+        }
+        if (!mbar_wait(smem_u32(keys ? &k_empty[s] : &v_empty[s]), ((t / stages) & 1) ^ 1, abort_flag)) return false;
+        const uint32_t bar = smem_u32(keys ? &k_full[s] : &v_full[s]);
+        mbar_expect_tx(bar, KV_BYTES);
+#pragma unroll
+        for (int pg = 0; pg < 16; ++pg) {
+          if (pg < pages_per_tile) {
+            const int row = (pages[pg] * p.Hkv + kvh) << p.page_shift;
+            for (int c = 0; c < DCH; ++c) {
+              const int off = s * KV_BYTES + c * CHUNK_BYTES + (pg << p.page_shift) * 128;
+              if (keys) tma_load_2d(smem_u32(Ks + off), &map_k, bar, c * 64, row);
+              else tma_load_2d(smem_u32(Vs + off), &map_v, bar, c * 64, row);
+            }
           }
         }
+        return true;
+      };
+      bool ok = load(true, 0);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) ok = load(true, t + 1);
+        if (ok) ok = load(false, t);
+        if (traced) timeline_mark_thread(30, t);
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
       constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
-      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
-      for (int t = 0; ok && t < n_tiles; ++t) {
-        const int s = t % STAGES;
-        ok = mbar_wait(smem_u32(&kv_full[s]), (t / STAGES) & 1, abort_flag) &&
-             mbar_wait(smem_u32(s_free), (t & 1) ^ 1, abort_flag);
-        if (!ok) break;
+      // S_g = Q_g K^T of key tile t
+      auto scores = [&](int g, int t) -> bool {
+        const int s = t % K_STAGES;
+        // (S_g is free: the P V of tile g's previous key tile, which read P_g from its columns,
+        // was issued before and the tensor pipe runs in order)
+        if (!mbar_wait(smem_u32(&k_full[s]), (t / K_STAGES) & 1, abort_flag)) return false;
         tcgen05_fence_after();
-        const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + s * KV_BYTES), va = smem_u32(Vs + s * KV_BYTES);
+        if (traced) timeline_mark_thread(10 + g, t);
+        const uint32_t qa = smem_u32(Qs + g * Q_BYTES), ka = smem_u32(Ks + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma(tmem_s, smem_desc(qa + (k / 4) * CHUNK_BYTES + (k % 4) * 32),
+          umma(tmem_base + g * BN, smem_desc(qa + (k / 4) * CHUNK_BYTES + (k % 4) * 32),
                smem_desc(ka + (k / 4) * CHUNK_BYTES + (k % 4) * 32), idesc_qk, k > 0 ? 1u : 0u);
-        tcgen05_commit(smem_u32(s_full));
-        ok = mbar_wait(smem_u32(p_full), t & 1, abort_flag);
-        if (!ok) break;
+        tcgen05_commit(smem_u32(&s_full[g]));
+        if (g == groups - 1) tcgen05_commit(smem_u32(&k_empty[s]));
+        return true;
+      };
+      // O_g += P_g V of key tile t
+      auto values = [&](int g, int t) -> bool {
+        const int s = t % V_STAGES;
+        if (!mbar_wait(smem_u32(&v_full[s]), (t / V_STAGES) & 1, abort_flag) ||
+            !mbar_wait(smem_u32(&p_full[g]), t & 1, abort_flag))
+          return false;
         tcgen05_fence_after();
-        const uint32_t pa = smem_u32(Ps);
+        if (traced) timeline_mark_thread(12 + g, t);
+        const uint32_t va = smem_u32(Vs + s * KV_BYTES);
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          umma(tmem_o, smem_desc(pa + (k / 4) * CHUNK_BYTES + (k % 4) * 32),
-               smem_desc_mn(va + k * 16 * 128, CHUNK_BYTES), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
-        tcgen05_commit(smem_u32(&kv_empty[s]));
-        tcgen05_commit(smem_u32(o_ready));
-      }
+          umma_ts(tmem_base + 2 * BN + g * 128, tmem_base + g * BN + k * 8,
+                  smem_desc_mn(va + k * 16 * 128, CHUNK_BYTES), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+        tcgen05_commit(smem_u32(&o_ready[g]));
+        if (g == groups - 1) tcgen05_commit(smem_u32(&v_empty[s]));
+        return true;
+      };
+      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
+      for (int g = 0; ok && g < groups; ++g) ok = scores(g, 0);
+      for (int t = 0; ok && t < n_tiles; ++t)
+        for (int g = 0; ok && g < groups; ++g) {
+          ok = values(g, t);
+          if (ok && t + 1 < n_tiles) ok = scores(g, t + 1);
+        }
     }
   } else {
-    // one thread per row
-    const int q4 = warp & 3;
-    const int r = q4 * 32 + lane;
-    const bool valid = r < n_valid;
-    const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
-    const int pos = valid ? pos0 + qi : -1;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-    const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int j0 = (first_tile + t) * BN;
-      ok = mbar_wait(smem_u32(s_full), t & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tcgen05_fence_after();
-      const bool all_visible = j0 + BN - 1 <= pos && j0 >= lo;
-      // the whole row of S into registers: four loads in flight, one wait
-      float sv[BN];
-#pragma unroll
-      for (int c = 0; c < BN; c += 32) tmem_load32_nowait(tmem_s + lane_addr + c, sv + c);
-      tmem_load_wait();
-      // S is read: the next tile's scores may overwrite it
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(s_free));
-      if (!all_visible) {
-#pragma unroll
-        for (int e = 0; e < BN; ++e) {
-          const int j = j0 + e;
-          if (!(j <= pos && j >= lo)) sv[e] = -INFINITY;
-        }
-      }
-      // the row's maximum, four independent chains
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int e = 0; e < BN; e += 4) {
-        mx4[0] = fmaxf(mx4[0], sv[e]);
-        mx4[1] = fmaxf(mx4[1], sv[e + 1]);
-        mx4[2] = fmaxf(mx4[2], sv[e + 2]);
-        mx4[3] = fmaxf(mx4[3], sv[e + 3]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m, mx * p.scale_log2);
-      const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = ex2(m - m_safe);
-      // probabilities -> shared memory (bfloat16, rows of 128 bytes, 16-byte pieces exchanged by
-      // the row's low three bits: the 128-byte swizzle of the MMA operand)
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < BN; c += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const float p0 = ex2(fmaf(sv[c + e], p.scale_log2, -m_safe));        // -inf gives 0
-          const float p1 = ex2(fmaf(sv[c + e + 1], p.scale_log2, -m_safe));
-          sum4[(e / 2) & 3] += p0 + p1;
-          packed[e / 2] = pack2(p0, p1);
-        }
-        const int idx = ((c % 64) / 8) ^ (r & 7);
-        *reinterpret_cast<uint4*>(Ps + (c / 64) * CHUNK_BYTES + r * 128 + idx * 16) =
-            make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      }
-      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      l = l * alpha + sum;
-      m = m_new;
-      if (t > 0) {
-        // the sum so far must be complete before it is rescaled
-        ok = mbar_wait(smem_u32(o_ready), (t - 1) & 1, abort_flag);
+    // one thread per row of query tile g
+    const int g = (warp - 2) >> 2;
+    if (g < groups && n_tiles > 0) {
+      const int q4 = warp & 3;
+      const int r = q4 * 32 + lane;
+      const int qg = q0 + g * QPT;                       // the tile's first query
+      const int nq = min(QPT, q_len - qg);
+      const int n_valid = QPT > 1 ? nq * GT : min(GT, G - g0);
+      const bool valid = r < n_valid;
+      const int qi = QPT > 1 ? r / GT : 0, gg = QPT > 1 ? r % GT : r;
+      const int pos = valid ? kv_len - q_len + qg + qi : -1;
+      const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+      const uint32_t lane_addr = static_cast<uint32_t>(q4 * 32) << 16;
+      const uint32_t tmem_s = tmem_base + g * BN, tmem_o = tmem_base + 2 * BN + g * 128;
+      const bool tracer = traced && (threadIdx.x & 127) == 64;
+      float m = -INFINITY, l = 0.f;
+      bool ok = true;
+      for (int t = 0; t < n_tiles; ++t) {
+        const int j0 = (first_tile + t) * BN;
+        ok = mbar_wait(smem_u32(&s_full[g]), t & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tcgen05_fence_after();
-        if (!__all_sync(0xffffffffu, alpha == 1.f)) {
+        if (tracer) timeline_mark_thread(20 + 4 * g, t);
+        const bool all_visible = j0 + BN - 1 <= pos && j0 >= lo;
+        // the whole row of S into registers: four loads in flight, one wait
+        float sv[BN];
+#pragma unroll
+        for (int c = 0; c < BN; c += 32) tmem_load32_nowait(tmem_s + lane_addr + c, sv + c);
+        tmem_load_wait();
+        if (tracer) timeline_mark_thread(21 + 4 * g, t);
+        if (!all_visible) {
+#pragma unroll
+          for (int e = 0; e < BN; ++e) {
+            const int j = j0 + e;
+            if (!(j <= pos && j >= lo)) sv[e] = -INFINITY;
+          }
+        }
+        // the row's maximum, four independent chains
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < BN; e += 4) {
+          mx4[0] = fmaxf(mx4[0], sv[e]);
+          mx4[1] = fmaxf(mx4[1], sv[e + 1]);
+          mx4[2] = fmaxf(mx4[2], sv[e + 2]);
+          mx4[3] = fmaxf(mx4[3], sv[e + 3]);
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = ex2(m - m_safe);
+        // (these scores were computed after the previous key tile's P V of this query tile, in
+        // order: P_g has been read and the sum in O_g is complete)
+        // probabilities -> tensor memory, bfloat16 pairs over the first 64 columns of S_g: the A
+        // operand of O += P V
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < BN; c += 64) {
+          float packed[32];
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) {
+            const float p0 = ex2(fmaf(sv[c + e], p.scale_log2, -m_safe));        // -inf gives 0
+            const float p1 = ex2(fmaf(sv[c + e + 1], p.scale_log2, -m_safe));
+            sum4[(e / 2) & 3] += p0 + p1;
+            packed[e / 2] = __uint_as_float(pack2(p0, p1));
+          }
+          tmem_store32(tmem_s + lane_addr + c / 2, packed);
+        }
+        const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        l = l * alpha + sum;
+        m = m_new;
+        if (tracer) timeline_mark_thread(22 + 4 * g, t);
+        if (t > 0 && !__all_sync(0xffffffffu, alpha == 1.f)) {
           float ov[D];
 #pragma unroll
           for (int c = 0; c < D; c += 32) tmem_load32_nowait(tmem_o + lane_addr + c, ov + c);
@@ -271,30 +327,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           }
           tmem_store_wait();
         }
+        tmem_store_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (tracer) timeline_mark_thread(23 + 4 * g, t);
+        if (lane == 0) mbar_arrive(smem_u32(&p_full[g]));
       }
-      fence_async_shared();
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(p_full));
-    }
-    if (ok && n_tiles > 0) {
-      ok = mbar_wait(smem_u32(o_ready), (n_tiles - 1) & 1, abort_flag);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok && n_tiles > 0) {
-      tcgen05_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = p.out + ((size_t)(q_begin + q0 + qi) * p.H + kvh * G + g0 + gg) * D;
+      if (ok) {
+        ok = mbar_wait(smem_u32(&o_ready[g]), (n_tiles - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tcgen05_fence_after();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        bf16* dst = p.out + ((size_t)(q_begin + qg + qi) * p.H + kvh * G + g0 + gg) * D;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        float v[32];
-        tmem_load32(tmem_o + lane_addr + c, v);
-        if (valid) {
+        for (int c = 0; c < D; c += 32) {
+          float v[32];
+          tmem_load32(tmem_o + lane_addr + c, v);
+          if (valid) {
 #pragma unroll
-          for (int e = 0; e < 32; e += 8)
-            *reinterpret_cast<uint4*>(dst + c + e) =
-                make_uint4(pack2(v[e] * inv, v[e + 1] * inv), pack2(v[e + 2] * inv, v[e + 3] * inv),
-                           pack2(v[e + 4] * inv, v[e + 5] * inv), pack2(v[e + 6] * inv, v[e + 7] * inv));
+            for (int e = 0; e < 32; e += 8)
+              *reinterpret_cast<uint4*>(dst + c + e) =
+                  make_uint4(pack2(v[e] * inv, v[e + 1] * inv), pack2(v[e + 2] * inv, v[e + 3] * inv),
+                             pack2(v[e + 4] * inv, v[e + 5] * inv), pack2(v[e + 6] * inv, v[e + 7] * inv));
+          }
         }
       }
     }
@@ -302,7 +359,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_s), "r"((uint32_t)TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
   }
 }
 
@@ -318,6 +375,18 @@ bool encode(CUtensorMap* map, void* base, int rank, const cuuint64_t* dims, cons
 
 }  // namespace
 
+// what the compiler and the driver make of the kernel: registers per thread, most threads per
+// block, static and (after the opt-in) most dynamic shared memory; and what a launch asks for
+TS_EXPORT int ts_attention_tcgen05_resources(int* out8) {
+  cudaFuncAttributes a;
+  cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+  out8[6] = (int)e;
+  if (cudaFuncGetAttributes(&a, attn_prefill_tc_kernel) != cudaSuccess) return -1;
+  out8[0] = a.numRegs; out8[1] = a.maxThreadsPerBlock; out8[2] = (int)a.sharedSizeBytes;
+  out8[3] = a.maxDynamicSharedSizeBytes; out8[4] = THREADS; out8[5] = (int)SMEM; out8[7] = (int)a.localSizeBytes;
+  return 0;
+}
+
 TS_EXPORT int ts_attention_tcgen05_error() {
   int flag = 0;
   if (cudaMemcpyFromSymbol(&flag, g_error_flag, sizeof(int)) != cudaSuccess) return -1;
@@ -325,7 +394,8 @@ TS_EXPORT int ts_attention_tcgen05_error() {
 }
 
 // q, out [T, H, D]; caches [num_pages, Hkv, page_size, D]; bfloat16.  tile_req / tile_q0 (optional,
-// num_tiles ints each): the request and the first query of every block of 128 / group queries.
+// num_tiles ints each): the request and the first query of every block of tile_queries =
+// 2 * (128 / group) queries (two query tiles).
 TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k_cache, const void* v_cache,
                                          const int* block_table, const int* cu_q, const int* kv_lens,
                                          int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
@@ -375,10 +445,11 @@ TS_EXPORT int ts_paged_attention_tcgen05(const void* q, void* out, const void* k
   }
   TS_REQUIRE((tile_req == nullptr) == (tile_q0 == nullptr) && (tile_req == nullptr || num_tiles > 0),
              "paged_attention_tcgen05: the work list is incomplete");
-  TS_REQUIRE(tile_req == nullptr || tile_queries == p.queries_per_tile,
+  const int per_block = GROUPS * p.queries_per_tile;
+  TS_REQUIRE(tile_req == nullptr || tile_queries == per_block,
              "paged_attention_tcgen05: the work list was cut for %d queries a block, the kernel takes %d",
-             tile_queries, p.queries_per_tile);
-  dim3 grid((max_q_len + p.queries_per_tile - 1) / p.queries_per_tile, (unsigned)gy, num_requests);
+             tile_queries, per_block);
+  dim3 grid((max_q_len + per_block - 1) / per_block, (unsigned)gy, num_requests);
   if (tile_req) grid = dim3(num_tiles, (unsigned)gy, 1);
   TS_LAUNCH("attn_prefill_tcgen05", attn_prefill_tc_kernel, grid, THREADS, SMEM, stream, mq, mk, mv, p);
   return 0;

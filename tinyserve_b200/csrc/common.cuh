@@ -47,6 +47,18 @@ struct TimelineRecord {
 constexpr unsigned TIMELINE_CAPACITY = 1u << 17;
 static __device__ TimelineRecord g_timeline[TIMELINE_CAPACITY];
 static __device__ unsigned g_timeline_count;
+// a mark of the calling thread, whichever it is, with a value of its own (a loop count, say)
+__device__ __forceinline__ void timeline_mark_thread(int tag, int value) {
+  unsigned long long ns;
+  unsigned sm;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns));
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+  const unsigned i = atomicAdd(&g_timeline_count, 1u);
+  if (i < TIMELINE_CAPACITY)
+    g_timeline[i] = TimelineRecord{ns, (int)sm, tag, (int)gridDim.x, (int)gridDim.y, (int)gridDim.z,
+                                   (int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z,
+                                   (int)(blockDim.x * blockDim.y * blockDim.z), value};
+}
 __device__ __forceinline__ void timeline_mark(int tag) {
   if (threadIdx.x | threadIdx.y | threadIdx.z) return;
   unsigned long long ns;
@@ -73,6 +85,7 @@ __device__ __forceinline__ void timeline_mark(int tag) {
   }
 #else
 __device__ __forceinline__ void timeline_mark(int) {}
+__device__ __forceinline__ void timeline_mark_thread(int, int) {}
 #define TS_DEFINE_TIMELINE()
 #endif
 

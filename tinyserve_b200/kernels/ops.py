@@ -602,7 +602,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         out = torch.empty_like(q)
         lib = _attention_tcgen05(D)
         group = H // Hkv
-        tile_queries = 128 // group if group < 128 else 1
+        tile_queries = 2 * (128 // group if group < 128 else 1)      # two query tiles of 128 rows a block
         work = attention_work(ctx, tile_queries, q.device)
         if work.num_decode:
             _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
