@@ -80,6 +80,47 @@ def test_rmsnorm_and_gated_activation(dtype):
     close(ops().gated_activation(gu, "silu"), g / (1 + torch.exp(-g)) * u, dtype, "silu")
     close(ops().gated_activation(gu, "gelu_tanh"),
           torch.nn.functional.gelu(g, approximate="tanh") * u, dtype, "gelu")
+    # gate and up columns alternating in blocks (the layout of a row-interleaved fused weight)
+    for block, inter in ((64, 192), (4, 100), (5, 15)):
+        gb = rnd(7, 2 * inter, seed=7, dtype=dtype, scale=2.0)
+        parts = gb.double().view(7, inter // block, 2, block)
+        g, u = parts[:, :, 0].reshape(7, inter), parts[:, :, 1].reshape(7, inter)
+        close(ops().gated_activation(gb, "silu", block=block), g / (1 + torch.exp(-g)) * u, dtype, f"blocks of {block}")
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 40, 64])
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gated_product(M, activation):
+    """The gate/up product with the activation in its epilogue (weight rows in blocks of 64), beside
+    the same product followed by the activation kernel, from plain rows and from rows without
+    their norm factor."""
+    from tinyserve_b200.parts.base import interleave_halves
+    o = ops()
+    inter, K = 9600, 72           # 150 row tiles: the product needs no cut along K
+    x = rnd(M, K, seed=1, dtype=torch.bfloat16)
+    gate, up = rnd(inter, K, seed=2, dtype=torch.bfloat16, scale=0.3), rnd(inter, K, seed=3, dtype=torch.bfloat16, scale=0.3)
+    w = interleave_halves(torch.cat([gate, up]), 64).contiguous()
+    g, u = x.double() @ gate.double().T, x.double() @ up.double().T
+    act = (g / (1 + torch.exp(-g))) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
+    launches = o.launch_count()
+    got = o.gated_linear(x, w, activation, 64)
+    assert o.launch_count() - launches == 1, "one kernel: the activation runs in the product's epilogue"
+    assert got.shape == (M, inter)
+    close(got, act * u, torch.bfloat16, "fused")
+    monkey = o.GATED_EPILOGUE
+    o.GATED_EPILOGUE = False
+    try:
+        close(o.gated_linear(x, w, activation, 64), act * u, torch.bfloat16, "product then activation")
+    finally:
+        o.GATED_EPILOGUE = monkey
+    if M <= 16:
+        sumsq = (rnd(1, 16, seed=5).abs() + 0.5).contiguous()
+        rows = o.ScaledRows(x, sumsq, 1, 1e-6)
+        scale = torch.rsqrt(sumsq[0, :M].double().cpu() / K + 1e-6)[:, None]
+        gs, us = g.cpu() * scale, u.cpu() * scale
+        acts = (gs / (1 + torch.exp(-gs))) if activation == "silu" else torch.nn.functional.gelu(gs, approximate="tanh")
+        close(o.gated_linear(rows, w, activation, 64), acts * us, torch.bfloat16, "fused, scaled rows")
+    assert o.gemm_tcgen05_error() == 0
 
 
 def _rope_ref(x, pos, cos, sin, R, interleaved):

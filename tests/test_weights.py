@@ -43,6 +43,15 @@ def test_loading_fuses_by_name_and_keeps_dtypes(tmp_path):
     assert torch.equal(attn.w["qkv_proj.weight"], fused) and fused.dtype == torch.bfloat16
     mlp = model.blocks[0].ffn
     assert torch.equal(mlp.w["gate_up_proj.weight"][160:], stored["model.layers.0.mlp.up_proj.weight"])
+    # a width that is a multiple of 64 (configuration A): gate and up rows alternate in blocks of 64
+    folder_a = make_model_dir(tmp_path / "a", "A", seed=1)
+    stored_a = load_file(os.path.join(folder_a, "model.safetensors"))
+    model_a = build_model(tiny_config("A"))
+    load_weights(model_a, folder_a, torch.float32, "cpu")
+    w = model_a.blocks[1].ffn.w["gate_up_proj.weight"]
+    gate, up = stored_a["model.layers.1.mlp.gate_proj.weight"].float(), stored_a["model.layers.1.mlp.up_proj.weight"].float()
+    assert gate.shape[0] == 128 and model_a.blocks[1].ffn.block == 64
+    assert torch.equal(w, torch.cat([gate[:64], up[:64], gate[64:], up[64:]]))
     # a vector stored in 32-bit stays 32-bit; a matrix takes the engine's dtype
     assert model.norm.w["weight"].dtype == torch.float32
     assert attn.q_norm.w["weight"].dtype == torch.float32

@@ -189,6 +189,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
+// gated feed-forward: act(gate) * up
+enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
+__device__ __forceinline__ float activate(float g, int act) {
+  if (act == ACT_SILU) return g / (1.f + expf(-g));
+  const float c = 0.7978845608028654f;
+  return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g)));
+}
+
 // a weight vector that is either float or bfloat16, chosen at run time
 struct VecParam {
   const void* ptr;

@@ -368,30 +368,30 @@ TS_EXPORT int ts_reduce_partials(int dtype, const float* partials, int splits, i
 }
 
 // ------------------------------------------------------------------ gated activation
-// in [rows, 2 * inter] = gate | up  ->  out [rows, inter] = act(gate) * up
-enum { ACT_SILU = 0, ACT_GELU_TANH = 1 };
-
-__device__ __forceinline__ float activate(float g, int act) {
-  if (act == ACT_SILU) return g / (1.f + expf(-g));
-  const float c = 0.7978845608028654f;
-  return 0.5f * g * (1.f + tanhf(c * (g + 0.044715f * g * g * g)));
-}
+// in [rows, 2 * inter] -> out [rows, inter] = act(gate) * up.  block == 0: in = gate | up (two
+// halves); block > 0: gate and up alternate in blocks of that many columns (gate columns
+// [0, block), up columns [0, block), gate columns [block, 2 block), ...), the layout of a fused
+// projection whose weight rows are interleaved so that one 128-row tile of the tcgen05 product
+// holds matching gate and up rows.
+__device__ __forceinline__ int gate_column(int c, int block) { return block ? (c / block) * 2 * block + c % block : c; }
 
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ in, T* __restrict__ out, int inter,
-                                        int act) {
+                                        int act, int block) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= inter) return;
   const T* r = in + row * 2 * inter;
-  out[row * inter + c] = from_f32<T>(activate(to_f32<T>(r[c]), act) * to_f32<T>(r[inter + c]));
+  const int g = gate_column(c, block), u = g + (block ? block : inter);
+  out[row * inter + c] = from_f32<T>(activate(to_f32<T>(r[g]), act) * to_f32<T>(r[u]));
 }
 
 // 16 bytes per thread and operand, for widths that are a multiple of 16 / sizeof(T)
 template <typename T>
-__global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int act) {
+__global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restrict__ out, int inter, int act,
+                                            int block) {
   constexpr int V = 16 / sizeof(T);
   pdl_trigger();
   pdl_wait();
@@ -399,12 +399,13 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restr
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
   if (c >= inter) return;
   const T* r = in + row * 2 * inter;
+  const int gc = gate_column(c, block), uc = gc + (block ? block : inter);      // block is a multiple of V
   float g[V], u[V], o[V];
 #pragma unroll
   for (int h = 0; h < V / 4; ++h) {
     float a[4], b[4];
-    Quad<T>::load(r + c + 4 * h, a);
-    Quad<T>::load(r + inter + c + 4 * h, b);
+    Quad<T>::load(r + gc + 4 * h, a);
+    Quad<T>::load(r + uc + 4 * h, b);
 #pragma unroll
     for (int e = 0; e < 4; ++e) { g[4 * h + e] = a[e]; u[4 * h + e] = b[e]; }
   }
@@ -418,26 +419,29 @@ __global__ void gated_activation_vec_kernel(const T* __restrict__ in, T* __restr
 }
 
 template <typename T>
-int launch_gated_activation(const void* in, void* out, int num_rows, int inter, int act, cudaStream_t stream) {
+int launch_gated_activation(const void* in, void* out, int num_rows, int inter, int act, int block,
+                            cudaStream_t stream) {
   constexpr int V = 16 / sizeof(T);
-  const bool vec = inter % V == 0 && (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
+  const bool vec = inter % V == 0 && block % V == 0 &&
+                   (reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) % 16 == 0;
   if (vec) {
     dim3 grid(num_rows, (inter / V + 255) / 256);
-    TS_LAUNCH("gated_activation", gated_activation_vec_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act);
+    TS_LAUNCH("gated_activation", gated_activation_vec_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block);
   } else {
     dim3 grid(num_rows, (inter + 255) / 256);
-    TS_LAUNCH("gated_activation", gated_activation_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act);
+    TS_LAUNCH("gated_activation", gated_activation_kernel<T>, grid, 256, 0, stream, (const T*)in, (T*)out, inter, act, block);
   }
   return 0;
 }
 
 TS_EXPORT int ts_gated_activation(int dtype, const void* in, void* out, int num_rows, int inter,
-                                  int act, cudaStream_t stream) {
+                                  int act, int block, cudaStream_t stream) {
   TS_REQUIRE(num_rows > 0 && inter > 0, "gated_activation: empty input");
+  TS_REQUIRE(block >= 0 && (block == 0 || inter % block == 0), "gated_activation: %d columns do not come in blocks of %d", inter, block);
   TS_REQUIRE((inter + 255) / 256 <= 65535, "gated_activation: width %d is too large", inter);
   TS_REQUIRE(act == ACT_SILU || act == ACT_GELU_TANH, "gated_activation: unknown activation %d", act);
-  if (dtype == TS_F32) return launch_gated_activation<float>(in, out, num_rows, inter, act, stream);
-  if (dtype == TS_BF16) return launch_gated_activation<__nv_bfloat16>(in, out, num_rows, inter, act, stream);
+  if (dtype == TS_F32) return launch_gated_activation<float>(in, out, num_rows, inter, act, block, stream);
+  if (dtype == TS_BF16) return launch_gated_activation<__nv_bfloat16>(in, out, num_rows, inter, act, block, stream);
   return ts_fail("gated_activation: unknown dtype %d", dtype);
 }
 

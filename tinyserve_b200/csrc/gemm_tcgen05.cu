@@ -52,6 +52,9 @@ struct GemmParams {
   VecParam norm_w;
   bf16* hprime;
   float* sumsq_out;
+  // Gated form (no K cuts, up to 64 tokens): the weight rows alternate in blocks of 64, gate rows
+  // then the matching up rows, so a 128-row tile holds both; out [M, N / 2] = act(gate) * up.
+  int gated_act;        // 0: off; else the activation's code + 1
 };
 constexpr int SUMSQ_STRIDE = 16;     // tokens of the residual form (one token tile of 16)
 
@@ -248,6 +251,39 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // no block leaves while a peer may still read its shared memory
     cluster_arrive();
     cluster_wait();
+  } else if (p.gated_act != 0) {
+    if constexpr (TILE_T <= 64) {
+      // lanes 0..63 hold gate rows, lanes 64..127 the up rows of the same output columns: the up
+      // half goes through shared memory (the ring is idle), the gate half activates and stores
+      float acc[TILE_T];
+#pragma unroll
+      for (int c = 0; c < TILE_T; c += 8) {
+        float v[8];
+        if (have) tmem_load8_sum<TILE_T>(taddr + c, v);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[c + i] = scaled ? v[i] * row_scale[c + i] : v[i];
+      }
+      float* up = reinterpret_cast<float*>(smem);               // [64][TILE_T + 1]
+      if (warp >= 2) {
+#pragma unroll
+        for (int i = 0; i < TILE_T; ++i) up[(threadIdx.x - 64) * (TILE_T + 1) + i] = acc[i];
+      }
+      __syncthreads();
+      const int col = n_tile * 64 + threadIdx.x, half_n = p.N / 2;
+      if (warp < 2 && col < half_n) {
+#pragma unroll
+        for (int i = 0; i < TILE_T; ++i) {
+          const int m = t0 + i;
+          if (m < p.M)
+            static_cast<bf16*>(p.out)[(size_t)m * p.ldc + col] =
+                __float2bfloat16_rn(activate(acc[i], p.gated_act - 1) * up[threadIdx.x * (TILE_T + 1) + i]);
+        }
+      }
+    }
   } else if (p.splits == 1) {
 #pragma unroll 1
     for (int c = 0; c < TILE_T; c += 8) {
@@ -674,17 +710,17 @@ namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, cudaStream_t stream);
+               float* sumsq_out, int gated_act, cudaStream_t stream);
 }
 
 TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                               long long ldw, long long ldc, int out_f32, int splits, float* partials,
                               int* counters, cudaStream_t stream) {
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, nullptr, 0, 0.f,
-                    nullptr, nullptr, 0, nullptr, nullptr, stream);
+                    nullptr, nullptr, 0, nullptr, nullptr, 0, stream);
 }
 
-// The same product with one or both of two extras, for up to 16 tokens.
+// The same product with extras.  The first two are for up to 16 tokens.
 // x_sumsq != nullptr: x holds rows v * norm_weight that still lack their RMSNorm factor, and
 // x_sumsq [x_tiles][16] the sums of v^2 over each 128 columns; every token's result is scaled by
 // rsqrt(sum / K + x_eps).
@@ -692,24 +728,30 @@ TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, in
 // are one thread-block cluster): residual [M, N] (float, contiguous) += x w^T; hprime [M, N]
 // (bfloat16) = residual * norm_w; sumsq_out [N / 128 rounded up][16] = the sums of residual^2
 // over each 128 columns, for the product that takes hprime as its x.
+// gated_act != 0 (up to 64 tokens, splits == 1, bfloat16 out [M, N / 2], ldc its leading
+// dimension, N a multiple of 128): the rows of w alternate in blocks of 64, gate rows then the
+// matching up rows; out = act(gate) * up with act = gated_act - 1 (0 SiLU, 1 GELU-tanh).
 TS_EXPORT int ts_gemm_tcgen05_fused(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                                     long long ldw, long long ldc, int out_f32, int splits, float* partials,
                                     int* counters, const float* x_sumsq, int x_tiles, float x_eps,
                                     float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-                                    float* sumsq_out, cudaStream_t stream) {
-  TS_REQUIRE(M <= SUMSQ_STRIDE, "gemm_tcgen05: the fused forms take up to %d tokens, got %d", SUMSQ_STRIDE, M);
+                                    float* sumsq_out, int gated_act, cudaStream_t stream) {
+  TS_REQUIRE((x_sumsq == nullptr && residual == nullptr) || M <= SUMSQ_STRIDE,
+             "gemm_tcgen05: the scaled-rows and residual forms take up to %d tokens, got %d", SUMSQ_STRIDE, M);
+  TS_REQUIRE(gated_act == 0 || (gated_act <= 2 && M <= 64 && splits == 1 && out && !out_f32 && !residual && N % 128 == 0),
+             "gemm_tcgen05: the gated form takes up to 64 tokens, no K cuts, a bfloat16 output and whole 128-row tiles");
   TS_REQUIRE(x_sumsq == nullptr || x_tiles > 0, "gemm_tcgen05: sums of squares without their tile count");
   TS_REQUIRE(residual == nullptr || (norm_w && hprime && sumsq_out && splits <= 8),
              "gemm_tcgen05: the residual form needs the norm's weight, both outputs and at most 8 cuts");
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, x_sumsq, x_tiles,
-                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, stream);
+                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, gated_act, stream);
 }
 
 namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, cudaStream_t stream) {
+               float* sumsq_out, int gated_act, cudaStream_t stream) {
   TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
   TS_REQUIRE(M <= 65535 * 128, "gemm_tcgen05: too many rows");
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
@@ -727,6 +769,7 @@ int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, lon
   p.x_sumsq = x_sumsq; p.x_tiles = x_tiles; p.x_eps = x_eps;
   p.residual = residual; p.norm_w = VecParam{norm_w, norm_w_is_f32};
   p.hprime = static_cast<bf16*>(hprime); p.sumsq_out = sumsq_out;
+  p.gated_act = gated_act;
   dim3 grid((N + TILE_N - 1) / TILE_N, (M + tile_t - 1) / tile_t, splits);
   switch (tile_t) {
     case 16: return launch<16>(mw, mx, p, grid, stream);

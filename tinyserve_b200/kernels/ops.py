@@ -272,13 +272,16 @@ def _persistent_scratch(device):
     return _partials[key]
 
 
-def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False, scale=None):
-    """``scale``: the ScaledRows whose ``data`` is ``x`` (tiled form only)."""
+def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False, scale=None,
+                    gated=0):
+    """``scale``: the ScaledRows whose ``data`` is ``x``; ``gated``: activation code + 1 of the
+    gated epilogue (out [M, N / 2]); both tiled form only."""
     M, K = x.shape
     N = weight.shape[0]
+    out_cols = N // 2 if gated else N
     out = None if partials_only else torch.empty(
-        M, N, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
-    form = "tiled" if partials_only or scale is not None else (form or TCGEN05_FORM)
+        M, out_cols, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
+    form = "tiled" if partials_only or scale is not None or gated else (form or TCGEN05_FORM)
     lib = _gemm_tcgen05()
     if form == "persistent":
         blocks = min(blocks or NUM_SMS, NUM_SMS)
@@ -297,11 +300,12 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None,
         need = lib.ts_gemm_tcgen05_scratch(c_int(M), c_int(N), c_int(splits))
         partials = torch.empty(need, dtype=torch.float32, device=x.device)
         counters = None if partials_only else _tile_counters(x.device)
-    if scale is not None:
+    if scale is not None or gated:
         _check(lib, lib.ts_gemm_tcgen05_fused(
             _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
-            c_longlong(weight.stride(0)), c_longlong(N), c_int(1 if out_float32 else 0), c_int(splits),
-            _ptr(partials), _ptr(counters), *scale.args(), None, None, c_int(0), None, None, _stream()))
+            c_longlong(weight.stride(0)), c_longlong(out_cols), c_int(1 if out_float32 else 0), c_int(splits),
+            _ptr(partials), _ptr(counters), *(scale.args() if scale is not None else _NO_SCALE), None, None,
+            c_int(0), None, None, c_int(gated), _stream()))
     else:
         _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
                                         c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
@@ -377,7 +381,7 @@ def _product_add_residual(pending, residual, weight, eps):
     _check(lib, lib.ts_gemm_tcgen05_fused(
         _ptr(x), _ptr(w), None, c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)), c_longlong(w.stride(0)),
         c_longlong(N), c_int(0), c_int(pending.splits()), None, None, *_NO_SCALE, _ptr(residual), _ptr(weight),
-        c_int(_vec_flag(weight, torch.bfloat16)), _ptr(hprime), _ptr(sumsq), _stream()))
+        c_int(_vec_flag(weight, torch.bfloat16)), _ptr(hprime), _ptr(sumsq), c_int(0), _stream()))
     return ScaledRows(hprime, sumsq, tiles, eps)
 
 
@@ -426,16 +430,43 @@ def rmsnorm(x, weight, eps, out=None):
     return out.view(shape)
 
 
-def gated_activation(gate_up, activation="silu"):
-    """[rows, 2 I] (gate | up) -> act(gate) * up, [rows, I]."""
+def gated_activation(gate_up, activation="silu", block=0):
+    """[rows, 2 I] -> act(gate) * up, [rows, I].  ``block`` 0: the input is gate | up; else gate
+    and up columns alternate in blocks of ``block`` (see gated_linear)."""
     gate_up = materialize(gate_up)
     _cuda(gate_up)
     rows, two_i = gate_up.shape
     out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
     lib = _elementwise()
     _check(lib, lib.ts_gated_activation(c_int(_dt(gate_up)), _ptr(gate_up), _ptr(out), c_int(rows),
-                                        c_int(two_i // 2), c_int(ACTIVATIONS[activation]), _stream()))
+                                        c_int(two_i // 2), c_int(ACTIVATIONS[activation]), c_int(block), _stream()))
     return out
+
+
+#: rows of gate and up alternate in blocks of this many in a fused gate/up weight: half a 128-row
+#: tile of the tcgen05 product
+GATED_BLOCK = 64
+#: let the tcgen05 product apply the gated activation in its epilogue
+GATED_EPILOGUE = os.environ.get("TINYSERVE_GATED_EPILOGUE", "1") != "0"
+
+
+def gated_linear(x, weight, activation="silu", block=0):
+    """act(gate) * up of x @ weight^T, [M, N / 2].  weight [N, K] holds gate rows then up rows
+    (``block`` 0) or alternates them in blocks of ``block`` rows.  With blocks of GATED_BLOCK, up
+    to 64 tokens and a product that needs no cut along K, the tcgen05 product does the activation
+    in its epilogue; otherwise the product is followed by the activation kernel.  x may be the
+    ScaledRows that add_rmsnorm returned."""
+    rows = x.data if isinstance(x, ScaledRows) else x
+    N, K = weight.shape
+    if (GATED_EPILOGUE and block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
+            and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05"
+            and TCGEN05_FORM == "tiled" and _tcgen05_ok(rows, weight, None)
+            and (rows is x or rows.shape[0] <= FUSED_MAX_TOKENS)
+            and gemm_splits(rows.shape[0], N, K) == 1):
+        _cuda(rows, weight)
+        return _linear_tcgen05(rows, weight, False, splits=1, gated=ACTIVATIONS[activation] + 1,
+                               scale=x if rows is not x else None)
+    return gated_activation(linear(x, weight), activation, block)
 
 
 def qk_norm_rope_kvwrite(qkv, positions, num_heads, num_kv_heads, head_dim, rotary=None,

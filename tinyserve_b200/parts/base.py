@@ -36,13 +36,26 @@ class ParamSpec:
     role "int_table": integer table, kept as int32.
     init: "normal" (N(0, 0.02)), "norm_weight" (1 + U(-0.1, 0.1)) or "zeros", used by
     the random-weights mode.  ``sources`` lists the checkpoint tensors that fill it
-    (default: one tensor of the same name and shape).
+    (default: one tensor of the same name and shape).  ``interleave_halves`` = b > 0: after the
+    sources are placed, the rows of the first and the second half alternate in blocks of b rows
+    (first-half rows [0, b), second-half rows [0, b), first-half rows [b, 2b), ...).
     """
 
     shape: tuple
     role: str = "matrix"
     init: str = "normal"
     sources: tuple = ()
+    interleave_halves: int = 0
+
+
+def interleave_halves(tensor, block: int):
+    """Rows of the two halves of ``tensor`` alternating in blocks of ``block`` rows."""
+    rows = tensor.shape[0]
+    if block <= 0:
+        return tensor
+    if rows % (2 * block):
+        raise ValueError(f"{rows} rows do not split into two halves of blocks of {block}")
+    return tensor.view(2, rows // (2 * block), block, *tensor.shape[1:]).transpose(0, 1).reshape(tensor.shape)
 
 
 @dataclass(frozen=True)

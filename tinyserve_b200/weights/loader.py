@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import torch
 from safetensors import safe_open
 
-from ..parts.base import ParamSpec, Source
+from ..parts.base import ParamSpec, Source, interleave_halves
 
 
 class WeightError(RuntimeError):
@@ -136,6 +136,8 @@ def load_weights(model, model_dir: str, dtype: torch.dtype, device) -> int:
                 src = handles[fname].get_tensor(e.name)
                 dst = param[e.row_start:e.row_end] if param.dim() else param
                 dst.copy_(src.to(pdtype) if src.dtype != pdtype else src)
+            if spec.interleave_halves:
+                param = interleave_halves(param, spec.interleave_halves).contiguous()
             tensors.setdefault(id(part), (part, {}))[1][local] = param
             total += param.numel() * param.element_size()
     finally:
