@@ -104,9 +104,12 @@ def test_gated_product(M, activation):
     act = (g / (1 + torch.exp(-g))) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
     launches = o.launch_count()
     got = o.gated_linear(x, w, activation, 64)
-    assert o.launch_count() - launches == 1, "one kernel: the activation runs in the product's epilogue"
+    if M <= o.FUSED_MAX_TOKENS:
+        assert o.launch_count() - launches == 1, "one kernel: the activation runs in the product's epilogue"
     assert got.shape == (M, inter)
     close(got, act * u, torch.bfloat16, "fused")
+    # the kernel's gated form itself takes up to 64 tokens
+    close(o._linear_tcgen05(x, w, False, splits=1, gated=o.ACTIVATIONS[activation] + 1), act * u, torch.bfloat16, "gated form")
     monkey = o.GATED_EPILOGUE
     o.GATED_EPILOGUE = False
     try:
@@ -334,6 +337,54 @@ def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=4)
     out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
     close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "decode attention")
+
+
+@pytest.mark.parametrize("H,Hkv,D,page", [(32, 8, 128, 16), (6, 2, 64, 8), (20, 1, 48, 16), (3, 3, 256, 32)])
+@pytest.mark.parametrize("window", [0, 100])
+@pytest.mark.parametrize("source", ["tensor", "partials"])
+@pytest.mark.parametrize("merge", ["cluster", "launch"])
+def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, merge, monkeypatch):
+    """Decode steps hand the fused q/k/v projection to the attention kernel, which applies the
+    per-head norm and the rotary encoding and writes the newest key and value itself: the same
+    outputs and the same cache as the norm/rotary kernel followed by the attention kernel."""
+    from tinyserve_b200.parts.rotary import Rotary
+    o = ops()
+    monkeypatch.setattr(o, "DECODE_MERGE", merge)
+    kv_lens = [1, 64, 65, 300, 129, 700, 17, 128]
+    B, width = len(kv_lens), (H + 2 * Hkv) * D
+    K = 256
+    x, w = rnd(B, K, seed=1, dtype=torch.bfloat16), rnd(width, K, seed=2, dtype=torch.bfloat16, scale=0.2)
+    if source == "partials" and width >= 256:
+        qkv = o._linear_tcgen05(x, w, False, splits=2, partials_only=True)
+    else:
+        qkv = o.linear(x, w)
+    k = [rnd(n, Hkv, D, seed=10 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
+    v = [rnd(n, Hkv, D, seed=30 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
+    kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=4)
+    pos = torch.tensor([n - 1 for n in kv_lens], dtype=torch.int32).cuda()
+    slots = torch.stack([table[b, (n - 1) // page] * page + (n - 1) % page for b, n in enumerate(kv_lens)]).int().cuda()
+    slots[6] = -1                      # this request writes nothing (its newest key is still used)
+    rot = Rotary(D, 1e4, "half")
+    rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(D, 1e4, 1024))
+    qw, kw = rnd(D, seed=5, dtype=torch.float32) + 1, rnd(D, seed=6, dtype=torch.float32) + 1
+    cu = torch.arange(B + 1, dtype=torch.int32).cuda()
+    ctx = SimpleNamespace(cu_q=cu, kv_lens=torch.tensor(kv_lens, dtype=torch.int32).cuda(), num_requests=B,
+                          max_q_len=1, max_kv_len=max(kv_lens))
+    view = SimpleNamespace(block_table=table, page_size=page, slot_mapping=slots)
+    results = []
+    for fused in (True, False):
+        monkeypatch.setattr(o, "FUSED_DECODE_QKV", fused)
+        kc_i, vc_i = kc.clone(), vc.clone()
+        launches = o.launch_count()
+        out = o.attention_from_qkv(qkv, pos, H, Hkv, D, rot, qw, kw, 1e-6, kc_i, vc_i, view, ctx, D ** -0.5, window)
+        results.append((out, kc_i, vc_i, o.launch_count() - launches))
+    (out_f, kc_f, vc_f, n_f), (out_u, kc_u, vc_u, n_u) = results
+    assert n_f < n_u, "fewer kernels"
+    live = [b for b in range(B) if b != 6]
+    assert torch.equal(kc_f, kc_u) and torch.equal(vc_f, vc_u), "the same cache, bit by bit"
+    assert (out_f[live].float() - out_u[live].float()).abs().max().item() <= 2.0 ** -7 * out_u.float().abs().max().item()
+    # the request without a slot: the two-kernel path reads a stale key there, the fused one its own
+    assert torch.isfinite(out_f.float()).all()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -58,6 +58,22 @@ struct MmaAttnParams {
   int heads_per_tile, queries_per_tile, head_tiles;
   int num_splits, window;
   float scale_log2;
+  // Decode straight from the fused q/k/v projection (from_qkv != 0; q is not read): every block
+  // builds its query rows itself (sum of the split-K partial tiles, per-head RMSNorm, rotary), and
+  // the block whose key range holds the newest position builds that key and value too, uses them
+  // from shared memory and (head tile 0) writes them to the cache.
+  int from_qkv;
+  const bf16* qkv;          // [T, (H + 2 Hkv) * D], or null: the partial tiles in `ps`
+  PartialSrc ps;
+  const int* positions;     // [T]
+  const int* slot_mapping;  // [T] cache slot of the token (page * page_size + row), -1: none
+  const float* rope_cos;    // [positions, D / 2]
+  const float* rope_sin;
+  VecParam q_weight, k_weight;
+  int has_norm;
+  float eps;
+  bf16* k_cache_out;        // the same caches, for the newest token's key and value
+  bf16* v_cache_out;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -323,6 +339,117 @@ __global__ void __launch_bounds__(PRE_THREADS) attn_prefill_kernel(MmaAttnParams
 
 // ------------------------------------------------------------------ decode (q_len == 1)
 constexpr int DEC_STAGES = 3;
+constexpr int ROPE_STEPS = (D / 4 + 31) / 32;      // pairs of pairs per lane over half a head
+
+// What a lane needs of the norm weights and of the rotary angles of a position, for its elements
+// of a head (pairs j, j + 1 of both halves): fetched before the dependency wait.
+struct HeadConsts {
+  float2 wa[ROPE_STEPS], wb[ROPE_STEPS], c[ROPE_STEPS], sn[ROPE_STEPS];
+};
+__device__ __forceinline__ void load_weights(HeadConsts& h, const VecParam& w, bool has_norm, int lane) {
+  constexpr int HALF = D / 2;
+#pragma unroll
+  for (int s = 0; s < ROPE_STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    h.wa[s] = h.wb[s] = make_float2(1.f, 1.f);
+    if (has_norm && j < HALF) {
+      h.wa[s] = make_float2(w[j], w[j + 1]);
+      h.wb[s] = make_float2(w[HALF + j], w[HALF + j + 1]);
+    }
+  }
+}
+__device__ __forceinline__ void load_angles(HeadConsts& h, const MmaAttnParams& p, int pos, int lane) {
+  constexpr int HALF = D / 2;
+#pragma unroll
+  for (int s = 0; s < ROPE_STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    h.c[s] = h.sn[s] = make_float2(0.f, 0.f);
+    if (j < HALF) {
+      h.c[s] = *reinterpret_cast<const float2*>(p.rope_cos + (size_t)pos * HALF + j);
+      h.sn[s] = *reinterpret_cast<const float2*>(p.rope_sin + (size_t)pos * HALF + j);
+    }
+  }
+}
+
+// One head of token t of the fused projection (column `col0` on, D wide), by one warp: the sum of
+// the partial tiles (or the plain row), RMSNorm over the head with the weights in `h` (has_norm),
+// rotary with the pairing (j, j + D / 2) (rotate), rounded to bfloat16, to `dst` (shared memory).
+// The arithmetic is that of qk_norm_rope_kvwrite (elementwise.cu), so both paths agree bit by bit.
+__device__ __forceinline__ void build_head(const MmaAttnParams& p, int t, int col0, bool rotate, const HeadConsts& h,
+                                           int lane, bf16* dst) {
+  constexpr int HALF = D / 2;
+  float2 a[ROPE_STEPS], b[ROPE_STEPS];
+#pragma unroll
+  for (int s = 0; s < ROPE_STEPS; ++s) a[s] = b[s] = make_float2(0.f, 0.f);
+  if (p.ps.base) {
+    // the loads of up to eight splits are in flight together; the sum runs in split order
+    for (int k0 = 0; k0 < p.ps.splits; k0 += 8) {
+      float2 qa[8][ROPE_STEPS], qb[8][ROPE_STEPS];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int s = 0; s < ROPE_STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (k0 + k < p.ps.splits && j < HALF) {
+            qa[k][s] = __ldcg(reinterpret_cast<const float2*>(p.ps.base + p.ps.offset(k0 + k, t, col0 + j)));
+            qb[k][s] = __ldcg(reinterpret_cast<const float2*>(p.ps.base + p.ps.offset(k0 + k, t, col0 + HALF + j)));
+          }
+        }
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+#pragma unroll
+        for (int s = 0; s < ROPE_STEPS; ++s) {
+          const int j = 2 * (lane + 32 * s);
+          if (k0 + k < p.ps.splits && j < HALF) {
+            a[s].x += qa[k][s].x; a[s].y += qa[k][s].y;
+            b[s].x += qb[k][s].x; b[s].y += qb[k][s].y;
+          }
+        }
+    }
+  } else {
+    const bf16* src = p.qkv + (size_t)t * (p.H + 2 * p.Hkv) * D + col0;
+#pragma unroll
+    for (int s = 0; s < ROPE_STEPS; ++s) {
+      const int j = 2 * (lane + 32 * s);
+      if (j < HALF) {
+        a[s] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + j));
+        b[s] = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + j));
+      }
+    }
+  }
+  if (!rotate) {       // a value head: copied as it is
+#pragma unroll
+    for (int s = 0; s < ROPE_STEPS; ++s) {
+      const int j = 2 * (lane + 32 * s);
+      if (j < HALF) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(a[s].x, a[s].y);
+        *reinterpret_cast<__nv_bfloat162*>(dst + HALF + j) = __floats2bfloat162_rn(b[s].x, b[s].y);
+      }
+    }
+    return;
+  }
+  float acc = 0.f;
+#pragma unroll
+  for (int s = 0; s < ROPE_STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < HALF) acc += a[s].x * a[s].x + a[s].y * a[s].y + b[s].x * b[s].x + b[s].y * b[s].y;
+  }
+  const float rstd = p.has_norm ? rsqrtf(warp_sum(acc) / (float)D + p.eps) : 1.f;
+#pragma unroll
+  for (int s = 0; s < ROPE_STEPS; ++s) {
+    const int j = 2 * (lane + 32 * s);
+    if (j < HALF) {
+      float a0 = a[s].x, a1 = a[s].y, b0 = b[s].x, b1 = b[s].y;
+      if (p.has_norm) {
+        a0 *= rstd * h.wa[s].x; a1 *= rstd * h.wa[s].y;
+        b0 *= rstd * h.wb[s].x; b1 *= rstd * h.wb[s].y;
+      }
+      const float2 c = h.c[s], sn = h.sn[s];
+      *reinterpret_cast<__nv_bfloat162*>(dst + j) = __floats2bfloat162_rn(a0 * c.x - b0 * sn.x, a1 * c.y - b1 * sn.y);
+      *reinterpret_cast<__nv_bfloat162*>(dst + HALF + j) = __floats2bfloat162_rn(b0 * c.x + a0 * sn.x, b1 * c.y + a1 * sn.y);
+    }
+  }
+}
 
 __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   extern __shared__ __align__(16) char smem[];
@@ -351,21 +478,66 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   const int tile_begin = first_tile + split * per_split;
   const int n_tiles = max(0, min(first_tile + total, tile_begin + per_split) - tile_begin);
   const int newest_tile = qpos / BN;
+  // from the projection itself the newest key never comes from the cache: every tile may be
+  // fetched before the wait, without that key, which this block makes itself
+  const bool from_qkv = p.from_qkv != 0;
+  const int j_load = from_qkv ? j_hi - 1 : j_hi;
+  const int late_tile = from_qkv ? -1 : newest_tile;
+  const bool has_newest = from_qkv && newest_tile >= tile_begin && newest_tile < tile_begin + n_tiles;
+  __shared__ __align__(16) bf16 newest_kv[2 * D];
 
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s)
-    if (s < n_tiles && tile_begin + s != newest_tile)
-      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+    if (s < n_tiles && tile_begin + s != late_tile)
+      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_load);
+  int slot = -1;
+  HeadConsts hq, hk;
+  if (from_qkv) {
+    const int pos_q = p.positions[q_begin];
+    slot = p.slot_mapping[q_begin];
+    load_angles(hq, p, pos_q, lane);
+    load_weights(hq, p.q_weight, p.has_norm, lane);
+    hk = hq;
+    if (has_newest) load_weights(hk, p.k_weight, p.has_norm, lane);
+  }
   pdl_wait();
-  for (int i = threadIdx.x; i < 16 * CH; i += THREADS) {
-    const int r = i / CH, c = i % CH;
-    const bool valid = r < ng;
-    const bf16* src = valid ? p.q + ((size_t)q_begin * p.H + kvh * G + g0 + r) * D + c * 8 : p.q;
-    cp_async16(smem_u32(Qs + r * ROW_BYTES + c * 16), src, valid);
+  if (from_qkv) {
+    // the heads this block makes, dealt to the warps in turn: the newest key (norm, rotary) and
+    // value where this block holds them, then the query rows; rows past the group are zero
+    const int extra = has_newest ? 2 : 0;
+    for (int i = warp; i < extra + 16; i += THREADS / 32) {
+      if (i < extra) {
+        build_head(p, q_begin, (p.H + (i == 0 ? 0 : p.Hkv) + kvh) * D, i == 0, hk, lane, newest_kv + i * D);
+        continue;
+      }
+      const int r = i - extra;
+      bf16* row = reinterpret_cast<bf16*>(Qs + r * ROW_BYTES);
+      if (r < ng) {
+        build_head(p, q_begin, (kvh * G + g0 + r) * D, true, hq, lane, row);
+      } else {
+        for (int d = lane * 2; d < D; d += 64) *reinterpret_cast<uint32_t*>(row + d) = 0u;
+      }
+    }
+    __syncthreads();
+    if (has_newest && head_tile == 0 && slot >= 0) {
+      const size_t page = slot >> p.page_shift, in_page = slot & p.page_mask;
+      const size_t at = (((page * p.Hkv + kvh) << p.page_shift) + in_page) * D;
+      for (int d = threadIdx.x * 2; d < 2 * D; d += THREADS * 2) {
+        bf16* dst = d < D ? p.k_cache_out + at + d : p.v_cache_out + at + (d - D);
+        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(newest_kv + d);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < 16 * CH; i += THREADS) {
+      const int r = i / CH, c = i % CH;
+      const bool valid = r < ng;
+      const bf16* src = valid ? p.q + ((size_t)q_begin * p.H + kvh * G + g0 + r) * D + c * 8 : p.q;
+      cp_async16(smem_u32(Qs + r * ROW_BYTES + c * 16), src, valid);
+    }
   }
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles && tile_begin + s == newest_tile)
+    if (s < n_tiles && tile_begin + s == late_tile)
       load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
     // the first group holds the query and all of these tiles; the others stay empty, so that the
     // loop below finds as many groups as it counts on
@@ -388,11 +560,20 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < n_tiles) {
       const int nb = nxt % DEC_STAGES;
-      load_kv_tile<BN, THREADS>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_hi);
+      load_kv_tile<BN, THREADS>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_load);
     }
     cp_async_commit();
     cp_async_wait<DEC_STAGES - 1>();
     __syncthreads();
+    if (has_newest && tile_begin + it == newest_tile) {
+      // the newest key and value take their row of the tile (the copy left zeros there)
+      const int row = qpos - newest_tile * BN, buf_n = it % DEC_STAGES;
+      for (int d = threadIdx.x * 2; d < 2 * D; d += THREADS * 2) {
+        char* dst = (d < D ? Ks : Vs) + (size_t)buf_n * BN * ROW_BYTES + row * ROW_BYTES + (d < D ? d : d - D) * 2;
+        *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(newest_kv + d);
+      }
+      __syncthreads();
+    }
     if (Q_IN_REGS && it == 0) {
       const int mi = lane >> 3, r = lane & 7;
 #pragma unroll
@@ -581,6 +762,15 @@ TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 // a mixed batch and their tokens (the scratch then has num_tiles rows in place of T).
 // counters: num_requests * Hkv * ceil(group / 16) zeroed ints (they return to zero); with them the
 // key ranges are merged inside the decode kernel, without them by a second launch.
+namespace {
+int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void* out, const void* k_cache,
+                             const void* v_cache, const int* block_table, const int* cu_q, const int* kv_lens,
+                             int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
+                             int max_blocks, float scale, int window, int num_splits, float* part_o,
+                             float* part_ml, int* counters, int decode_only, const int* tile_req,
+                             const int* tile_q0, int num_tiles, int tile_queries, cudaStream_t stream);
+}
+
 TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
                                      const int* block_table, const int* cu_q, const int* kv_lens,
                                      int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
@@ -588,6 +778,56 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int num_splits, float* part_o, float* part_ml, int* counters,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
                                      int tile_queries, cudaStream_t stream) {
+  return paged_attention_mma_impl(nullptr, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
+                                  num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
+                                  part_o, part_ml, counters, decode_only, tile_req, tile_q0, num_tiles,
+                                  tile_queries, stream);
+}
+
+// Decode (every request brings one token) straight from the fused q/k/v projection: qkv
+// [T, (H + 2 Hkv) * D] bfloat16, or null with the projection's split-K partial tiles (partials,
+// splits, n_tiles, t_tiles, tile_t as gemm_tcgen05.cu leaves them).  The kernel applies the
+// per-head RMSNorm (q_weight, k_weight of D elements, bfloat16 or float; null: none) and the
+// rotary encoding (cos, sin [positions, D / 2], pairing (j, j + D / 2) over the whole head) itself
+// and writes the token's key and value to slot_mapping[t] of the caches.  merge: 1 a combine
+// launch (scratch as for ts_paged_attention_mma), 2 clusters (up to 8 key ranges).
+TS_EXPORT int ts_paged_attention_mma_from_qkv(const void* qkv, const float* partials, int splits, int n_tiles,
+                                              int t_tiles, int tile_t, const int* positions,
+                                              const int* slot_mapping, const float* cos, const float* sin,
+                                              const void* q_weight, const void* k_weight, int weight_is_f32,
+                                              float eps, void* out, void* k_cache, void* v_cache,
+                                              const int* block_table, const int* cu_q, const int* kv_lens,
+                                              int num_tokens, int num_requests, int H, int Hkv, int page_size,
+                                              int max_blocks, float scale, int window, int num_splits,
+                                              float* part_o, float* part_ml, int merge, cudaStream_t stream) {
+  TS_REQUIRE((qkv != nullptr) != (partials != nullptr), "paged_attention_mma_from_qkv: the projection or its partial tiles");
+  TS_REQUIRE(partials == nullptr || (splits > 0 && n_tiles * 128 >= (H + 2 * Hkv) * D && tile_t > 0),
+             "paged_attention_mma_from_qkv: partial tiles do not fit the row length");
+  TS_REQUIRE(positions && slot_mapping && cos && sin && k_cache && v_cache,
+             "paged_attention_mma_from_qkv: positions, slots, rotary tables and caches are needed");
+  TS_REQUIRE((q_weight == nullptr) == (k_weight == nullptr), "paged_attention_mma_from_qkv: q and k norm weights come together");
+  TS_REQUIRE(merge == 1 || merge == 2, "paged_attention_mma_from_qkv: merge is 1 (launch) or 2 (cluster)");
+  MmaAttnParams extra = {};
+  extra.from_qkv = 1;
+  extra.qkv = static_cast<const bf16*>(qkv);
+  extra.ps = PartialSrc{partials, splits, n_tiles, t_tiles, tile_t};
+  extra.positions = positions; extra.slot_mapping = slot_mapping;
+  extra.rope_cos = cos; extra.rope_sin = sin;
+  extra.q_weight = VecParam{q_weight, weight_is_f32}; extra.k_weight = VecParam{k_weight, weight_is_f32};
+  extra.has_norm = q_weight != nullptr; extra.eps = eps;
+  extra.k_cache_out = static_cast<bf16*>(k_cache); extra.v_cache_out = static_cast<bf16*>(v_cache);
+  return paged_attention_mma_impl(&extra, nullptr, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
+                                  num_requests, 1, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o,
+                                  part_ml, nullptr, merge, nullptr, nullptr, 0, 0, stream);
+}
+
+namespace {
+int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void* out, const void* k_cache,
+                             const void* v_cache, const int* block_table, const int* cu_q, const int* kv_lens,
+                             int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
+                             int max_blocks, float scale, int window, int num_splits, float* part_o,
+                             float* part_ml, int* counters, int decode_only, const int* tile_req,
+                             const int* tile_q0, int num_tiles, int tile_queries, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
@@ -595,7 +835,7 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   TS_REQUIRE(num_splits == 1 || (decode_only && ((part_o && part_ml) || (decode_only == 2 && num_splits <= 8 && !counters))),
              "paged_attention_mma: splits are for decode and need scratch");
   TS_REQUIRE(num_requests <= 65535, "paged_attention_mma: more than 65535 requests");
-  MmaAttnParams p;
+  MmaAttnParams p = from_qkv ? *from_qkv : MmaAttnParams{};
   p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.counters = counters;
@@ -658,3 +898,5 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
   TS_LAUNCH("attn_prefill", attn_prefill_kernel, grid, PRE_THREADS, smem, stream, p);
   return 0;
 }
+}  // namespace
+

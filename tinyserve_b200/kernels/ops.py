@@ -453,15 +453,15 @@ GATED_EPILOGUE = os.environ.get("TINYSERVE_GATED_EPILOGUE", "1") != "0"
 def gated_linear(x, weight, activation="silu", block=0):
     """act(gate) * up of x @ weight^T, [M, N / 2].  weight [N, K] holds gate rows then up rows
     (``block`` 0) or alternates them in blocks of ``block`` rows.  With blocks of GATED_BLOCK, up
-    to 64 tokens and a product that needs no cut along K, the tcgen05 product does the activation
-    in its epilogue; otherwise the product is followed by the activation kernel.  x may be the
+    to FUSED_MAX_TOKENS tokens and a product that needs no cut along K, the tcgen05 product does
+    the activation in its epilogue; otherwise the product is followed by the activation kernel.  x may be the
     ScaledRows that add_rmsnorm returned."""
     rows = x.data if isinstance(x, ScaledRows) else x
     N, K = weight.shape
     if (GATED_EPILOGUE and block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05"
             and TCGEN05_FORM == "tiled" and _tcgen05_ok(rows, weight, None)
-            and (rows is x or rows.shape[0] <= FUSED_MAX_TOKENS)
+            and rows.shape[0] <= FUSED_MAX_TOKENS          # measured: at 64 tokens the epilogue costs 9 % of the step
             and gemm_splits(rows.shape[0], N, K) == 1):
         _cuda(rows, weight)
         return _linear_tcgen05(rows, weight, False, splits=1, gated=ACTIVATIONS[activation] + 1,
@@ -692,6 +692,58 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         c_int(H), c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)),
         c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _stream()),
         launches)
+    return out
+
+
+#: decode steps: let the attention kernel take the fused q/k/v projection itself (per-head norm,
+#: rotary and the cache write happen inside it; one kernel fewer per layer)
+FUSED_DECODE_QKV = os.environ.get("TINYSERVE_FUSED_DECODE_QKV", "1") != "0"
+
+
+def attention_from_qkv(qkv, positions, num_heads, num_kv_heads, head_dim, rotary, q_weight, k_weight, eps,
+                       k_cache, v_cache, view, ctx, scale, window=0, write_cache=True):
+    """Per-head norm of q and k, rotary encoding, cache write of k and v, attention over the cache:
+    qkv [T, (H + 2 Hkv) * D] (a tensor, or the SplitPartials of the projection) -> [T, H, D].
+    Two kernels (qk_norm_rope_kvwrite, paged_attention), or, when every request brings one token
+    (bfloat16, full-width rotary with the (j, j + D/2) pairing), the decode kernel alone: it makes
+    its query rows and the newest key and value itself."""
+    dtype = qkv.dtype
+    H, Hkv, D = num_heads, num_kv_heads, head_dim
+    plain = isinstance(qkv, torch.Tensor)
+    # (up to FUSED_MAX_TOKENS requests: measured, at 64 the separate kernel is 4 % of the step faster)
+    fused = (FUSED_DECODE_QKV and write_cache and dtype == torch.bfloat16 and ctx.max_q_len == 1
+             and qkv.shape[0] <= FUSED_MAX_TOKENS
+             and BF16_ATTENTION in ("mma", "tcgen05") and D in SUPPORTED_HEAD_DIMS and D <= MMA_MAX_HEAD_DIM
+             and rotary is not None and rotary.rotary_dim == D and not rotary.interleaved
+             and DECODE_MERGE != "kernel" and (q_weight is None) == (k_weight is None)
+             and k_cache is not None and k_cache.dtype == torch.bfloat16
+             and (isinstance(qkv, SplitPartials) or (plain and qkv.is_contiguous()))
+             and (q_weight is None or q_weight.dtype == k_weight.dtype))
+    if not fused:
+        q = qk_norm_rope_kvwrite(qkv, positions, H, Hkv, D, rotary=rotary, q_weight=q_weight, k_weight=k_weight,
+                                 eps=eps, k_cache=k_cache, v_cache=v_cache,
+                                 slot_mapping=view.slot_mapping if write_cache else None, page_size=view.page_size)
+        return paged_attention(q, k_cache, v_cache, view, ctx, scale, window)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (H + 2 * Hkv) * D:
+        raise ValueError("qkv must be [T, (H + 2 Hkv) * D]")
+    parts = _NO_PARTIALS if plain else qkv.args()
+    _cuda(qkv if plain else None, positions, k_cache, v_cache, view.slot_mapping, view.block_table, rotary.cos, rotary.sin)
+    out = torch.empty(T, H, D, dtype=dtype, device=qkv.device)
+    num_splits = decode_splits(ctx.num_requests, ctx.max_kv_len, H, Hkv)
+    cluster = DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    part_o = part_ml = None
+    if num_splits > 1 and not cluster:
+        part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty(T * H * num_splits * 2, dtype=torch.float32, device=qkv.device)
+    lib = _attention_mma(D)
+    _check(lib, lib.ts_paged_attention_mma_from_qkv(
+        _ptr(qkv) if plain else None, *parts, _ptr(positions), _ptr(view.slot_mapping), _ptr(rotary.cos),
+        _ptr(rotary.sin), _ptr(q_weight), _ptr(k_weight), c_int(_vec_flag(q_weight, dtype) if q_weight is not None else 0),
+        c_float(eps), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
+        _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(H), c_int(Hkv), c_int(view.page_size),
+        c_int(view.block_table.stride(0)), c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o),
+        _ptr(part_ml), c_int(2 if cluster else 1), _stream()), 2 if num_splits > 1 and not cluster else 1)
     return out
 
 

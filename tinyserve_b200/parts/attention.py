@@ -61,16 +61,12 @@ class Attention(Mixer):
         qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"), allow_partials=True)
         cache = ctx.cache(call.cache)
         view = ctx.group(cache.group)
-        q = ops.qk_norm_rope_kvwrite(
-            qkv, ctx.positions, self.num_heads, self.num_kv_heads, self.head_dim,
-            rotary=self.position,
-            q_weight=self.q_norm.w["weight"] if self.q_norm is not None else None,
-            k_weight=self.k_norm.w["weight"] if self.k_norm is not None else None,
-            eps=self.q_norm.eps if self.q_norm is not None else 0.0,
-            k_cache=cache.k, v_cache=cache.v,
-            slot_mapping=view.slot_mapping if call.writes_cache else None,
-            page_size=view.page_size)
-        out = ops.paged_attention(q, cache.k, cache.v, view, ctx, self.scale, self.window)
+        out = ops.attention_from_qkv(
+            qkv, ctx.positions, self.num_heads, self.num_kv_heads, self.head_dim, self.position,
+            self.q_norm.w["weight"] if self.q_norm is not None else None,
+            self.k_norm.w["weight"] if self.k_norm is not None else None,
+            self.q_norm.eps if self.q_norm is not None else 0.0,
+            cache.k, cache.v, view, ctx, self.scale, self.window, write_cache=call.writes_cache)
         return ops.linear(out.view(out.shape[0], self.q_size), self.w["o_proj.weight"], allow_pending=True)
 
 
