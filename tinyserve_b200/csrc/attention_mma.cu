@@ -490,6 +490,10 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   for (int s = 0; s < DEC_STAGES - 1; ++s)
     if (s < n_tiles && tile_begin + s != late_tile)
       load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_load);
+  // the timeline build follows the blocks of one (request, KV group): marks 40.. with the key
+  // range as their value
+  const bool traced = blockIdx.x == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+  if (traced) timeline_mark_thread(40, split);          // first tiles on their way
   int slot = -1;
   HeadConsts hq, hk;
   if (from_qkv) {
@@ -500,7 +504,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     hk = hq;
     if (has_newest) load_weights(hk, p.k_weight, p.has_norm, lane);
   }
+  if (traced) timeline_mark_thread(41, split);          // constants fetched
   pdl_wait();
+  if (traced) timeline_mark_thread(42, split);          // the projection is there
   if (from_qkv) {
     // the heads this block makes, dealt to the warps in turn: the newest key (norm, rotary) and
     // value where this block holds them, then the query rows; rows past the group are zero
@@ -543,6 +549,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     // loop below finds as many groups as it counts on
     cp_async_commit();
   }
+  if (traced) timeline_mark_thread(43, split);          // query rows (and the newest key) made
   int pos[2], lo[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -592,6 +599,7 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   }
   cp_async_wait<0>();
   __syncthreads();
+  if (traced) timeline_mark_thread(44, split);          // all key tiles done
 
   // merge the four warps' partial softmax through shared memory (the K buffers are free now)
   float* sm_o = reinterpret_cast<float*>(Ks);                  // [4][16][D]
@@ -678,9 +686,11 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
         }
       p.out[((size_t)q_begin * p.H + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
+    if (traced) timeline_mark_thread(45, split);        // merged and stored
     // no block leaves while a peer may still read its shared memory
     cluster_arrive();
     cluster_wait();
+    if (traced) timeline_mark_thread(46, split);
     return;
   }
   if (p.num_splits == 1 || p.counters == nullptr) return;

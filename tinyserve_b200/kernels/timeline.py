@@ -60,6 +60,7 @@ def main(argv=None):
     ap.add_argument("--intermediate", type=int, default=12288)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--kernels", type=int, default=20, help="how many launches to print")
+    ap.add_argument("--marks", action="store_true", help="also print the kernels' own marks of their traced blocks")
     a = ap.parse_args(argv)
     if os.environ.get("TINYSERVE_TIMELINE", "0") != "1":
         print("set TINYSERVE_TIMELINE=1: the kernels record nothing otherwise", file=sys.stderr)
@@ -103,6 +104,15 @@ def main(argv=None):
         grid, threads = launch["key"]
         print(f"{str(grid):>16} x {threads:<5} {len(launch['start']):5d} | {us(launch['start'], min)} {us(launch['start'], max)} |"
               f" {us(launch[1], min)} {us(launch[1], max)} | {us(launch[2], max)} | {us(launch[3], max)}")
+    marks = records[records["tag"] >= 10]
+    if a.marks and len(marks):
+        # the kernels' own marks (one traced block or group of blocks per launch) inside the window shown
+        t_lo, t_hi = base, max(max(launch["start"]) for launch in launches[first:first + a.kernels])
+        print("marks of traced blocks (us, tag, value, grid):")
+        for r in marks:
+            if t_lo <= int(r["ns"]) <= t_hi + 20000:
+                print(f"{(int(r['ns']) - base) / 1e3:8.2f}  tag {int(r['tag']):3d}  value {int(r['pad']):3d}  "
+                      f"{tuple(int(v) for v in r['grid'])}")
     return 0
 
 
