@@ -170,3 +170,170 @@ def test_toy_mixer_with_state_runs_through_the_engine(dtype, tol, tmp_path):
     finally:
         ARCHITECTURES.pop("ToyDecayForCausalLM", None)
         MIXERS.pop("toy_decay", None)
+
+
+# ----------------------------------------------------------------------------- routing, positions
+def _register_routed():
+    """A toy feed-forward with top-1 routing over small experts (router logits in 32-bit) and a
+    toy position encoding (rotary tables with linearly spaced frequencies and a position scale),
+    both defined here, beside the package's attention."""
+    from tinyserve_b200.config import (LayerCall, LayerSpec, ModelConfig, ModelSpec, PartSpec,
+                                       register_architecture)
+    from tinyserve_b200.kernels import ops
+    from tinyserve_b200.parts import FeedForward, ParamSpec
+    from tinyserve_b200.parts.base import PositionEncoding, register_feed_forward, register_position_encoding
+
+    class RoutedFFN(FeedForward):
+        """y_t = down_e(gelu(up_e(x_t))) * p_e with e = argmax of the router's 32-bit logits and
+        p_e its softmax probability: routing by data, experts as stacked tensors."""
+        tree_name = "moe"
+
+        def __init__(self, hidden_size, expert_size, num_experts):
+            super().__init__()
+            self.h, self.i, self.e = hidden_size, expert_size, num_experts
+
+        def param_specs(self):
+            return {"router.weight": ParamSpec((self.e, self.h)),
+                    "up.weight": ParamSpec((self.e * self.i, self.h)),
+                    "down.weight": ParamSpec((self.e * self.h, self.i))}
+
+        def forward(self, h, ctx):
+            logits = h.float() @ self.w["router.weight"].float().T
+            prob, expert = logits.softmax(-1).max(-1)
+            up = self.w["up.weight"].view(self.e, self.i, self.h)
+            down = self.w["down.weight"].view(self.e, self.h, self.i)
+            out = torch.zeros_like(h)
+            for e in expert.unique().tolist():
+                rows = (expert == e).nonzero().squeeze(-1)
+                mid = torch.nn.functional.gelu(ops.materialize(ops.linear(h[rows].contiguous(), up[e])).float(),
+                                               approximate="tanh").to(h.dtype)
+                y = ops.materialize(ops.linear(mid, down[e]))
+                out[rows] = (y.float() * prob[rows, None]).to(h.dtype)
+            return out
+
+    class LinearRotary(PositionEncoding):
+        """Rotary tables with frequencies 1 / (1 + k) and positions divided by ``scale``: the
+        attention part and its kernels only see rotary_dim, the pairing and the two tables."""
+
+        def __init__(self, rotary_dim, scale):
+            super().__init__()
+            self.rotary_dim, self.scale, self.interleaved = rotary_dim, float(scale), False
+            self.cos = self.sin = None
+
+        def prepare(self, runtime):
+            freq = 1.0 / (1.0 + torch.arange(self.rotary_dim // 2, dtype=torch.float64))
+            ang = torch.outer(torch.arange(runtime.max_positions, dtype=torch.float64) / self.scale, freq)
+            self.cos, self.sin = ang.cos().float().to(runtime.device), ang.sin().float().to(runtime.device)
+
+    @dataclass(frozen=True)
+    class RoutedConfig(ModelConfig):
+        architecture: ClassVar[str] = "ToyRoutedForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+        experts: int = 0
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"], raw["experts"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size,
+                    "hidden_size": self.hidden_size, "experts": self.experts}
+
+        def model_spec(self):
+            h = self.hidden_size
+            norm = PartSpec("rmsnorm", {"eps": 1e-6})
+            attn = PartSpec("attention", {
+                "hidden_size": h, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16,
+                "position": PartSpec("toy_linear_rotary", {"rotary_dim": 16, "scale": 2.0})})
+            routed = PartSpec("toy_routed", {"hidden_size": h, "expert_size": 24, "num_experts": self.experts})
+            dense = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 64, "activation": "silu"})
+            layers = (LayerSpec(attn, routed, norm), LayerSpec(attn, dense, norm))
+            return ModelSpec(self.vocab_size, h, layers, (LayerCall(0, 0), LayerCall(1, 1)), norm, False)
+
+    register_feed_forward("toy_routed", RoutedFFN)
+    register_position_encoding("toy_linear_rotary", LinearRotary)
+    register_architecture(RoutedConfig.architecture, RoutedConfig)
+    return RoutedConfig
+
+
+def _plain_routed(weights, cfg, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T, h, H, Hkv, D = len(ids), cfg.hidden_size, 4, 2, 16
+    norm = lambda x, wt: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * wt
+    r = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    freq = 1.0 / (1.0 + torch.arange(D // 2, dtype=torch.float64))
+    ang = torch.outer(torch.arange(T, dtype=torch.float64) / 2.0, freq)
+    c, s = ang.cos().float().double()[:, None], ang.sin().float().double()[:, None]
+
+    def rope(z):
+        a, b = z[..., :D // 2], z[..., D // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    def attention(x, p):
+        q = rope((x @ w[p + "q_proj.weight"].T).view(T, H, D))
+        k = rope((x @ w[p + "k_proj.weight"].T).view(T, Hkv, D))
+        v = (x @ w[p + "v_proj.weight"].T).view(T, Hkv, D)
+        k, v = k.repeat_interleave(H // Hkv, 1), v.repeat_interleave(H // Hkv, 1)
+        sc = torch.einsum("thd,shd->hts", q, k) * D ** -0.5
+        mask = torch.arange(T)[None] <= torch.arange(T)[:, None]
+        o = torch.einsum("hts,shd->thd", sc.masked_fill(~mask[None], float("-inf")).softmax(-1), v)
+        return o.reshape(T, H * D) @ w[p + "o_proj.weight"].T
+
+    def routed(x, p, experts_of):
+        logits = x @ w[p + "router.weight"].T
+        prob, expert = logits.softmax(-1).max(-1)
+        experts_of.append(expert)
+        up = w[p + "up.weight"].view(cfg.experts, 24, h)
+        down = w[p + "down.weight"].view(cfg.experts, h, 24)
+        rows = [torch.nn.functional.gelu(x[t] @ up[expert[t]].T, approximate="tanh") @ down[expert[t]].T * prob[t]
+                for t in range(T)]
+        return torch.stack(rows)
+
+    def dense(x, p):
+        g, u = x @ w[p + "gate_proj.weight"].T, x @ w[p + "up_proj.weight"].T
+        return (g / (1 + torch.exp(-g)) * u) @ w[p + "down_proj.weight"].T
+
+    chosen = []
+    for layer in (0, 1):
+        p = f"model.layers.{layer}."
+        r = r + attention(norm(r, w[p + "input_layernorm.weight"]), p + "self_attn.")
+        x = norm(r, w[p + "post_attention_layernorm.weight"])
+        r = r + (routed(x, p + "moe.", chosen) if layer == 0 else dense(x, p + "mlp."))
+    return norm(r, w["model.norm.weight"]) @ w["lm_head.weight"].T, chosen[0]
+
+
+def test_toy_routed_feed_forward_and_position_encoding_run_through_the_engine(tmp_path):
+    """float32, so that the engine and the plain form route every token to the same expert."""
+    import os
+    from safetensors.torch import load_file
+    from tinyserve_b200.config import ARCHITECTURES, EngineConfig
+    from tinyserve_b200.engine.batch import StepEntry
+    from tinyserve_b200.engine.runner import ModelRunner
+    from tinyserve_b200.parts.base import FEED_FORWARDS, POSITION_ENCODINGS
+    from tinyserve_b200.weights import write_random_model
+    RoutedConfig = _register_routed()
+    try:
+        cfg = RoutedConfig(vocab_size=83, hidden_size=48, experts=5)
+        folder = write_random_model(cfg, str(tmp_path), seed=5, store_dtype="float32")
+        weights = load_file(os.path.join(folder, "model.safetensors"))
+        # a router that matters: spread its logits, so that several experts are chosen
+        assert weights["model.layers.0.moe.up.weight"].shape == (5 * 24, 48)
+        runner = ModelRunner(EngineConfig(model=folder, dtype="float32", max_model_len=96, block_size=8,
+                                          max_num_seqs=2, max_num_batched_tokens=64, num_blocks=20))
+        ids = random_ids(83, 45, seed=4)
+        ref, experts = _plain_routed(weights, cfg, ids)
+        assert len(experts.unique()) >= 2, "the routing is not trivial"
+        mgr = runner.manager
+        mgr.begin("a")
+        got = [runner.step([StepEntry("a", ids[:30], list(range(30)))]),
+               runner.step([StepEntry("a", ids[30:32], [0, 1])])]
+        got += [runner.step([StepEntry("a", [ids[t]], [0])]) for t in range(32, 45)]
+        mgr.free("a")
+        got = torch.cat(got).double().cpu()
+        assert (got - ref).abs().max().item() < 2e-5 * ref.abs().max().item()
+        mgr.check_invariants()
+    finally:
+        ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
+        FEED_FORWARDS.pop("toy_routed", None)
+        POSITION_ENCODINGS.pop("toy_linear_rotary", None)
