@@ -198,6 +198,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
       constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
+      const uint64_t q_desc = smem_desc(smem_u32(Qs)), k_desc = smem_desc(smem_u32(Ks));
+      const uint64_t v_desc = smem_desc_mn(smem_u32(Vs), CHUNK_BYTES);
       // S_g = Q_g K^T of key tile t
       auto scores = [&](int g, int t) -> bool {
         const int s = t % K_STAGES;
@@ -206,11 +208,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (!mbar_wait(smem_u32(&k_full[s]), (t / K_STAGES) & 1, abort_flag)) return false;
         tcgen05_fence_after();
         if (traced) timeline_mark_thread(10 + g, t);
-        const uint32_t qa = smem_u32(Qs + g * Q_BYTES), ka = smem_u32(Ks + s * KV_BYTES);
+        // descriptors: a base made once, plus the operand's offset in 16-byte units (the address is
+        // the descriptor's low field; shared memory ends below its range).  The issuing thread is
+        // one serial chain of instructions: whatever it computes per MMA delays every MMA.
+        const uint64_t qd = q_desc + g * (Q_BYTES >> 4), kd = k_desc + s * (KV_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          umma(tmem_base + g * BN, smem_desc(qa + (k / 4) * CHUNK_BYTES + (k % 4) * 32),
-               smem_desc(ka + (k / 4) * CHUNK_BYTES + (k % 4) * 32), idesc_qk, k > 0 ? 1u : 0u);
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t off = ((k / 4) * CHUNK_BYTES + (k % 4) * 32) >> 4;
+          umma(tmem_base + g * BN, qd + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
+        }
         tcgen05_commit(smem_u32(&s_full[g]));
         if (g == groups - 1) tcgen05_commit(smem_u32(&k_empty[s]));
         return true;
@@ -223,11 +229,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           return false;
         tcgen05_fence_after();
         if (traced) timeline_mark_thread(12 + g, t);
-        const uint32_t va = smem_u32(Vs + s * KV_BYTES);
+        const uint64_t vd = v_desc + s * (KV_BYTES >> 4);
+        const uint32_t o_addr = tmem_base + 2 * BN + g * 128, p_addr = tmem_base + g * BN;
 #pragma unroll
         for (int k = 0; k < BN / 16; ++k)
-          umma_ts(tmem_base + 2 * BN + g * 128, tmem_base + g * BN + k * 8,
-                  smem_desc_mn(va + k * 16 * 128, CHUNK_BYTES), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+          umma_ts(o_addr, p_addr + k * 8, vd + ((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
         tcgen05_commit(smem_u32(&o_ready[g]));
         if (g == groups - 1) tcgen05_commit(smem_u32(&v_empty[s]));
         return true;

@@ -172,17 +172,18 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // issuer: four MMAs of K = 16 per stage
     pdl_wait();
     const uint32_t idesc = instr_desc(TILE_T);
+    const uint64_t desc0 = smem_desc(smem_u32(smem));
     bool ok = true;
     for (int i = 0; i < nkb && ok; ++i) {
       const int s = i % C::STAGES;
       ok = mbar_wait(smem_u32(&full[s]), (i / C::STAGES) & 1, abort_flag);
       if (!ok) break;
       tcgen05_fence_after();
-      const uint32_t a0 = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-      const uint32_t b0 = a0 + W_STAGE_BYTES;
+      // one descriptor per operand and stage; a K step of 16 is 32 bytes = 2 address units on
+      const uint64_t ad = desc0 + (uint64_t)s * (C::STAGE_BYTES >> 4), bd = ad + (W_STAGE_BYTES >> 4);
 #pragma unroll
       for (int k = 0; k < BK / 16; ++k)
-        umma(tmem_base + (k % Accs<TILE_T>::N) * TILE_T, smem_desc(a0 + k * 32), smem_desc(b0 + k * 32), idesc,
+        umma(tmem_base + (k % Accs<TILE_T>::N) * TILE_T, ad + 2 * k, bd + 2 * k, idesc,
              (i > 0 || k >= Accs<TILE_T>::N) ? 1u : 0u);
       tcgen05_commit(smem_u32(&empty[s]));
     }
