@@ -806,7 +806,7 @@ __global__ void qk_norm_rope_kvwrite_rows4_kernel(const T* __restrict__ qkv, T* 
                                                   T* __restrict__ v_cache,
                                                   const int* __restrict__ slot_mapping, int page_size,
                                                   int heads_total) {
-  constexpr int D = LPH * 8, HALF = D / 2, HPW = 32 / LPH, U = 2;
+  constexpr int D = LPH * 8, HALF = D / 2, HPW = 32 / LPH, U = 3;
   pdl_trigger();
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane / LPH, j = 4 * (lane % LPH);
