@@ -295,7 +295,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           mx4[3] = fmaxf(mx4[3], sv[e + 3]);
         }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float m_new = fmaxf(m, mx * p.scale_log2);
+        // The reference maximum only moves when the row's maximum has grown by more than 2^8:
+        // until then the probabilities are taken against the old reference (at most 256, exact
+        // enough in bfloat16 and harmless in the 32-bit sums) and O needs no rescaling; the final
+        // division by the row sum, kept against the same reference, gives the same result.
+        const float m_cand = fmaxf(m, mx * p.scale_log2);
+        const float m_new = (m_cand - m <= 8.f) ? m : m_cand;      // -inf - -inf: moves (to -inf), harmless
         const float m_safe = m_new == -INFINITY ? 0.f : m_new;
         const float alpha = ex2(m - m_safe);
         // (these scores were computed after the previous key tile's P V of this query tile, in
