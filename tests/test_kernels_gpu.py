@@ -343,14 +343,19 @@ def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("source", ["tensor", "partials"])
 @pytest.mark.parametrize("merge", ["cluster", "launch"])
-def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, merge, monkeypatch):
+@pytest.mark.parametrize("lengths", ["mixed", "long"])
+def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, merge, lengths, monkeypatch):
     """Decode steps hand the fused q/k/v projection to the attention kernel, which applies the
     per-head norm and the rotary encoding and writes the newest key and value itself: the same
     outputs and the same cache as the norm/rotary kernel followed by the attention kernel."""
     from tinyserve_b200.parts.rotary import Rotary
     o = ops()
     monkeypatch.setattr(o, "DECODE_MERGE", merge)
-    kv_lens = [1, 64, 65, 300, 129, 700, 17, 128]
+    # "long": two requests with so many keys that there are more key ranges than a cluster takes
+    kv_lens_of = {"mixed": [1, 64, 65, 300, 129, 700, 17, 128], "long": [3000, 2177]}
+    if lengths == "long" and (merge == "launch" or source == "tensor"):
+        pytest.skip("one pass over the long contexts is enough")
+    kv_lens = kv_lens_of[lengths]
     B, width = len(kv_lens), (H + 2 * Hkv) * D
     K = 256
     x, w = rnd(B, K, seed=1, dtype=torch.bfloat16), rnd(width, K, seed=2, dtype=torch.bfloat16, scale=0.2)
@@ -363,9 +368,10 @@ def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, m
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=4)
     pos = torch.tensor([n - 1 for n in kv_lens], dtype=torch.int32).cuda()
     slots = torch.stack([table[b, (n - 1) // page] * page + (n - 1) % page for b, n in enumerate(kv_lens)]).int().cuda()
-    slots[6] = -1                      # this request writes nothing (its newest key is still used)
+    dropped = 6 if B > 6 else 1
+    slots[dropped] = -1                # this request writes nothing (its newest key is still used)
     rot = Rotary(D, 1e4, "half")
-    rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(D, 1e4, 1024))
+    rot.cos, rot.sin = (t.cuda() for t in Rotary.tables(D, 1e4, 4096))
     qw, kw = rnd(D, seed=5, dtype=torch.float32) + 1, rnd(D, seed=6, dtype=torch.float32) + 1
     cu = torch.arange(B + 1, dtype=torch.int32).cuda()
     ctx = SimpleNamespace(cu_q=cu, kv_lens=torch.tensor(kv_lens, dtype=torch.int32).cuda(), num_requests=B,
@@ -380,11 +386,42 @@ def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, m
         results.append((out, kc_i, vc_i, o.launch_count() - launches))
     (out_f, kc_f, vc_f, n_f), (out_u, kc_u, vc_u, n_u) = results
     assert n_f < n_u, "fewer kernels"
-    live = [b for b in range(B) if b != 6]
+    live = [b for b in range(B) if b != dropped]
     assert torch.equal(kc_f, kc_u) and torch.equal(vc_f, vc_u), "the same cache, bit by bit"
     assert (out_f[live].float() - out_u[live].float()).abs().max().item() <= 2.0 ** -7 * out_u.float().abs().max().item()
     # the request without a slot: the two-kernel path reads a stale key there, the fused one its own
     assert torch.isfinite(out_f.float()).all()
+
+
+@pytest.mark.parametrize("D,H,Hkv", [(128, 8, 2), (64, 6, 1)])
+@pytest.mark.parametrize("window", [0, 700])
+def test_prefill_attention_long_prompt(D, H, Hkv, window, bf16_attention):
+    """A prompt of 2,500 tokens after a prefix of 300 (20 and more key tiles per block, uneven last
+    query block), beside a short request; the reference runs on the GPU in 32-bit."""
+    if bf16_attention == "simt":
+        pytest.skip("the 32-bit kernel has its own tests")
+    page = 16
+    kv_lens, q_lens = [2800, 75], [2500, 75]
+    k = [rnd(n, Hkv, D, seed=70 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
+    v = [rnd(n, Hkv, D, seed=80 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
+    q = rnd(sum(q_lens), H, D, seed=33, dtype=torch.bfloat16)
+    kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 4, seed=6)
+    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None)
+    want, at = [], 0
+    for kb, vb, n in zip(k, v, q_lens):
+        S = kb.shape[0]
+        qq = q[at:at + n].float()                                       # [n, H, D]
+        kk = kb.cuda().float().repeat_interleave(H // Hkv, 1)             # [S, H, D]
+        vv = vb.cuda().float().repeat_interleave(H // Hkv, 1)
+        sc = torch.einsum("thd,shd->hts", qq, kk) * D ** -0.5
+        pos = torch.arange(S - n, S, device="cuda")[:, None]
+        j = torch.arange(S, device="cuda")[None]
+        vis = (j <= pos) & ((j > pos - window) if window else True)
+        want.append(torch.einsum("hts,shd->thd", sc.masked_fill(~vis[None], float("-inf")).softmax(-1), vv))
+        at += n
+    close(out, torch.cat(want), torch.bfloat16, "long prompt")
+    if bf16_attention == "tcgen05":
+        assert ops().attention_tcgen05_error(D) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
