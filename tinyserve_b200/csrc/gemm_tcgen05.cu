@@ -83,7 +83,7 @@ __device__ __forceinline__ void tmem_load8_sum(uint32_t addr, float (&v)[8]) {
 template <int TILE_T> struct Cfg {
   static constexpr int X_STAGE_BYTES = TILE_T * BK * 2;
   static constexpr int STAGE_BYTES = W_STAGE_BYTES + X_STAGE_BYTES;
-  // two blocks share an SM: stay below ~100 KB of stages
+  // two blocks share an SM: the ring and the barriers of a block stay below 113 KB
   static constexpr int RING = TS_GEMM_RING_KB * 1024;
   static constexpr int STAGES = RING / STAGE_BYTES < 2 ? 2 : (RING / STAGE_BYTES > 8 ? 8 : RING / STAGE_BYTES);
   static constexpr int TMEM_COLS = Accs<TILE_T>::N * TILE_T < 32 ? 32 : Accs<TILE_T>::N * TILE_T;
@@ -324,41 +324,41 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = scaled ? v[i] * row_scale[c + i] : v[i];
     }
     if (p.out != nullptr) {
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      const int before = atomicAdd(&p.counters[tile], 1);
-      *is_last = before == p.splits - 1;
-      if (*is_last) p.counters[tile] = 0;
-    }
-    __syncthreads();
-    if (*is_last) {
       __threadfence();
-      const float* base = p.partials + (size_t)tile * (TILE_T * TILE_N);
-      const size_t split_stride = (size_t)tiles * (TILE_T * TILE_N);
-      // eight columns at a time, so that eight chains of loads are in flight per thread
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const int before = atomicAdd(&p.counters[tile], 1);
+        *is_last = before == p.splits - 1;
+        if (*is_last) p.counters[tile] = 0;
+      }
+      __syncthreads();
+      if (*is_last) {
+        __threadfence();
+        const float* base = p.partials + (size_t)tile * (TILE_T * TILE_N);
+        const size_t split_stride = (size_t)tiles * (TILE_T * TILE_N);
+        // eight columns at a time, so that eight chains of loads are in flight per thread
 #pragma unroll 1
-      for (int c0 = 0; c0 < TILE_T && t0 + c0 < p.M; c0 += 8) {
-        float sum[8];
+        for (int c0 = 0; c0 < TILE_T && t0 + c0 < p.M; c0 += 8) {
+          float sum[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sum[i] = 0.f;
-        for (int s = 0; s < p.splits; ++s) {
-          const float* src = base + s * split_stride + c0 * TILE_N + warp * 32 + lane;
+          for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+          for (int s = 0; s < p.splits; ++s) {
+            const float* src = base + s * split_stride + c0 * TILE_N + warp * 32 + lane;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * TILE_N);
-        }
-        if (n < p.N) {
+            for (int i = 0; i < 8; ++i) sum[i] += __ldcg(src + i * TILE_N);
+          }
+          if (n < p.N) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int m = t0 + c0 + i;
-            if (m < p.M) {
-              if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = sum[i];
-              else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[i]);
+            for (int i = 0; i < 8; ++i) {
+              const int m = t0 + c0 + i;
+              if (m < p.M) {
+                if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = sum[i];
+                else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[i]);
+              }
             }
           }
         }
       }
-    }
     }
   }
   tcgen05_fence_before();
