@@ -224,3 +224,31 @@ def test_position_encoding_alone(part_runner):
     cos, sin = plain.rope_tables(cfg["head_dim"], cfg["rope_theta"], 128, torch.float32)
     assert torch.equal(rot.cos.cpu(), cos) and torch.equal(rot.sin.cpu(), sin)
     assert rot.cos.data_ptr() == runner.model.blocks[3].mixer.position.cos.data_ptr(), "one table is shared"
+
+
+def test_command_line_writes_random_weights_and_generates(tmp_path):
+    """python -m tinyserve_b200 random-weights, then generate --prompt-ids: the command line drives
+    the same engine and prints the same greedy tokens as the plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from helpers import tiny_config
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny_config("A").to_dict()))
+    folder = str(tmp_path / "model")
+    run = lambda *args: subprocess.run([sys.executable, "-m", "tinyserve_b200", *args], cwd=root,
+                                       capture_output=True, text=True, timeout=600)
+    made = run("random-weights", "--config", str(cfg_path), "--out", folder, "--seed", "7", "--store-dtype", "float32")
+    assert made.returncode == 0 and made.stdout.strip() == folder, made.stderr
+    prompt = random_ids(256, 9, seed=2)
+    out = run("generate", "--model", folder, "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "10",
+              "--temperature", "0", "--repetition-penalty", "1.0", "--ignore-eos", "--dtype", "float32",
+              "--max-model-len", "64", "--max-num-seqs", "2", "--max-num-batched-tokens", "64",
+              "--num-blocks", "16", "--no-cuda-graphs")
+    assert out.returncode == 0, out.stderr[-2000:]
+    cfg, weights = plain.load_folder(folder)
+    assert [int(t) for t in out.stdout.strip().splitlines()[-1].split()] == plain.greedy_generate(cfg, weights, prompt, 10)
+    assert run("serve").returncode == 2
+    assert run("generate").returncode == 2
