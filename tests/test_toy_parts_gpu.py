@@ -337,3 +337,99 @@ def test_toy_routed_feed_forward_and_position_encoding_run_through_the_engine(tm
         ARCHITECTURES.pop("ToyRoutedForCausalLM", None)
         FEED_FORWARDS.pop("toy_routed", None)
         POSITION_ENCODINGS.pop("toy_linear_rotary", None)
+
+
+# ----------------------------------------------------------------------------- a layer on another's cache
+def _register_shared():
+    from tinyserve_b200.config import (LayerCall, LayerSpec, ModelConfig, ModelSpec, PartSpec,
+                                       register_architecture)
+
+    @dataclass(frozen=True)
+    class SharedConfig(ModelConfig):
+        """Two attention layers; the second keeps no keys of its own: its queries read the first
+        layer's cache (the run order says so: same cache entry, writes_cache=False)."""
+        architecture: ClassVar[str] = "ToySharedCacheForCausalLM"
+        vocab_size: int = 0
+        hidden_size: int = 0
+
+        @classmethod
+        def from_dict(cls, raw):
+            return cls(raw["vocab_size"], raw["hidden_size"])
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "vocab_size": self.vocab_size, "hidden_size": self.hidden_size}
+
+        def model_spec(self):
+            h = self.hidden_size
+            norm = PartSpec("rmsnorm", {"eps": 1e-6})
+            attn = PartSpec("attention", {
+                "hidden_size": h, "num_heads": 4, "num_kv_heads": 2, "head_dim": 32, "qk_norm": norm,
+                "position": PartSpec("rotary", {"rotary_dim": 32, "theta": 1e4, "pairing": "half"})})
+            ffn = PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 64, "activation": "silu"})
+            layers = (LayerSpec(attn, ffn, norm), LayerSpec(attn, ffn, norm))
+            order = (LayerCall(0, 0), LayerCall(1, 0, writes_cache=False))
+            return ModelSpec(self.vocab_size, h, layers, order, norm, True)
+
+    register_architecture(SharedConfig.architecture, SharedConfig)
+    return SharedConfig
+
+
+def _plain_shared(weights, cfg, ids):
+    w = {k: v.double() for k, v in weights.items()}
+    T, H, Hkv, D = len(ids), 4, 2, 32
+    norm = lambda x, wt: x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * wt
+    r = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    inv = 1.0 / 1e4 ** (torch.arange(0, D, 2, dtype=torch.float64) / D)
+    ang = torch.outer(torch.arange(T, dtype=torch.float64), inv)
+    c, s = ang.cos().float().double()[:, None], ang.sin().float().double()[:, None]
+
+    def rope(z):
+        a, b = z[..., :D // 2], z[..., D // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    kept = {}
+    for layer in (0, 1):
+        p = f"model.layers.{layer}."
+        x = norm(r, w[p + "input_layernorm.weight"])
+        q = rope(norm((x @ w[p + "self_attn.q_proj.weight"].T).view(T, H, D), w[p + "self_attn.q_norm.weight"]))
+        if layer == 0:
+            kept["k"] = rope(norm((x @ w[p + "self_attn.k_proj.weight"].T).view(T, Hkv, D), w[p + "self_attn.k_norm.weight"]))
+            kept["v"] = (x @ w[p + "self_attn.v_proj.weight"].T).view(T, Hkv, D)
+        k, v = kept["k"].repeat_interleave(H // Hkv, 1), kept["v"].repeat_interleave(H // Hkv, 1)
+        sc = torch.einsum("thd,shd->hts", q, k) * D ** -0.5
+        mask = torch.arange(T)[None] <= torch.arange(T)[:, None]
+        o = torch.einsum("hts,shd->thd", sc.masked_fill(~mask[None], float("-inf")).softmax(-1), v).reshape(T, H * D)
+        r = r + o @ w[p + "self_attn.o_proj.weight"].T
+        x = norm(r, w[p + "post_attention_layernorm.weight"])
+        g, u = x @ w[p + "mlp.gate_proj.weight"].T, x @ w[p + "mlp.up_proj.weight"].T
+        r = r + (g / (1 + torch.exp(-g)) * u) @ w[p + "mlp.down_proj.weight"].T
+    return norm(r, w["model.norm.weight"]) @ w["model.embed_tokens.weight"].T
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", 3e-2)])
+def test_a_layer_reads_another_layers_cache(dtype, tol, tmp_path):
+    import os
+    from safetensors.torch import load_file
+    from tinyserve_b200.config import ARCHITECTURES, EngineConfig
+    from tinyserve_b200.engine.batch import StepEntry
+    from tinyserve_b200.engine.runner import ModelRunner
+    from tinyserve_b200.weights import write_random_model
+    SharedConfig = _register_shared()
+    try:
+        cfg = SharedConfig(vocab_size=71, hidden_size=64)
+        folder = write_random_model(cfg, str(tmp_path), seed=9)
+        weights = load_file(os.path.join(folder, "model.safetensors"))
+        runner = ModelRunner(EngineConfig(model=folder, dtype=dtype, max_model_len=96, block_size=8,
+                                          max_num_seqs=2, max_num_batched_tokens=64, num_blocks=20))
+        assert len(runner.model.cache_entries) == 1, "one cache entry for both layers"
+        ids = random_ids(71, 40, seed=6)
+        ref = _plain_shared(weights, cfg, ids)
+        mgr = runner.manager
+        mgr.begin("a")
+        got = [runner.step([StepEntry("a", ids[:25], list(range(25)))])]
+        got += [runner.step([StepEntry("a", [ids[t]], [0])]) for t in range(25, 40)]
+        mgr.free("a")
+        got = torch.cat(got).double().cpu()
+        assert (got - ref).abs().max().item() < tol * ref.abs().max().item()
+    finally:
+        ARCHITECTURES.pop("ToySharedCacheForCausalLM", None)
