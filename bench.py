@@ -222,6 +222,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--impl", default="tinyserve_b200")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     a = ap.parse_args()
     if a.impl == "reference":
@@ -241,7 +242,7 @@ def main() -> int:
     peaks = load_peaks()
     sizes = sorted({1, a.batch, 64}) if not a.no_points else [a.batch]
     llm = LLM(model_config=config, random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
-              block_size=16, max_num_seqs=max(sizes), max_num_batched_tokens=PREFILL_TOKENS,
+              block_size=a.block_size, max_num_seqs=max(sizes), max_num_batched_tokens=PREFILL_TOKENS,
               num_blocks=max(sizes) * (CONTEXT // 16) // 2 + 256, use_cuda_graphs=False, seed=a.seed)
     llm.runner.capture_decode_graphs(sizes)
 
@@ -269,7 +270,7 @@ def main() -> int:
                    "layers_of_model": QWEN3_8B["num_hidden_layers"], "hidden": raw["hidden_size"],
                    "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
                    "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"],
-                   "vocab": raw["vocab_size"], "prompt_len": PROMPT_LEN, "block_size": 16,
+                   "vocab": raw["vocab_size"], "prompt_len": PROMPT_LEN, "block_size": a.block_size,
                    "l2": "inputs larger than L2 (weights read every step)",
                    "peaks": peaks["source"], "peak_hbm_gbs": peaks["hbm_gbs"],
                    "peak_bf16_tflops": peaks["bf16_tflops"], "bf16_gemm": ops.BF16_GEMM},

@@ -319,7 +319,8 @@ def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window, b
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32)])
+@pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32),
+                                           (8, 2, 128, 64), (6, 3, 64, 32)])      # pages of 32 and 64: whole pages by TMA
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])
 @pytest.mark.parametrize("merge", ["cluster", "launch", "kernel"])
 def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention, merge, monkeypatch):
@@ -339,7 +340,8 @@ def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf
     close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "decode attention")
 
 
-@pytest.mark.parametrize("H,Hkv,D,page", [(32, 8, 128, 16), (6, 2, 64, 8), (20, 1, 48, 16), (3, 3, 256, 32)])
+@pytest.mark.parametrize("H,Hkv,D,page", [(32, 8, 128, 16), (6, 2, 64, 8), (20, 1, 48, 16), (3, 3, 256, 32),
+                                           (16, 4, 128, 64)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("source", ["tensor", "partials"])
 @pytest.mark.parametrize("merge", ["cluster", "launch"])

@@ -15,7 +15,7 @@
 // Visibility as serve.py:668-680: key j is seen by the query at position p iff j <= p and, with a
 // window W > 0, j > p - W.  Keys are found through the block table; the cache layout is
 // [page, kv_head, slot, head_dim].
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 #ifndef TS_HEAD_DIM
 #error "compile with -DTS_HEAD_DIM=<head size, a multiple of 16>"
@@ -76,9 +76,6 @@ struct MmaAttnParams {
   bf16* v_cache_out;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
 // 16 bytes global -> shared; `valid` false writes zeros (the source is not read)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;
@@ -130,10 +127,20 @@ __device__ __forceinline__ void load_kv_tile(char* ks, char* vs, const MmaAttnPa
   }
 }
 
+// Where 16 bytes of a key or value tile lie in shared memory: row `key`, 16-byte piece `piece` of
+// the row.  Padded rows (cp.async path), or, for tiles brought by TMA, 64-column chunks of
+// 128-byte rows with the 128-byte swizzle (a piece changes place with the row's low three bits);
+// both keep ldmatrix free of bank conflicts.
+template <bool SWZ>
+__device__ __forceinline__ uint32_t kv_piece(const char* tile, int key, int piece) {
+  if (SWZ) return smem_u32(tile + (piece >> 3) * (BN * 128) + key * 128 + (((piece & 7) ^ (key & 7)) << 4));
+  return smem_u32(tile + key * ROW_BYTES + piece * 16);
+}
+
 // S[16 x (8 * NT)] += Q[16 x D] * K^T for the NT*8 keys that start at row `key0` of the K tile.
 // `qs` points at this warp's 16 query rows in shared memory (used when the fragments are not held
 // in registers); `qf` holds them otherwise.
-template <int NT>
+template <int NT, bool SWZ = false>
 __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const char* qs, const uint32_t (*qf)[4],
                                         const char* ks, int key0, int lane) {
   static_assert(NT % 2 == 0, "key tiles come in pairs");
@@ -150,7 +157,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const char* qs, const
 #pragma unroll
     for (int np = 0; np < NT / 2; ++np) {
       uint32_t b[4];
-      ldmatrix_x4(b, smem_u32(ks + (key0 + np * 16 + (mi >> 1) * 8 + r) * ROW_BYTES + (kstep * 2 + (mi & 1)) * 16));
+      ldmatrix_x4(b, kv_piece<SWZ>(ks, key0 + np * 16 + (mi >> 1) * 8 + r, kstep * 2 + (mi & 1)));
       mma_bf16(s[2 * np], a, b[0], b[1]);
       mma_bf16(s[2 * np + 1], a, b[2], b[3]);
     }
@@ -158,7 +165,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NT][4], const char* qs, const
 }
 
 // O[16 x D] += P[16 x (8 * NT)] * V for the keys that start at row `key0` of the V tile
-template <int NT>
+template <int NT, bool SWZ = false>
 __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[NT][4], const char* vs,
                                         int key0, int lane) {
   const int mi = lane >> 3, r = lane & 7;
@@ -172,7 +179,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[N
 #pragma unroll
     for (int dp = 0; dp < D / 16; ++dp) {
       uint32_t b[4];
-      ldmatrix_x4_trans(b, smem_u32(vs + (key0 + kk * 16 + (mi & 1) * 8 + r) * ROW_BYTES + (dp * 2 + (mi >> 1)) * 16));
+      ldmatrix_x4_trans(b, kv_piece<SWZ>(vs, key0 + kk * 16 + (mi & 1) * 8 + r, dp * 2 + (mi >> 1)));
       mma_bf16(o[2 * dp], a, b[0], b[1]);
       mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
     }
@@ -451,11 +458,31 @@ __device__ __forceinline__ void build_head(const MmaAttnParams& p, int t, int co
   }
 }
 
-__global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
+// TMA false: key and value tiles come by cp.async, 16 bytes a thread, into padded rows (any head
+// size in steps of 16, any page size).  TMA true (head sizes in steps of 64, pages of 32 or 64
+// keys): one thread fetches whole pages as boxes of page x 64 columns with the 128-byte swizzle
+// and an mbarrier per stage counts their bytes; an SM streams about half as much again this way
+// as through its load/store unit's miss queue.  Whole pages come, also the keys past the
+// request's length in its last page: those are masked, and must hold finite numbers (the engine's
+// cache starts as zeros and only ever takes keys and values).
+template <bool TMA>
+__device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const CUtensorMap* map_k,
+                                                 const CUtensorMap* map_v) {
   extern __shared__ __align__(16) char smem[];
+  constexpr int KV_TILE = TMA ? BN * D * 2 : BN * ROW_BYTES;      // bytes of the keys (or values) of a stage
   char* Qs = smem;                                   // [16][ROW_BYTES]
-  char* Ks = Qs + 16 * ROW_BYTES;                    // [DEC_STAGES][BN][ROW_BYTES]
-  char* Vs = Ks + DEC_STAGES * BN * ROW_BYTES;       // [DEC_STAGES][BN][ROW_BYTES]
+  char* Ks = TMA ? reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(Qs + 16 * ROW_BYTES) + 1023) & ~uintptr_t(1023))
+                 : Qs + 16 * ROW_BYTES;              // [DEC_STAGES][KV_TILE]
+  char* Vs = Ks + DEC_STAGES * KV_TILE;              // [DEC_STAGES][KV_TILE]
+  __shared__ uint64_t full[DEC_STAGES];              // (TMA) the stage's bytes have landed
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  if (TMA && threadIdx.x == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(smem_u32(&full[s]), 1);
+    abort_flag_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (TMA) __syncthreads();
 
   pdl_trigger();
   // The lengths, the block table and every cached key but the newest were written before this
@@ -486,10 +513,33 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   const bool has_newest = from_qkv && newest_tile >= tile_begin && newest_tile < tile_begin + n_tiles;
   __shared__ __align__(16) bf16 newest_kv[2 * D];
 
+  // tile `tile` of the keys and values into stage `stage`
+  auto load_tile = [&](int stage, int tile, int j_end) {
+    if (TMA) {
+      // the boxes of a tile (pages x 64-column chunks x keys/values) are dealt to the lanes of
+      // warp 0, so that issuing them costs the block one box's time, not sixteen; lane 0's
+      // arrival carries the tile's byte count, so the stage cannot complete before it
+      if (threadIdx.x < 32) {
+        const int pages_per_tile = BN >> p.page_shift, boxes = pages_per_tile * (D / 64) * 2;
+        const uint32_t bar = smem_u32(&full[stage]);
+        if (threadIdx.x == 0) mbar_expect_tx(bar, 2 * KV_TILE);
+        __syncwarp();
+        for (int i = threadIdx.x; i < boxes; i += 32) {
+          const int values = i & 1, c = (i >> 1) % (D / 64), pg = (i >> 1) / (D / 64);
+          const int j = tile * BN + (pg << p.page_shift);
+          const int page = j < j_hi ? bt[j >> p.page_shift] : 0;                        // past the end: the null page
+          const int row = (page * p.Hkv + kvh) << p.page_shift;
+          const int off = stage * KV_TILE + c * (BN * 128) + (pg << p.page_shift) * 128;
+          tma_load_2d(smem_u32((values ? Vs : Ks) + off), values ? map_v : map_k, bar, c * 64, row);
+        }
+      }
+    } else {
+      load_kv_tile<BN, THREADS>(Ks + stage * KV_TILE, Vs + stage * KV_TILE, p, bt, kvh, tile * BN, j_lo, j_end);
+    }
+  };
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s)
-    if (s < n_tiles && tile_begin + s != late_tile)
-      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_load);
+    if (s < n_tiles && tile_begin + s != late_tile) load_tile(s, tile_begin + s, j_load);
   // the timeline build follows the blocks of one (request, KV group): marks 40.. with the key
   // range as their value
   const bool traced = blockIdx.x == 0 && blockIdx.z == 0 && threadIdx.x == 0;
@@ -543,11 +593,14 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   }
 #pragma unroll
   for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < n_tiles && tile_begin + s == late_tile)
-      load_kv_tile<BN, THREADS>(Ks + s * BN * ROW_BYTES, Vs + s * BN * ROW_BYTES, p, bt, kvh, (tile_begin + s) * BN, j_lo, j_hi);
+    if (s < n_tiles && tile_begin + s == late_tile) load_tile(s, tile_begin + s, j_hi);
     // the first group holds the query and all of these tiles; the others stay empty, so that the
     // loop below finds as many groups as it counts on
     cp_async_commit();
+  }
+  if (TMA) {        // only the query rows came by cp.async
+    cp_async_wait<0>();
+    __syncthreads();
   }
   if (traced) timeline_mark_thread(43, split);          // query rows (and the newest key) made
   int pos[2], lo[2];
@@ -565,18 +618,22 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
 
   for (int it = 0; it < n_tiles; ++it) {
     const int nxt = it + DEC_STAGES - 1;
-    if (nxt < n_tiles) {
-      const int nb = nxt % DEC_STAGES;
-      load_kv_tile<BN, THREADS>(Ks + nb * BN * ROW_BYTES, Vs + nb * BN * ROW_BYTES, p, bt, kvh, (tile_begin + nxt) * BN, j_lo, j_load);
+    if (nxt < n_tiles) load_tile(nxt % DEC_STAGES, tile_begin + nxt, j_load);
+    if (TMA) {
+      mbar_wait(smem_u32(&full[it % DEC_STAGES]), (it / DEC_STAGES) & 1, abort_flag);      // bounded
+    } else {
+      cp_async_commit();
+      cp_async_wait<DEC_STAGES - 1>();
     }
-    cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
     __syncthreads();
     if (has_newest && tile_begin + it == newest_tile) {
-      // the newest key and value take their row of the tile (the copy left zeros there)
+      // the newest key and value take their row of the tile (the copy left zeros or stale bytes there)
       const int row = qpos - newest_tile * BN, buf_n = it % DEC_STAGES;
       for (int d = threadIdx.x * 2; d < 2 * D; d += THREADS * 2) {
-        char* dst = (d < D ? Ks : Vs) + (size_t)buf_n * BN * ROW_BYTES + row * ROW_BYTES + (d < D ? d : d - D) * 2;
+        const int e = d < D ? d : d - D;          // element of the head; two neighbours per thread
+        char* tile = (d < D ? Ks : Vs) + (size_t)buf_n * KV_TILE;
+        char* dst = TMA ? tile + (e / 64) * (BN * 128) + row * 128 + ((((e % 64) / 8) ^ (row & 7)) << 4) + (e % 8) * 2
+                        : tile + row * ROW_BYTES + e * 2;
         *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(newest_kv + d);
       }
       __syncthreads();
@@ -591,9 +648,9 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
     const int jbase = (tile_begin + it) * BN + warp * 16;
     if (jbase < j_hi) {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      qk_tile<2>(s, Qs, qf, Ks + buf * BN * ROW_BYTES, warp * 16, lane);
+      qk_tile<2, TMA>(s, Qs, qf, Ks + buf * KV_TILE, warp * 16, lane);
       softmax_tile<2>(s, o, m, l, pos, lo, jbase, p.scale_log2, lane);
-      pv_tile<2>(o, s, Vs + buf * BN * ROW_BYTES, warp * 16, lane);
+      pv_tile<2, TMA>(o, s, Vs + buf * KV_TILE, warp * 16, lane);
     }
     __syncthreads();
   }
@@ -734,6 +791,16 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
   }
 }
 
+__global__ void __launch_bounds__(THREADS) attn_decode_kernel(MmaAttnParams p) {
+  attn_decode_body<false>(p, nullptr, nullptr);
+}
+constexpr bool TMA_HEAD = D % 64 == 0;        // boxes are 64 columns wide
+__global__ void __launch_bounds__(THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       MmaAttnParams p) {
+  attn_decode_body<TMA_HEAD>(p, &map_k, &map_v);
+}
+
 // out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
 // (block x merges partial row x into output row x, or into head x % H of token tokens[x / H])
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -778,7 +845,7 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
                              float* part_ml, int* counters, int decode_only, const int* tile_req,
-                             const int* tile_q0, int num_tiles, int tile_queries, cudaStream_t stream);
+                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream);
 }
 
 TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cache, const void* v_cache,
@@ -787,11 +854,11 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      int page_size, int max_blocks, float scale, int window,
                                      int num_splits, float* part_o, float* part_ml, int* counters,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
-                                     int tile_queries, cudaStream_t stream) {
+                                     int tile_queries, int num_pages, cudaStream_t stream) {
   return paged_attention_mma_impl(nullptr, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
                                   part_o, part_ml, counters, decode_only, tile_req, tile_q0, num_tiles,
-                                  tile_queries, stream);
+                                  tile_queries, num_pages, stream);
 }
 
 // Decode (every request brings one token) straight from the fused q/k/v projection: qkv
@@ -809,7 +876,8 @@ TS_EXPORT int ts_paged_attention_mma_from_qkv(const void* qkv, const float* part
                                               const int* block_table, const int* cu_q, const int* kv_lens,
                                               int num_tokens, int num_requests, int H, int Hkv, int page_size,
                                               int max_blocks, float scale, int window, int num_splits,
-                                              float* part_o, float* part_ml, int merge, cudaStream_t stream) {
+                                              float* part_o, float* part_ml, int merge, int num_pages,
+                                              cudaStream_t stream) {
   TS_REQUIRE((qkv != nullptr) != (partials != nullptr), "paged_attention_mma_from_qkv: the projection or its partial tiles");
   TS_REQUIRE(partials == nullptr || (splits > 0 && n_tiles * 128 >= (H + 2 * Hkv) * D && tile_t > 0),
              "paged_attention_mma_from_qkv: partial tiles do not fit the row length");
@@ -828,7 +896,7 @@ TS_EXPORT int ts_paged_attention_mma_from_qkv(const void* qkv, const float* part
   extra.k_cache_out = static_cast<bf16*>(k_cache); extra.v_cache_out = static_cast<bf16*>(v_cache);
   return paged_attention_mma_impl(&extra, nullptr, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, 1, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o,
-                                  part_ml, nullptr, merge, nullptr, nullptr, 0, 0, stream);
+                                  part_ml, nullptr, merge, nullptr, nullptr, 0, 0, num_pages, stream);
 }
 
 namespace {
@@ -837,7 +905,7 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
                              float* part_ml, int* counters, int decode_only, const int* tile_req,
-                             const int* tile_q0, int num_tiles, int tile_queries, cudaStream_t stream) {
+                             const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
@@ -863,12 +931,37 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
   cudaError_t e;
   if (decode_only) {
     p.heads_per_tile = 16; p.queries_per_tile = 1; p.head_tiles = (G + 15) / 16;
-    const size_t smem = (size_t)(16 + 2 * DEC_STAGES * BN) * ROW_BYTES;
-    static bool configured = false;
-    if (!configured) {
-      e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    // whole pages by TMA where the sizes allow it (TINYSERVE_DECODE_TMA=0: never)
+    static const bool tma_allowed = [] {
+      const char* v = getenv("TINYSERVE_DECODE_TMA");
+      return !(v && v[0] == '0');
+    }();
+    // (pages of 32 and 64 keys: measured on B200, 64 requests x 4096 keys, pages of 64: 6.67 TB/s by
+    // TMA against 5.78 by cp.async; with pages of 16 both reach 5.4: the 4 KB pieces are what limits)
+    const bool tma = tma_allowed && TMA_HEAD && num_pages > 0 && page_size >= 32 && page_size <= BN &&
+                     ((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
+    CUtensorMap mk, mv;
+    if (tma) {
+      EncodeTiledFn fn = encode_tiled();
+      TS_REQUIRE(fn != nullptr, "paged_attention_mma: the driver's tensor-map encoder was not found");
+      const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * Hkv * page_size};
+      const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+      const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+      const cuuint32_t elem[2] = {1, 1};
+      for (int i = 0; i < 2; ++i)
+        TS_REQUIRE(fn(i ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(i ? v_cache : k_cache), dims,
+                      strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS,
+                   "paged_attention_mma: cuTensorMapEncodeTiled failed for the cache");
+    }
+    const size_t smem = tma ? (size_t)16 * ROW_BYTES + 1024 + (size_t)2 * DEC_STAGES * BN * D * 2
+                            : (size_t)(16 + 2 * DEC_STAGES * BN) * ROW_BYTES;
+    static bool configured = false, configured_tma = false;
+    if (!(tma ? configured_tma : configured)) {
+      e = tma ? cudaFuncSetAttribute(attn_decode_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+              : cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return ts_fail("paged_attention_mma: %s", cudaGetErrorString(e));
-      configured = true;
+      (tma ? configured_tma : configured) = true;
     }
     // tile_req / tile_q0 here: the one-token requests of a mixed batch and their tokens
     TS_REQUIRE(tile_req == nullptr || counters == nullptr, "paged_attention_mma: a request list merges by its own launch");
@@ -876,11 +969,13 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
     dim3 grid(Hkv * p.head_tiles, num_splits, count);
     if (decode_only == 2 && num_splits > 1 && num_splits <= 8 && counters == nullptr) {
       p.cluster_merge = 1;
-      e = ts_launch_cluster(attn_decode_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), p);
+      e = tma ? ts_launch_cluster(attn_decode_tma_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), mk, mv, p)
+              : ts_launch_cluster(attn_decode_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), p);
       if (e != cudaSuccess) return ts_fail("attn_decode (clusters of %d): %s", num_splits, cudaGetErrorString(e));
       return 0;
     }
-    TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
+    if (tma) TS_LAUNCH("attn_decode_tma", attn_decode_tma_kernel, grid, THREADS, smem, stream, mk, mv, p);
+    else TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
     if (num_splits > 1 && counters == nullptr) {
       TS_LAUNCH("attention_combine", attention_combine_kernel, (tile_req ? count : num_tokens) * H,
                 D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,

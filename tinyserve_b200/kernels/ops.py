@@ -589,6 +589,12 @@ def timeline_read(reset=True):
     return out[np.argsort(out["ns"], kind="stable")]
 
 
+def _tma_pages(k_cache, v_cache):
+    """The page count that lets the decode kernel fetch whole pages by TMA, or 0 where the caches
+    are not plain [pages, kv heads, page, head] blocks of memory."""
+    return k_cache.shape[0] if k_cache.is_contiguous() and v_cache.is_contiguous() else 0
+
+
 def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     """Key ranges for the tensor-core decode kernel: as many as fit in one wave of blocks (two
     per SM), with at least two tiles of 64 keys per range."""
@@ -613,7 +619,8 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
         _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(1), c_int(H), c_int(Hkv),
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
         c_int(num_splits), _ptr(part_o), _ptr(part_ml), None, c_int(2 if cluster else 1), _ptr(work.dec_req),
-        _ptr(work.dec_tok), c_int(n), c_int(0), _stream()), 2 if num_splits > 1 and not cluster else 1)
+        _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), _stream()),
+        2 if num_splits > 1 and not cluster else 1)
 
 
 def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
@@ -683,7 +690,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
             c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
-            _stream()), launches)
+            c_int(_tma_pages(k_cache, v_cache)), _stream()), launches)
         return out
     lib = _attention(D)
     _check(lib, lib.ts_paged_attention(
@@ -743,7 +750,8 @@ def attention_from_qkv(qkv, positions, num_heads, num_kv_heads, head_dim, rotary
         c_float(eps), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
         _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(H), c_int(Hkv), c_int(view.page_size),
         c_int(view.block_table.stride(0)), c_float(scale), c_int(window), c_int(num_splits), _ptr(part_o),
-        _ptr(part_ml), c_int(2 if cluster else 1), _stream()), 2 if num_splits > 1 and not cluster else 1)
+        _ptr(part_ml), c_int(2 if cluster else 1), c_int(_tma_pages(k_cache, v_cache)), _stream()),
+        2 if num_splits > 1 and not cluster else 1)
     return out
 
 
