@@ -149,41 +149,42 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      // queries: rows (query, head) with the head fastest; one box per 64 columns and query tile
-      const uint32_t qbar = smem_u32(q_full);
-      mbar_expect_tx(qbar, groups * DCH * 64 * 2 * GT * QPT);
-      for (int g = 0; g < groups; ++g)
-        for (int c = 0; c < DCH; ++c)
-          tma_load_3d(smem_u32(Qs + g * Q_BYTES + c * CHUNK_BYTES), &map_q, qbar, c * 64, kvh * G + g0,
-                      q_begin + q0 + g * QPT);
+    if (n_tiles > 0) {
+      if (lane == 0) {
+        // queries: rows (query, head) with the head fastest; one box per 64 columns and query tile
+        const uint32_t qbar = smem_u32(q_full);
+        mbar_expect_tx(qbar, groups * DCH * 64 * 2 * GT * QPT);
+        for (int g = 0; g < groups; ++g)
+          for (int c = 0; c < DCH; ++c)
+            tma_load_3d(smem_u32(Qs + g * Q_BYTES + c * CHUNK_BYTES), &map_q, qbar, c * 64, kvh * G + g0,
+                        q_begin + q0 + g * QPT);
+      }
       const int* bt = p.block_table + (size_t)b * p.max_blocks;
       const int pages_per_tile = BN >> p.page_shift;
       // Keys and values have rings of their own, and the keys run one tile ahead: a stage of keys
       // is free as soon as both tiles' scores are computed, long before its values have been used.
-      // The pages of a tile are looked up in one go (independent loads), before the wait.
+      // The boxes of a tile (pages x 64-column chunks) are dealt to the lanes of the warp, so that
+      // issuing them takes one box's time; lane 0's arrival carries the tile's byte count, so the
+      // stage cannot complete before it.
       auto load = [&](bool keys, int t) -> bool {
         const int stages = keys ? K_STAGES : V_STAGES, s = t % stages;
         const int j0 = (first_tile + t) * BN;
-        int pages[16];
-#pragma unroll
-        for (int pg = 0; pg < 16; ++pg) {
-          const int j = j0 + (pg << p.page_shift);
-          pages[pg] = pg < pages_per_tile && j < j_hi ? bt[j >> p.page_shift] : 0;   // past the end: the null page
-        }
-        if (!mbar_wait(smem_u32(keys ? &k_empty[s] : &v_empty[s]), ((t / stages) & 1) ^ 1, abort_flag)) return false;
+        int ok = 1;
+        if (lane == 0)
+          ok = mbar_wait(smem_u32(keys ? &k_empty[s] : &v_empty[s]), ((t / stages) & 1) ^ 1, abort_flag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) return false;
         const uint32_t bar = smem_u32(keys ? &k_full[s] : &v_full[s]);
-        mbar_expect_tx(bar, KV_BYTES);
-#pragma unroll
-        for (int pg = 0; pg < 16; ++pg) {
-          if (pg < pages_per_tile) {
-            const int row = (pages[pg] * p.Hkv + kvh) << p.page_shift;
-            for (int c = 0; c < DCH; ++c) {
-              const int off = s * KV_BYTES + c * CHUNK_BYTES + (pg << p.page_shift) * 128;
-              if (keys) tma_load_2d(smem_u32(Ks + off), &map_k, bar, c * 64, row);
-              else tma_load_2d(smem_u32(Vs + off), &map_v, bar, c * 64, row);
-            }
-          }
+        if (lane == 0) mbar_expect_tx(bar, KV_BYTES);
+        __syncwarp();
+        for (int i = lane; i < pages_per_tile * DCH; i += 32) {
+          const int pg = i / DCH, c = i % DCH;
+          const int j = j0 + (pg << p.page_shift);
+          const int page = j < j_hi ? bt[j >> p.page_shift] : 0;          // past the end: the null page
+          const int row = (page * p.Hkv + kvh) << p.page_shift;
+          const int off = s * KV_BYTES + c * CHUNK_BYTES + (pg << p.page_shift) * 128;
+          if (keys) tma_load_2d(smem_u32(Ks + off), &map_k, bar, c * 64, row);
+          else tma_load_2d(smem_u32(Vs + off), &map_v, bar, c * 64, row);
         }
         return true;
       };
@@ -191,7 +192,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int t = 0; ok && t < n_tiles; ++t) {
         if (t + 1 < n_tiles) ok = load(true, t + 1);
         if (ok) ok = load(false, t);
-        if (traced) timeline_mark_thread(30, t);
+        if (traced && lane == 0) timeline_mark_thread(30, t);
       }
     }
   } else if (warp == 1) {
