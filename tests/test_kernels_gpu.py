@@ -110,12 +110,7 @@ def test_gated_product(M, activation):
     close(got, act * u, torch.bfloat16, "fused")
     # the kernel's gated form itself takes up to 64 tokens
     close(o._linear_tcgen05(x, w, False, splits=1, gated=o.ACTIVATIONS[activation] + 1), act * u, torch.bfloat16, "gated form")
-    monkey = o.GATED_EPILOGUE
-    o.GATED_EPILOGUE = False
-    try:
-        close(o.gated_linear(x, w, activation, 64), act * u, torch.bfloat16, "product then activation")
-    finally:
-        o.GATED_EPILOGUE = monkey
+    close(o.gated_activation(o.linear(x, w), activation, 64), act * u, torch.bfloat16, "product then activation")
     if M <= 16:
         sumsq = (rnd(1, 16, seed=5).abs() + 0.5).contiguous()
         rows = o.ScaledRows(x, sumsq, 1, 1e-6)
@@ -194,17 +189,14 @@ def test_gemm_simt(M, N, K, dtypes):
     dtype, f32_out = dtypes
     o = ops()
     x, w, b = rnd(M, K, seed=1, dtype=dtype), rnd(N, K, seed=2, dtype=dtype), rnd(N, seed=3, dtype=dtype)
-    old, o.BF16_GEMM = o.BF16_GEMM, "simt"
-    try:
-        out = o.linear(x, w, b, out_float32=f32_out)
-        want = x.double() @ w.double().T + b.double()
-        assert out.dtype == (torch.float32 if f32_out or dtype == torch.float32 else dtype)
-        close(out, want, torch.float32 if f32_out else dtype, "gemm")
-        # a row's result does not depend on the rows around it
-        alone = o.linear(x[M // 2:M // 2 + 1].contiguous(), w, b, out_float32=f32_out)
-        assert torch.equal(alone[0], out[M // 2])
-    finally:
-        o.BF16_GEMM = old
+    linear = o.linear if dtype == torch.float32 else o._linear_simt
+    out = linear(x, w, b, out_float32=f32_out)
+    want = x.double() @ w.double().T + b.double()
+    assert out.dtype == (torch.float32 if f32_out or dtype == torch.float32 else dtype)
+    close(out, want, torch.float32 if f32_out else dtype, "gemm")
+    # a row's result does not depend on the rows around it
+    alone = linear(x[M // 2:M // 2 + 1].contiguous(), w, b, out_float32=f32_out)
+    assert torch.equal(alone[0], out[M // 2])
 
 
 def test_linear_bf16_library_path():
@@ -256,21 +248,20 @@ def _attention_ref(q, k, v, q_lens, scale, window):
     return torch.cat(out)
 
 
-def _run_attention(q, kc, vc, table, q_lens, kv_lens, page, scale, window, splits):
+def _run_attention(q, kc, vc, table, q_lens, kv_lens, page, scale, window, splits, backend=None):
     cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32).cuda()
     ctx = SimpleNamespace(cu_q=cu, kv_lens=torch.tensor(kv_lens, dtype=torch.int32).cuda(),
                           num_requests=len(q_lens), max_q_len=max(q_lens), max_kv_len=max(kv_lens))
     view = SimpleNamespace(block_table=table, page_size=page)
-    return ops().paged_attention(q, kc, vc, view, ctx, scale, window, num_splits=splits)
+    return ops().paged_attention(q, kc, vc, view, ctx, scale, window, num_splits=splits, backend=backend)
 
 
-@pytest.fixture(params=["tcgen05", "mma", "simt"])
-def bf16_attention(request):
-    """The bfloat16 attention back ends: tcgen05 prefill (+ mma.sync decode), mma.sync, 32-bit FMA."""
+def _backends(dtype, D, page):
+    """The kernels that can run this case: the one the engine picks by head size, and the slower
+    ones below it (the engine reaches those at other head sizes)."""
     o = ops()
-    old, o.BF16_ATTENTION = o.BF16_ATTENTION, request.param
-    yield request.param
-    o.BF16_ATTENTION = old
+    chosen = o.attention_backend(dtype, D, page)
+    return {"tcgen05": ["tcgen05", "mma", "simt"], "mma": ["mma", "simt"], "simt": ["simt"]}[chosen]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -278,31 +269,29 @@ def bf16_attention(request):
                                            (5, 5, 80, 32), (16, 2, 128, 16), (80, 1, 16, 8), (4, 2, 256, 16),
                                            (32, 8, 128, 16), (6, 2, 64, 8), (3, 1, 128, 128), (200, 1, 64, 16)])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 3), (23, 1), (23, 4)])
-def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention):
-    if dtype == torch.float32 and bf16_attention != "mma":
-        pytest.skip("float32 has one back end")
-    if bf16_attention == "tcgen05" and (D not in (64, 128) or page < 8 or splits > 1):
-        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128, pages of 8 and more, no splits")
+def test_paged_attention_mixed_batch(dtype, H, Hkv, D, page, window, splits):
     # a whole prompt, a decode token, a portion after a prefix, two tokens, a long decode
     kv_lens, q_lens = [70, 133, 97, 2, 300], [70, 1, 29, 2, 1]
     k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
     v = [rnd(n, Hkv, D, seed=20 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
     q = rnd(sum(q_lens), H, D, seed=30, dtype=dtype)
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=1)
-    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
-    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "attention")
-    if bf16_attention == "tcgen05" and dtype == torch.bfloat16:
+    want = _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window)
+    for backend in _backends(dtype, D, page):
+        if backend == "tcgen05" and splits > 1:
+            continue                       # prefill has no key ranges
+        out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits, backend)
+        close(out, want, dtype, f"attention ({backend})")
+    if dtype == torch.bfloat16 and D in ops().TCGEN05_HEAD_DIMS:
         assert ops().attention_tcgen05_error(D) == 0
 
 
 @pytest.mark.parametrize("H,Hkv,D,page", [(16, 8, 128, 16), (6, 2, 64, 8), (10, 2, 48, 16)])
 @pytest.mark.parametrize("window", [0, 200])
-def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window, bf16_attention):
+def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window):
     """A serving step in the middle of a run: many requests decode, two bring portions of their
     prompts.  The one-token requests go to the decode kernel by a request list (long ones in
     several key ranges), the portions to the prefill kernel by a work list of blocks."""
-    if bf16_attention == "tcgen05" and D not in (64, 128):
-        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
     dtype = torch.bfloat16
     gen = torch.Generator().manual_seed(5)
     q_lens = [1, 1, 150, 1, 1, 1, 37, 1, 1, 2, 1]
@@ -312,50 +301,50 @@ def test_paged_attention_many_decodes_beside_portions(H, Hkv, D, page, window, b
     v = [rnd(n, Hkv, D, seed=60 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
     q = rnd(sum(q_lens), H, D, seed=31, dtype=dtype)
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 5, seed=2)
-    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None)
-    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "attention")
-    if bf16_attention == "tcgen05":
+    want = _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window)
+    for backend in _backends(dtype, D, page):
+        out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None, backend)
+        close(out, want, dtype, f"attention ({backend})")
+    if D in ops().TCGEN05_HEAD_DIMS:
         assert ops().attention_tcgen05_error(D) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,Hkv,D,page", [(4, 4, 64, 16), (8, 2, 128, 16), (20, 1, 48, 8), (3, 1, 256, 32),
                                            (8, 2, 128, 64), (6, 3, 64, 32)])      # pages of 32 and 64: whole pages by TMA
-@pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3)])
-@pytest.mark.parametrize("merge", ["cluster", "launch", "kernel"])
-def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits, bf16_attention, merge, monkeypatch):
+@pytest.mark.parametrize("window,splits", [(0, 1), (0, 7), (130, 1), (130, 3), (0, 11)])   # 11 ranges: no cluster
+def test_paged_attention_decode_batch(dtype, H, Hkv, D, page, window, splits):
     """Every request brings one token: the decode kernels."""
-    if (dtype == torch.float32 and bf16_attention != "mma") or bf16_attention == "tcgen05":
-        pytest.skip("float32 has one back end; decode has no tcgen05 kernel")
-    if merge != "launch" and (dtype == torch.float32 or bf16_attention == "simt" or splits == 1):
-        pytest.skip("only the tensor-core decode kernel merges its key ranges itself")
-    monkeypatch.setattr(ops(), "DECODE_MERGE", merge)
     kv_lens = [1, 64, 65, 300, 129, 1000, 17]
     q_lens = [1] * len(kv_lens)
     k = [rnd(n, Hkv, D, seed=10 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
     v = [rnd(n, Hkv, D, seed=20 + i, dtype=dtype).cpu() for i, n in enumerate(kv_lens)]
     q = rnd(len(kv_lens), H, D, seed=30, dtype=dtype)
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 3, seed=4)
-    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits)
-    close(out, _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window), dtype, "decode attention")
+    want = _attention_ref(q.cpu(), k, v, q_lens, D ** -0.5, window)
+    for backend in _backends(dtype, D, page):
+        if backend == "tcgen05":
+            continue                       # decode has no tcgen05 kernel: it is the mma decode kernel
+        out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, splits, backend)
+        close(out, want, dtype, f"decode attention ({backend})")
+    if dtype == torch.bfloat16 and D <= ops().MMA_MAX_HEAD_DIM:
+        assert ops().attention_mma_error(D) == 0
 
 
 @pytest.mark.parametrize("H,Hkv,D,page", [(32, 8, 128, 16), (6, 2, 64, 8), (20, 1, 48, 16), (3, 3, 256, 32),
                                            (16, 4, 128, 64)])
 @pytest.mark.parametrize("window", [0, 100])
 @pytest.mark.parametrize("source", ["tensor", "partials"])
-@pytest.mark.parametrize("merge", ["cluster", "launch"])
 @pytest.mark.parametrize("lengths", ["mixed", "long"])
-def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, merge, lengths, monkeypatch):
+def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, lengths):
     """Decode steps hand the fused q/k/v projection to the attention kernel, which applies the
     per-head norm and the rotary encoding and writes the newest key and value itself: the same
     outputs and the same cache as the norm/rotary kernel followed by the attention kernel."""
     from tinyserve_b200.parts.rotary import Rotary
     o = ops()
-    monkeypatch.setattr(o, "DECODE_MERGE", merge)
     # "long": two requests with so many keys that there are more key ranges than a cluster takes
     kv_lens_of = {"mixed": [1, 64, 65, 300, 129, 700, 17, 128], "long": [3000, 2177]}
-    if lengths == "long" and (merge == "launch" or source == "tensor"):
+    if lengths == "long" and source == "tensor":
         pytest.skip("one pass over the long contexts is enough")
     kv_lens = kv_lens_of[lengths]
     B, width = len(kv_lens), (H + 2 * Hkv) * D
@@ -381,34 +370,47 @@ def test_decode_attention_from_the_projection(H, Hkv, D, page, window, source, m
     view = SimpleNamespace(block_table=table, page_size=page, slot_mapping=slots)
     results = []
     for fused in (True, False):
-        monkeypatch.setattr(o, "FUSED_DECODE_QKV", fused)
         kc_i, vc_i = kc.clone(), vc.clone()
         launches = o.launch_count()
-        out = o.attention_from_qkv(qkv, pos, H, Hkv, D, rot, qw, kw, 1e-6, kc_i, vc_i, view, ctx, D ** -0.5, window)
+        out = o.attention_from_qkv(qkv, pos, H, Hkv, D, rot, qw, kw, 1e-6, kc_i, vc_i, view, ctx, D ** -0.5, window,
+                                   fused=fused)
         results.append((out, kc_i, vc_i, o.launch_count() - launches))
     (out_f, kc_f, vc_f, n_f), (out_u, kc_u, vc_u, n_u) = results
     assert n_f < n_u, "fewer kernels"
     live = [b for b in range(B) if b != dropped]
     assert torch.equal(kc_f, kc_u) and torch.equal(vc_f, vc_u), "the same cache, bit by bit"
     assert (out_f[live].float() - out_u[live].float()).abs().max().item() <= 2.0 ** -7 * out_u.float().abs().max().item()
-    # the request without a slot: the two-kernel path reads a stale key there, the fused one its own
-    assert torch.isfinite(out_f.float()).all()
+    # and both against the plain formulas in float64: per-head norm, rotary, attention over the old
+    # keys and the newest one (the request without a slot too: the fused kernel uses its own newest
+    # key although it writes none)
+    full = o.materialize(qkv).double().cpu().view(B, H + 2 * Hkv, D)
+    qh, kh, vh = full[:, :H], full[:, H:H + Hkv], full[:, H + Hkv:]
+    def norm_rope(x, w, at):
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w.double().cpu()
+        c, s_ = rot.cos.cpu()[at].double()[:, None], rot.sin.cpu()[at].double()[:, None]
+        x1, x2 = x.chunk(2, -1)
+        return torch.cat([x1 * c - x2 * s_, x2 * c + x1 * s_], -1)
+    at = pos.long().cpu()
+    qn = norm_rope(qh, qw, at).to(torch.bfloat16).double()
+    kn, vn = norm_rope(kh, kw, at).to(torch.bfloat16), vh.to(torch.bfloat16)
+    k_all = [torch.cat([k[b][:n - 1], kn[b][None]]) for b, n in enumerate(kv_lens)]
+    v_all = [torch.cat([v[b][:n - 1], vn[b][None]]) for b, n in enumerate(kv_lens)]
+    want = _attention_ref(qn, k_all, v_all, [1] * B, D ** -0.5, window)
+    close(out_f, want, torch.bfloat16, "fused path against float64")
+    close(out_u[live], want[live], torch.bfloat16, "two-kernel path against float64")
 
 
 @pytest.mark.parametrize("D,H,Hkv", [(128, 8, 2), (64, 6, 1)])
 @pytest.mark.parametrize("window", [0, 700])
-def test_prefill_attention_long_prompt(D, H, Hkv, window, bf16_attention):
+def test_prefill_attention_long_prompt(D, H, Hkv, window):
     """A prompt of 2,500 tokens after a prefix of 300 (20 and more key tiles per block, uneven last
     query block), beside a short request; the reference runs on the GPU in 32-bit."""
-    if bf16_attention == "simt":
-        pytest.skip("the 32-bit kernel has its own tests")
     page = 16
     kv_lens, q_lens = [2800, 75], [2500, 75]
     k = [rnd(n, Hkv, D, seed=70 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
     v = [rnd(n, Hkv, D, seed=80 + i, dtype=torch.bfloat16).cpu() for i, n in enumerate(kv_lens)]
     q = rnd(sum(q_lens), H, D, seed=33, dtype=torch.bfloat16)
     kc, vc, table = _paged(k, v, page, sum(-(-n // page) for n in kv_lens) + 4, seed=6)
-    out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None)
     want, at = [], 0
     for kb, vb, n in zip(k, v, q_lens):
         S = kb.shape[0]
@@ -421,16 +423,16 @@ def test_prefill_attention_long_prompt(D, H, Hkv, window, bf16_attention):
         vis = (j <= pos) & ((j > pos - window) if window else True)
         want.append(torch.einsum("hts,shd->thd", sc.masked_fill(~vis[None], float("-inf")).softmax(-1), vv))
         at += n
-    close(out, torch.cat(want), torch.bfloat16, "long prompt")
-    if bf16_attention == "tcgen05":
-        assert ops().attention_tcgen05_error(D) == 0
+    for backend in ("tcgen05", "mma"):
+        out = _run_attention(q, kc, vc, table, q_lens, kv_lens, page, D ** -0.5, window, None, backend)
+        close(out, torch.cat(want), torch.bfloat16, f"long prompt ({backend})")
+    assert ops().attention_tcgen05_error(D) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("splits", [1, 5])
-def test_attention_finds_one_far_key(dtype, splits, bf16_attention):
-    if bf16_attention == "tcgen05":
-        pytest.skip("decode has no tcgen05 kernel")
+@pytest.mark.parametrize("backend", ["mma", "simt"])
+def test_attention_finds_one_far_key(dtype, splits, backend):
     """Among 700 keys one, on a page of its own early in the sequence, matches the query: the
     output must be that key's value."""
     H, Hkv, D, page, n, far = 4, 2, 32, 16, 700, 37
@@ -440,14 +442,17 @@ def test_attention_finds_one_far_key(dtype, splits, bf16_attention):
     direction = torch.ones(D) / math.sqrt(D)
     k[far] = (direction * 40).to(dtype)
     q[0, :] = (direction * 40).to(dtype).cuda()
+    if dtype == torch.float32 and backend == "mma":
+        pytest.skip("float32 has one kernel")
     kc, vc, table = _paged([k], [v], page, 60, seed=2)
-    out = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, 0, splits)
+    run = lambda *a: _run_attention(*a, backend=backend)
+    out = run(q, kc, vc, table, [1], [n], page, 1.0, 0, splits)
     want = v[far].repeat_interleave(H // Hkv, 0)
     assert (out[0].float().cpu() - want.float()).abs().max().item() < 1e-3
     # with a window that ends one key after it, it is hidden; one wider, it is seen
-    hidden = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, n - 1 - far, splits)
+    hidden = run(q, kc, vc, table, [1], [n], page, 1.0, n - 1 - far, splits)
     assert (hidden[0].float().cpu() - want.float()).abs().max().item() > 0.1
-    seen = _run_attention(q, kc, vc, table, [1], [n], page, 1.0, n - far, splits)
+    seen = run(q, kc, vc, table, [1], [n], page, 1.0, n - far, splits)
     assert (seen[0].float().cpu() - want.float()).abs().max().item() < 1e-3
 
 
@@ -535,26 +540,24 @@ def test_repetition_penalty():
                                    (8, 40000, 512), (3, 24576, 4096)])
 @pytest.mark.parametrize("splits", [1, 2, 5])
 @pytest.mark.parametrize("f32_out", [False, True])
-@pytest.mark.parametrize("form", ["persistent", "tiled"])
-def test_gemm_tcgen05(M, N, K, splits, f32_out, form):
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_gemm_tcgen05(M, N, K, splits, f32_out, with_bias):
     o = ops()
     x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
     splits = min(splits, -(-K // 64))
-    # the persistent form is cut by blocks, not by splits: 148, 37 and 7 blocks
-    blocks = {1: 148, 2: 37}.get(splits, 7) if form == "persistent" else None
-    out = o._linear_tcgen05(x, w, f32_out, splits=splits, form=form, blocks=blocks)
+    bias = rnd(N, seed=3, dtype=torch.bfloat16 if M % 2 else torch.float32, scale=3.0) if with_bias else None
+    out = o._linear_tcgen05(x, w, f32_out, splits=splits, bias=bias)
     torch.cuda.synchronize()
     assert o.gemm_tcgen05_error() == 0, "a block gave up on a wait"
-    want = x.double() @ w.double().T
+    want = x.double() @ w.double().T + (bias.double() if with_bias else 0)
     close(out, want, torch.float32 if f32_out else torch.bfloat16, "tcgen05 gemm")
-    again = o._linear_tcgen05(x, w, f32_out, splits=splits, form=form, blocks=blocks)
+    again = o._linear_tcgen05(x, w, f32_out, splits=splits, bias=bias)
     assert torch.equal(out, again), "the split-K sum is the same every run"
     assert int(o._tile_counters(x.device).abs().sum()) == 0, "tile counters returned to zero"
 
 
 def test_linear_picks_tcgen05_and_falls_back():
     o = ops()
-    assert o.BF16_GEMM == "tcgen05"
     x, w = rnd(8, 4096, seed=1, dtype=torch.bfloat16), rnd(4096, 4096, seed=2, dtype=torch.bfloat16, scale=0.05)
     close(o.linear(x, w), x.double() @ w.double().T, torch.bfloat16, "decode-shaped")
     x2, w2 = rnd(8, 100, seed=3, dtype=torch.bfloat16), rnd(50, 100, seed=4, dtype=torch.bfloat16)
@@ -562,6 +565,11 @@ def test_linear_picks_tcgen05_and_falls_back():
     assert o.TCGEN05_MAX_TOKENS < 300
     x3 = rnd(300, 256, seed=5, dtype=torch.bfloat16)
     close(o.linear(x3, w[:64, :256].contiguous()), x3.double() @ w[:64, :256].double().T, torch.bfloat16, "many rows")
+    # with a bias: the tcgen05 epilogue for few rows, the library's bias epilogue for many
+    b = rnd(4096, seed=6, dtype=torch.bfloat16, scale=2.0)
+    close(o.linear(x, w, b), x.double() @ w.double().T + b.double(), torch.bfloat16, "bias, few rows")
+    x4 = rnd(300, 4096, seed=7, dtype=torch.bfloat16)
+    close(o.linear(x4, w, b), x4.double() @ w.double().T + b.double(), torch.bfloat16, "bias, many rows")
     assert o.gemm_tcgen05_error() == 0
 
 

@@ -7,9 +7,9 @@
 //            tiles that lie wholly below a warp's rows skip the mask;
 //   decode : requests that bring one token.  A block handles the heads of one KV group (up to 16
 //            rows) and one of `num_splits` key ranges; its 4 warps take 16 keys each of every
-//            64-key tile (3 stages in flight) and merge their partial softmax at the end.  The
-//            ranges are merged by the block of a (request, KV group) that finishes last, or by
-//            attention_combine_kernel when no counters are given.
+//            64-key tile (3 stages in flight) and merge their partial softmax at the end.  Up
+//            to 8 ranges are the blocks of a cluster and merge through distributed shared memory;
+//            more are merged by attention_combine_kernel.
 // Scores, running maxima, sums and the output accumulate in 32-bit; exp2 with scale * log2(e);
 // the probabilities are rounded to bfloat16 for P * V, as tinykernels.py:386-413 and 993 do.
 // Visibility as serve.py:668-680: key j is seen by the query at position p iff j <= p and, with a
@@ -52,7 +52,6 @@ struct MmaAttnParams {
   const int* tile_q0;
   float* part_o;            // [T, H, splits, D]
   float* part_ml;           // [T, H, splits, 2]  (max in the log2 domain, sum)
-  int* counters;            // [requests * gridDim.x] zeros: the block that arrives last merges the key ranges
   int cluster_merge;        // the key ranges of a (request, KV group) form a cluster and merge in shared memory
   int H, Hkv, page_shift, page_mask, max_blocks;
   int heads_per_tile, queries_per_tile, head_tiles;
@@ -620,7 +619,9 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     const int nxt = it + DEC_STAGES - 1;
     if (nxt < n_tiles) load_tile(nxt % DEC_STAGES, tile_begin + nxt, j_load);
     if (TMA) {
-      mbar_wait(smem_u32(&full[it % DEC_STAGES]), (it / DEC_STAGES) & 1, abort_flag);      // bounded
+      // bounded; a wait that ran out raises the block's abort flag and the status word, the loop
+      // goes on over whatever the stage holds, and the block stores no output at the end
+      mbar_wait(smem_u32(&full[it % DEC_STAGES]), (it / DEC_STAGES) & 1, abort_flag);
     } else {
       cp_async_commit();
       cp_async_wait<DEC_STAGES - 1>();
@@ -679,6 +680,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     }
   }
   __syncthreads();
+  const bool stores = !TMA || abort_flag_s == 0;
   for (int i = threadIdx.x; i < ng * D; i += THREADS) {
     const int r = i / D, d = i % D;
     float mx = -INFINITY;
@@ -694,7 +696,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     }
     const int head = kvh * G + g0 + r;
     if (p.num_splits == 1) {
-      p.out[((size_t)q_begin * p.H + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      if (stores) p.out[((size_t)q_begin * p.H + head) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     } else if (p.cluster_merge) {
       // this thread has read its four values of (r, d); the first warp's place now holds their sum
       sm_o[r * D + d] = num;
@@ -741,7 +743,7 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
           num = fmaf(wgt, os[s], num);
           den = fmaf(wgt, ls[s], den);
         }
-      p.out[((size_t)q_begin * p.H + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+      if (stores) p.out[((size_t)q_begin * p.H + kvh * G + g0 + r) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
     if (traced) timeline_mark_thread(45, split);        // merged and stored
     // no block leaves while a peer may still read its shared memory
@@ -749,45 +751,6 @@ __device__ __forceinline__ void attn_decode_body(const MmaAttnParams& p, const C
     cluster_wait();
     if (traced) timeline_mark_thread(46, split);
     return;
-  }
-  if (p.num_splits == 1 || p.counters == nullptr) return;
-
-  // The block of this (request, KV group) that arrives last merges the key ranges; nobody waits.
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int* counter = p.counters + (size_t)b * gridDim.x + blockIdx.x;
-    s_last = atomicAdd(counter, 1) == p.num_splits - 1;
-    if (s_last) *counter = 0;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  float* sm_w = sm_o;                                           // [num_splits][16] normalised weights
-  const size_t row0 = (size_t)q_begin * p.H + kvh * G + g0;
-  for (int r = threadIdx.x; r < ng; r += THREADS) {
-    const float* ml = p.part_ml + (row0 + r) * p.num_splits * 2;
-    float mx = -INFINITY;
-    for (int s = 0; s < p.num_splits; ++s) mx = fmaxf(mx, __ldcg(ml + 2 * s));
-    float den = 0.f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float ms = __ldcg(ml + 2 * s);
-      den += ms == -INFINITY ? 0.f : exp2f(ms - mx) * __ldcg(ml + 2 * s + 1);
-    }
-    const float inv = den > 0.f ? 1.f / den : 0.f;
-    for (int s = 0; s < p.num_splits; ++s) {
-      const float ms = __ldcg(ml + 2 * s);
-      sm_w[s * 16 + r] = ms == -INFINITY ? 0.f : exp2f(ms - mx) * inv;
-    }
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < ng * D; i += THREADS) {
-    const int r = i / D, d = i % D;
-    const float* po = p.part_o + (row0 + r) * p.num_splits * D + d;
-    float v = 0.f;
-    for (int s = 0; s < p.num_splits; ++s) v = fmaf(sm_w[s * 16 + r], __ldcg(po + (size_t)s * D), v);
-    p.out[(row0 + r) * D + d] = __float2bfloat16_rn(v);
   }
 }
 
@@ -830,21 +793,28 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
 
 TS_EXPORT int ts_attention_mma_head_dim() { return D; }
 
+// 1 if a block of the TMA decode kernel ever gave up on a wait since the library was loaded
+// (reads device memory: synchronises)
+TS_EXPORT int ts_attention_mma_error() {
+  int flag = 0;
+  if (cudaMemcpyFromSymbol(&flag, g_error_flag, sizeof(int)) != cudaSuccess) return -1;
+  return flag;
+}
+
 // decode_only != 0: every request brings one token (requests with another count are skipped);
-// decode_only == 2: up to 8 key ranges without counters are merged through the distributed shared
+// decode_only == 2: up to 8 key ranges are merged through the distributed shared
 // memory of a cluster (no scratch is touched, no second launch);
 // num_splits > 1 needs scratch: part_o T*H*splits*D floats, part_ml T*H*splits*2 floats.
 // tile_req / tile_q0 (optional, num_tiles ints each): for the prefill kernel the request and the
 // first query of every block of tile_queries queries; with decode_only the one-token requests of
 // a mixed batch and their tokens (the scratch then has num_tiles rows in place of T).
-// counters: num_requests * Hkv * ceil(group / 16) zeroed ints (they return to zero); with them the
-// key ranges are merged inside the decode kernel, without them by a second launch.
+// Key ranges that are no cluster are merged by a second launch.
 namespace {
 int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void* out, const void* k_cache,
                              const void* v_cache, const int* block_table, const int* cu_q, const int* kv_lens,
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
-                             float* part_ml, int* counters, int decode_only, const int* tile_req,
+                             float* part_ml, int decode_only, const int* tile_req,
                              const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream);
 }
 
@@ -852,12 +822,12 @@ TS_EXPORT int ts_paged_attention_mma(const void* q, void* out, const void* k_cac
                                      const int* block_table, const int* cu_q, const int* kv_lens,
                                      int num_tokens, int num_requests, int max_q_len, int H, int Hkv,
                                      int page_size, int max_blocks, float scale, int window,
-                                     int num_splits, float* part_o, float* part_ml, int* counters,
+                                     int num_splits, float* part_o, float* part_ml,
                                      int decode_only, const int* tile_req, const int* tile_q0, int num_tiles,
                                      int tile_queries, int num_pages, cudaStream_t stream) {
   return paged_attention_mma_impl(nullptr, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window, num_splits,
-                                  part_o, part_ml, counters, decode_only, tile_req, tile_q0, num_tiles,
+                                  part_o, part_ml, decode_only, tile_req, tile_q0, num_tiles,
                                   tile_queries, num_pages, stream);
 }
 
@@ -896,7 +866,7 @@ TS_EXPORT int ts_paged_attention_mma_from_qkv(const void* qkv, const float* part
   extra.k_cache_out = static_cast<bf16*>(k_cache); extra.v_cache_out = static_cast<bf16*>(v_cache);
   return paged_attention_mma_impl(&extra, nullptr, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                                   num_requests, 1, H, Hkv, page_size, max_blocks, scale, window, num_splits, part_o,
-                                  part_ml, nullptr, merge, nullptr, nullptr, 0, 0, num_pages, stream);
+                                  part_ml, merge, nullptr, nullptr, 0, 0, num_pages, stream);
 }
 
 namespace {
@@ -904,19 +874,18 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
                              const void* v_cache, const int* block_table, const int* cu_q, const int* kv_lens,
                              int num_tokens, int num_requests, int max_q_len, int H, int Hkv, int page_size,
                              int max_blocks, float scale, int window, int num_splits, float* part_o,
-                             float* part_ml, int* counters, int decode_only, const int* tile_req,
+                             float* part_ml, int decode_only, const int* tile_req,
                              const int* tile_q0, int num_tiles, int tile_queries, int num_pages, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && num_requests > 0 && max_q_len > 0, "paged_attention_mma: empty batch");
   TS_REQUIRE(H > 0 && Hkv > 0 && H % Hkv == 0, "paged_attention_mma: %d heads over %d KV heads", H, Hkv);
   TS_REQUIRE(page_size > 0 && (page_size & (page_size - 1)) == 0, "paged_attention_mma: page size %d is no power of two", page_size);
   TS_REQUIRE(num_splits >= 1 && num_splits <= 64, "paged_attention_mma: num_splits %d out of range", num_splits);
-  TS_REQUIRE(num_splits == 1 || (decode_only && ((part_o && part_ml) || (decode_only == 2 && num_splits <= 8 && !counters))),
+  TS_REQUIRE(num_splits == 1 || (decode_only && ((part_o && part_ml) || (decode_only == 2 && num_splits <= 8))),
              "paged_attention_mma: splits are for decode and need scratch");
   TS_REQUIRE(num_requests <= 65535, "paged_attention_mma: more than 65535 requests");
   MmaAttnParams p = from_qkv ? *from_qkv : MmaAttnParams{};
   p.q = (const bf16*)q; p.out = (bf16*)out; p.k_cache = (const bf16*)k_cache; p.v_cache = (const bf16*)v_cache;
   p.block_table = block_table; p.cu_q = cu_q; p.kv_lens = kv_lens; p.part_o = part_o; p.part_ml = part_ml;
-  p.counters = counters;
   p.cluster_merge = 0;
   p.tile_req = tile_req;
   p.tile_q0 = tile_q0;
@@ -931,14 +900,10 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
   cudaError_t e;
   if (decode_only) {
     p.heads_per_tile = 16; p.queries_per_tile = 1; p.head_tiles = (G + 15) / 16;
-    // whole pages by TMA where the sizes allow it (TINYSERVE_DECODE_TMA=0: never)
-    static const bool tma_allowed = [] {
-      const char* v = getenv("TINYSERVE_DECODE_TMA");
-      return !(v && v[0] == '0');
-    }();
+    // whole pages by TMA where the sizes allow it
     // (pages of 32 and 64 keys: measured on B200, 64 requests x 4096 keys, pages of 64: 6.67 TB/s by
     // TMA against 5.78 by cp.async; with pages of 16 both reach 5.4: the 4 KB pieces are what limits)
-    const bool tma = tma_allowed && TMA_HEAD && num_pages > 0 && page_size >= 32 && page_size <= BN &&
+    const bool tma = TMA_HEAD && num_pages > 0 && page_size >= 32 && page_size <= BN &&
                      ((uintptr_t)k_cache | (uintptr_t)v_cache) % 16 == 0;
     CUtensorMap mk, mv;
     if (tma) {
@@ -964,10 +929,9 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
       (tma ? configured_tma : configured) = true;
     }
     // tile_req / tile_q0 here: the one-token requests of a mixed batch and their tokens
-    TS_REQUIRE(tile_req == nullptr || counters == nullptr, "paged_attention_mma: a request list merges by its own launch");
     const int count = tile_req ? num_tiles : num_requests;
     dim3 grid(Hkv * p.head_tiles, num_splits, count);
-    if (decode_only == 2 && num_splits > 1 && num_splits <= 8 && counters == nullptr) {
+    if (decode_only == 2 && num_splits > 1 && num_splits <= 8) {
       p.cluster_merge = 1;
       e = tma ? ts_launch_cluster(attn_decode_tma_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), mk, mv, p)
               : ts_launch_cluster(attn_decode_kernel, grid, dim3(THREADS), smem, stream, dim3(1, num_splits, 1), p);
@@ -976,7 +940,7 @@ int paged_attention_mma_impl(const MmaAttnParams* from_qkv, const void* q, void*
     }
     if (tma) TS_LAUNCH("attn_decode_tma", attn_decode_tma_kernel, grid, THREADS, smem, stream, mk, mv, p);
     else TS_LAUNCH("attn_decode", attn_decode_kernel, grid, THREADS, smem, stream, p);
-    if (num_splits > 1 && counters == nullptr) {
+    if (num_splits > 1) {
       TS_LAUNCH("attention_combine", attention_combine_kernel, (tile_req ? count : num_tokens) * H,
                 D >= 128 ? 128 : (D >= 64 ? 64 : 32), 0, stream,
                 (const float*)part_o, (const float*)part_ml, p.out, num_splits, H, tile_q0);

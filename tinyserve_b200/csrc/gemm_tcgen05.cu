@@ -55,6 +55,7 @@ struct GemmParams {
   // Gated form (no K cuts, up to 64 tokens): the weight rows alternate in blocks of 64, gate rows
   // then the matching up rows, so a 128-row tile holds both; out [M, N / 2] = act(gate) * up.
   int gated_act;        // 0: off; else the activation's code + 1
+  VecParam bias;        // [N] added to every token's result (plain output only); ptr null: none
 };
 constexpr int SUMSQ_STRIDE = 16;     // tokens of the residual form (one token tile of 16)
 
@@ -286,6 +287,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   } else if (p.splits == 1) {
+    const float bn = (p.bias.ptr != nullptr && n < p.N) ? p.bias[n] : 0.f;
 #pragma unroll 1
     for (int c = 0; c < TILE_T; c += 8) {
       float v[8];
@@ -298,6 +300,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] *= row_scale[c + i];
       }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += bn;
       if (n < p.N) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -336,12 +340,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         __threadfence();
         const float* base = p.partials + (size_t)tile * (TILE_T * TILE_N);
         const size_t split_stride = (size_t)tiles * (TILE_T * TILE_N);
+        const float bn = (p.bias.ptr != nullptr && n < p.N) ? p.bias[n] : 0.f;
         // eight columns at a time, so that eight chains of loads are in flight per thread
 #pragma unroll 1
         for (int c0 = 0; c0 < TILE_T && t0 + c0 < p.M; c0 += 8) {
           float sum[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+          for (int i = 0; i < 8; ++i) sum[i] = bn;
           for (int s = 0; s < p.splits; ++s) {
             const float* src = base + s * split_stride + c0 * TILE_N + warp * 32 + lane;
 #pragma unroll
@@ -365,276 +370,6 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   timeline_mark(3);        // results stored
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
-  }
-}
-
-// ---------------------------------------------------------------------------- persistent form
-// One block per SM.  The iterations (tile, 64-wide slice of K), tiles in row-major order, form one
-// line; block b takes the b-th of gridDim.x equal stretches of it ("stream-K"), so every SM pulls
-// the same number of bytes.  A stretch is cut at tile borders into segments; the ring of stages
-// runs through all of them without draining: warp 0 loads, warp 1 issues the MMAs into one of two
-// accumulator buffers in tensor memory, warps 2..5 drain the other buffer (each warp owns the 32
-// lanes of its quarter).  A segment that covers its tile's whole K is written out directly.  Of a
-// tile that several blocks share, each block stores its partial to its own slot (a block has at
-// most two such segments: its first and its last), bumps the counter of (tile, quarter), and the
-// warp that arrives last adds the contributors in block order and writes the output: no waiting.
-constexpr int P_THREADS = 192;
-// Shared memory of the ring of stages.  About 100 KB lets the blocks of two consecutive products
-// share an SM, so that the next product's blocks set up and fetch their first weights (before
-// their pdl_wait) while this one still runs.
-#ifndef TS_PERSISTENT_SMEM_KB
-#define TS_PERSISTENT_SMEM_KB 100
-#endif
-
-struct PersistentParams {
-  void* out;
-  float* partials;      // [2 * blocks][TILE_T][128]
-  int* counters;        // [tiles * 4], zero between calls
-  int M, N, K, ldc, out_f32;
-  int n_tiles, t_tiles, kb_total, per_block;
-  long long total;      // tiles * kb_total
-};
-
-template <int TILE_T> struct PCfg {
-  static constexpr int STAGE_BYTES = W_STAGE_BYTES + TILE_T * BK * 2;
-  static constexpr int STAGES = (TS_PERSISTENT_SMEM_KB * 1024) / STAGE_BYTES > 12 ? 12 : (TS_PERSISTENT_SMEM_KB * 1024) / STAGE_BYTES;
-  static constexpr int ACCS = TILE_T <= 32 ? 4 : 2;          // two buffers of ACCS accumulators
-  static constexpr int BUF_COLS = ACCS * TILE_T;
-  static constexpr int TMEM_COLS = 2 * BUF_COLS < 32 ? 32 : 2 * BUF_COLS;
-  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 512;
-};
-
-// walks the segments of this block's stretch; i counts the slices inside the segment
-struct UnitIter {
-  long long f, f1;
-  int i, nkb, kb0, n_tile, t_tile, tile;
-  bool first;           // the stretch's first segment
-  __device__ __forceinline__ void decode(const PersistentParams& p) {
-    tile = static_cast<int>(f / p.kb_total);
-    kb0 = static_cast<int>(f - (long long)tile * p.kb_total);
-    nkb = static_cast<int>(min((long long)(p.kb_total - kb0), f1 - f));
-    n_tile = tile % p.n_tiles;
-    t_tile = tile / p.n_tiles;
-  }
-  __device__ __forceinline__ void start(const PersistentParams& p) {
-    f = (long long)blockIdx.x * p.per_block;
-    f1 = min(p.total, f + p.per_block);
-    i = 0;
-    first = true;
-    if (f < f1) decode(p);
-  }
-  __device__ __forceinline__ bool valid(const PersistentParams&) const { return f < f1; }
-  __device__ __forceinline__ bool whole(const PersistentParams& p) const { return kb0 == 0 && nkb == p.kb_total; }
-  __device__ __forceinline__ void next_block(const PersistentParams& p) {
-    if (++i >= nkb) next_unit(p);
-  }
-  __device__ __forceinline__ void next_unit(const PersistentParams& p) {
-    f += nkb;
-    i = 0;
-    first = false;
-    if (f < f1) decode(p);
-  }
-};
-
-template <int TILE_T>
-__global__ void __launch_bounds__(P_THREADS)
-gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                          PersistentParams p) {
-  using C = PCfg<TILE_T>;
-  extern __shared__ char smem_raw[];
-  char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  char* ctrl = smem + (size_t)C::STAGES * C::STAGE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(ctrl);            // [STAGES]
-  uint64_t* empty = full + C::STAGES;                            // [STAGES]
-  uint64_t* acc_full = empty + C::STAGES;                        // [2]
-  uint64_t* acc_empty = acc_full + 2;                            // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  pdl_trigger();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(smem_u32(&full[s]), 1);
-      mbar_init(smem_u32(&empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&acc_full[b]), 1);
-      mbar_init(smem_u32(&acc_empty[b]), 4);
-    }
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                 ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)C::TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  tcgen05_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      // weight tiles of the first round are fetched before pdl_wait(), their token tiles after
-      UnitIter it;
-      it.start(p);
-      uint32_t count = 0;
-      for (UnitIter a = it; a.valid(p) && count < (uint32_t)C::STAGES; a.next_block(p), ++count) {
-        const uint32_t bar = smem_u32(&full[count]);
-        mbar_expect_tx(bar, C::STAGE_BYTES);
-        tma_load_2d(smem_u32(smem + (size_t)count * C::STAGE_BYTES), &map_w, bar, (a.kb0 + a.i) * BK, a.n_tile * TILE_N);
-      }
-      pdl_wait();
-      count = 0;
-      for (; it.valid(p) && count < (uint32_t)C::STAGES; it.next_block(p), ++count)
-        tma_load_2d(smem_u32(smem + (size_t)count * C::STAGE_BYTES + W_STAGE_BYTES), &map_x, smem_u32(&full[count]),
-                    (it.kb0 + it.i) * BK, it.t_tile * TILE_T);
-      uint32_t armed = count;
-      for (; it.valid(p); it.next_block(p), ++count) {
-        const uint32_t s = count % C::STAGES, round = count / C::STAGES;
-        if (!mbar_wait(smem_u32(&empty[s]), (round & 1) ^ 1, abort_flag)) break;
-        const uint32_t bar = smem_u32(&full[s]);
-        mbar_expect_tx(bar, C::STAGE_BYTES);
-        char* stage = smem + (size_t)s * C::STAGE_BYTES;
-        tma_load_2d(smem_u32(stage), &map_w, bar, (it.kb0 + it.i) * BK, it.n_tile * TILE_N);
-        tma_load_2d(smem_u32(stage + W_STAGE_BYTES), &map_x, bar, (it.kb0 + it.i) * BK, it.t_tile * TILE_T);
-        armed = count + 1;
-      }
-      if (*abort_flag) {
-        const uint32_t from = armed > (uint32_t)C::STAGES ? armed - C::STAGES : 0;
-        for (uint32_t i = from; i < armed; ++i) {
-          const uint32_t bar = smem_u32(&full[i % C::STAGES]);
-          for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar, (i / C::STAGES) & 1); ++w) {}
-        }
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      pdl_wait();
-      const uint32_t idesc = instr_desc(TILE_T);
-      UnitIter it;
-      it.start(p);
-      uint32_t count = 0, j = 0;
-      bool ok = true;
-      for (; ok && it.valid(p); it.next_unit(p), ++j) {
-        const uint32_t b = j & 1, around = j >> 1;
-        if (around > 0) ok = mbar_wait(smem_u32(&acc_empty[b]), (around & 1) ^ 1, abort_flag);
-        if (!ok) break;
-        tcgen05_fence_after();
-        for (int i = 0; i < it.nkb; ++i, ++count) {
-          const uint32_t s = count % C::STAGES;
-          ok = mbar_wait(smem_u32(&full[s]), (count / C::STAGES) & 1, abort_flag);
-          if (!ok) break;
-          tcgen05_fence_after();
-          const uint32_t a0 = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-          const uint32_t b0 = a0 + W_STAGE_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / 16; ++k)
-            umma(tmem_base + b * C::BUF_COLS + (k % C::ACCS) * TILE_T, smem_desc(a0 + k * 32), smem_desc(b0 + k * 32),
-                 idesc, (i > 0 || k >= C::ACCS) ? 1u : 0u);
-          tcgen05_commit(smem_u32(&empty[s]));
-        }
-        if (ok) tcgen05_commit(smem_u32(&acc_full[b]));
-      }
-    }
-  } else {
-    // epilogue warps: quarter q of the 128 rows
-    pdl_wait();
-    const int q = warp & 3;
-    UnitIter it;
-    it.start(p);
-    uint32_t j = 0;
-    for (; it.valid(p); it.next_unit(p), ++j) {
-      const uint32_t b = j & 1;
-      bool have = mbar_wait(smem_u32(&acc_full[b]), (j >> 1) & 1, abort_flag);
-      have = __all_sync(0xffffffffu, have);
-      if (!have) break;
-      tcgen05_fence_after();
-      const int row = q * 32 + lane;
-      const int n = it.n_tile * TILE_N + row;
-      const int t0 = it.t_tile * TILE_T;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + b * C::BUF_COLS;
-      const bool whole = it.whole(p);
-      float* mine = p.partials + (size_t)(2 * blockIdx.x + (it.first ? 0 : 1)) * (TILE_T * TILE_N);
-#pragma unroll 1
-      for (int c = 0; c < TILE_T; c += 8) {
-        float v[8];
-        tmem_load8(taddr + c, v);
-#pragma unroll
-        for (int a = 1; a < C::ACCS; ++a) {
-          float t[8];
-          tmem_load8(taddr + a * TILE_T + c, t);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] += t[e];
-        }
-        if (whole) {
-          if (n < p.N) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int m = t0 + c + e;
-              if (m < p.M) {
-                if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = v[e];
-                else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[e]);
-              }
-            }
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) mine[(c + e) * TILE_N + row] = v[e];
-        }
-      }
-      // the accumulator buffer is free again
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&acc_empty[b]));
-      if (!whole) {
-        // blocks whose stretches touch this tile
-        const long long t_begin = (long long)it.tile * p.kb_total;
-        const int b_first = static_cast<int>(t_begin / p.per_block);
-        const int b_last = static_cast<int>((t_begin + p.kb_total - 1) / p.per_block);
-        __threadfence();
-        __syncwarp();
-        int last = 0;
-        if (lane == 0) {
-          last = atomicAdd(&p.counters[it.tile * 4 + q], 1) == b_last - b_first;
-          if (last) p.counters[it.tile * 4 + q] = 0;
-        }
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-#pragma unroll 1
-          for (int c0 = 0; c0 < TILE_T && t0 + c0 < p.M; c0 += 8) {
-            float sum[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) sum[e] = 0.f;
-            for (int cb = b_first; cb <= b_last; ++cb) {
-              // the tile is the contributor's first segment iff its stretch starts inside the tile
-              const int slot = 2 * cb + (((long long)cb * p.per_block) / p.kb_total == it.tile ? 0 : 1);
-              const float* src = p.partials + (size_t)slot * (TILE_T * TILE_N) + row;
-#pragma unroll
-              for (int e = 0; e < 8; ++e) sum[e] += __ldcg(src + (c0 + e) * TILE_N);
-            }
-            if (n < p.N) {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const int m = t0 + c0 + e;
-                if (m < p.M) {
-                  if (p.out_f32) static_cast<float*>(p.out)[(size_t)m * p.ldc + n] = sum[e];
-                  else static_cast<bf16*>(p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[e]);
-                }
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-  tcgen05_fence_before();
-  __syncthreads();
-  if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((uint32_t)C::TMEM_COLS) : "memory");
   }
 }
@@ -673,20 +408,6 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, di
   return 0;
 }
 
-template <int TILE_T>
-int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const PersistentParams& p, int grid,
-                      cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_wx_persistent_kernel<TILE_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)PCfg<TILE_T>::SMEM);
-    if (e != cudaSuccess) return ts_fail("gemm_tcgen05: %s", cudaGetErrorString(e));
-    configured = true;
-  }
-  TS_LAUNCH("gemm_tcgen05_persistent", gemm_wx_persistent_kernel<TILE_T>, grid, P_THREADS, PCfg<TILE_T>::SMEM, stream, mw, mx, p);
-  return 0;
-}
-
 }  // namespace
 
 // 1 if a block ever gave up on a wait since the library was loaded (reads device memory: syncs)
@@ -711,14 +432,17 @@ namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, int gated_act, cudaStream_t stream);
+               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, cudaStream_t stream);
 }
 
+// bias: [N] float or bfloat16 (bias_is_f32), added to every token's result; needs an output
+// (not with out == nullptr, where only partial tiles are produced).  nullptr: none.
 TS_EXPORT int ts_gemm_tcgen05(const void* x, const void* w, void* out, int M, int N, int K, long long ldx,
                               long long ldw, long long ldc, int out_f32, int splits, float* partials,
-                              int* counters, cudaStream_t stream) {
+                              int* counters, const void* bias, int bias_is_f32, cudaStream_t stream) {
+  TS_REQUIRE(bias == nullptr || out != nullptr, "gemm_tcgen05: a bias needs an output, not partial tiles only");
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, nullptr, 0, 0.f,
-                    nullptr, nullptr, 0, nullptr, nullptr, 0, stream);
+                    nullptr, nullptr, 0, nullptr, nullptr, 0, bias, bias_is_f32, stream);
 }
 
 // The same product with extras.  The first two are for up to 16 tokens.
@@ -745,14 +469,14 @@ TS_EXPORT int ts_gemm_tcgen05_fused(const void* x, const void* w, void* out, int
   TS_REQUIRE(residual == nullptr || (norm_w && hprime && sumsq_out && splits <= 8),
              "gemm_tcgen05: the residual form needs the norm's weight, both outputs and at most 8 cuts");
   return gemm_tiled(x, w, out, M, N, K, ldx, ldw, ldc, out_f32, splits, partials, counters, x_sumsq, x_tiles,
-                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, gated_act, stream);
+                    x_eps, residual, norm_w, norm_w_is_f32, hprime, sumsq_out, gated_act, nullptr, 0, stream);
 }
 
 namespace {
 int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, long long ldx, long long ldw,
                long long ldc, int out_f32, int splits, float* partials, int* counters, const float* x_sumsq,
                int x_tiles, float x_eps, float* residual, const void* norm_w, int norm_w_is_f32, void* hprime,
-               float* sumsq_out, int gated_act, cudaStream_t stream) {
+               float* sumsq_out, int gated_act, const void* bias, int bias_is_f32, cudaStream_t stream) {
   TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
   TS_REQUIRE(M <= 65535 * 128, "gemm_tcgen05: too many rows");
   TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
@@ -771,6 +495,7 @@ int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, lon
   p.residual = residual; p.norm_w = VecParam{norm_w, norm_w_is_f32};
   p.hprime = static_cast<bf16*>(hprime); p.sumsq_out = sumsq_out;
   p.gated_act = gated_act;
+  p.bias = VecParam{bias, bias_is_f32};
   dim3 grid((N + TILE_N - 1) / TILE_N, (M + tile_t - 1) / tile_t, splits);
   switch (tile_t) {
     case 16: return launch<16>(mw, mx, p, grid, stream);
@@ -780,40 +505,3 @@ int gemm_tiled(const void* x, const void* w, void* out, int M, int N, int K, lon
   }
 }
 }  // namespace
-
-// scratch floats of the persistent form for `blocks` blocks
-TS_EXPORT long long ts_gemm_tcgen05_persistent_scratch(int M, int blocks) {
-  const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  return 2LL * blocks * tile_t * TILE_N;
-}
-
-// The persistent (stream-K) form with `blocks` blocks (one per SM).  partials holds
-// ts_gemm_tcgen05_persistent_scratch floats; counters 4 ints per tile, all zero.
-TS_EXPORT int ts_gemm_tcgen05_persistent(const void* x, const void* w, void* out, int M, int N, int K,
-                                         long long ldx, long long ldw, long long ldc, int out_f32, int blocks,
-                                         float* partials, int* counters, cudaStream_t stream) {
-  TS_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: empty operand");
-  TS_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_tcgen05: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA), got K=%d", K);
-  TS_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
-  TS_REQUIRE(blocks >= 1 && partials && counters, "gemm_tcgen05: the persistent form needs blocks, scratch and counters");
-  const int tile_t = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
-  CUtensorMap mw, mx;
-  TS_REQUIRE(make_map(&mw, w, N, K, ldw, TILE_N), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the weights");
-  TS_REQUIRE(make_map(&mx, x, M, K, ldx, tile_t), "gemm_tcgen05: cuTensorMapEncodeTiled failed for the activations");
-  PersistentParams p;
-  p.out = out; p.partials = partials; p.counters = counters;
-  p.M = M; p.N = N; p.K = K; p.ldc = (int)ldc; p.out_f32 = out_f32;
-  p.n_tiles = (N + TILE_N - 1) / TILE_N;
-  p.t_tiles = (M + tile_t - 1) / tile_t;
-  p.kb_total = (K + BK - 1) / BK;
-  p.total = (long long)p.n_tiles * p.t_tiles * p.kb_total;
-  long long grid = blocks < p.total ? blocks : p.total;
-  p.per_block = (int)((p.total + grid - 1) / grid);
-  grid = (p.total + p.per_block - 1) / p.per_block;        // no block without work
-  switch (tile_t) {
-    case 16: return launch_persistent<16>(mw, mx, p, (int)grid, stream);
-    case 32: return launch_persistent<32>(mw, mx, p, (int)grid, stream);
-    case 64: return launch_persistent<64>(mw, mx, p, (int)grid, stream);
-    default: return launch_persistent<128>(mw, mx, p, (int)grid, stream);
-  }
-}

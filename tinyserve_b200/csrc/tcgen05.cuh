@@ -37,6 +37,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   *abort_flag = 1;
   atomicExch(&g_error_flag, 1);
+  ts_raise_status(TS_STATUS_WAIT, 1);
   return false;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {

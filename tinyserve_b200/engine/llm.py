@@ -214,6 +214,7 @@ class LLM:
 
     def _finish_async(self, live, host, event, raw) -> list:
         event.synchronize()
+        self.runner.raise_on_device_error()
         tokens = host.tolist()
         outputs = []
         for i, req, at in live:
@@ -261,6 +262,7 @@ class LLM:
         n = len(live)
         self._tokens_host[:n].copy_(tokens_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.runner.raise_on_device_error()
         tokens = self._tokens_host[:n].tolist()
         self.num_generated_tokens += n
         for i, req in enumerate(live):

@@ -288,6 +288,12 @@ class ModelRunner:
         device (None if nothing is wanted).  The entries' tokens are computed afterwards."""
         return self.launch(self.prepare(entries))
 
+    def raise_on_device_error(self):
+        """Raise ``ops.DeviceError`` if a kernel has reported that it gave up on a wait or met an
+        index out of range.  Reads host memory only: call it after a synchronisation that covers
+        the steps in question (reading tokens or logits back is one)."""
+        ops.raise_on_device_error()
+
     def state_slots_on_device(self, n):
         """int32 [n] view of the state slots of the step that was launched last."""
         return self._seg(self._dev, "state_slots", n)

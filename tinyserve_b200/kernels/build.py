@@ -27,6 +27,8 @@ NVCC_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "--shared", "-Xcompiler", "-fPIC
 
 _lock = threading.Lock()
 _loaded: dict = {}
+#: called with every library right after it is loaded (the bindings register their status words)
+on_load: list = []
 
 
 class BuildError(RuntimeError):
@@ -120,6 +122,8 @@ def load_unit(source: str, defines: dict | None = None) -> ctypes.CDLL:
     path = compile_unit(source, defines)
     lib = ctypes.CDLL(path)
     lib.ts_last_error.restype = ctypes.c_char_p
+    for hook in on_load:
+        hook(lib)
     with _lock:
         _loaded[key] = lib
     return lib

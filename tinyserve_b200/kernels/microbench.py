@@ -1,6 +1,6 @@
 """Time one kernel of the package at a given size, after warm-up, with CUDA events.
 
-    python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|tcgen05_tiled|tcgen05_persistent|cublas]
+    python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|cublas]
     python -m tinyserve_b200.kernels.microbench attention --batch 8 --q-len 1 --kv-len 640
     python -m tinyserve_b200.kernels.microbench norm --rows 8 --n 4096
     python -m tinyserve_b200.kernels.microbench rope --rows 2048
@@ -50,11 +50,9 @@ def bench_gemm(a):
     copies = a.copies or max(2, min(16, int(300e6 // nbytes) + 1))
     ws = [torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
-    form = "tiled" if a.impl == "tcgen05_tiled" else ("persistent" if a.impl == "tcgen05_persistent" else ops.TCGEN05_FORM)
-    splits = (a.splits or ops.gemm_splits(a.m, a.n, a.k)) if form == "tiled" else None
+    splits = a.splits or ops.gemm_splits(a.m, a.n, a.k)
     if a.impl.startswith("tcgen05"):
-        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, form=form, blocks=a.blocks or None,
-                                           partials_only=a.partials_only)
+        fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, partials_only=a.partials_only)
     else:
         fn = lambda i: torch.mm(x, ws[i].t())
     us = _time(fn, copies, a.iters, a.graph)
@@ -84,7 +82,8 @@ def bench_attention(a):
     ctx = SimpleNamespace(cu_q=cu, kv_lens=kv, num_requests=B, max_q_len=q_len, max_kv_len=kv_len,
                           host={"cu_q": cu.tolist(), "kv_lens": kv.tolist()}, tile_cache={})
     views = [SimpleNamespace(block_table=t, page_size=page) for t in tables]
-    fn = lambda i: ops.paged_attention(q, kc, vc, views[i], ctx, D ** -0.5, 0, num_splits=a.splits or None)
+    fn = lambda i: ops.paged_attention(q, kc, vc, views[i], ctx, D ** -0.5, 0, num_splits=a.splits or None,
+                                     backend=a.backend or None)
     us = _time(fn, copies, a.iters, a.graph)
     kv_bytes = B * kv_len * 2 * Hkv * D * 2
     flops = 4.0 * B * H * D * (q_len * kv_len - q_len * (q_len - 1) / 2)
@@ -132,8 +131,7 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--blocks", type=int, default=0, help="blocks of the persistent product (default: one per SM)")
-    ap.add_argument("--impl", choices=["tcgen05", "tcgen05_tiled", "tcgen05_persistent", "cublas"], default="tcgen05")
+    ap.add_argument("--impl", choices=["tcgen05", "cublas"], default="tcgen05")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--q-len", type=int, default=1)
     ap.add_argument("--kv-len", type=int, default=640)
@@ -141,6 +139,8 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--backend", choices=["tcgen05", "mma", "simt"], default="",
+                    help="attention: a slower kernel than the one the head size selects")
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=0)
     ap.add_argument("--iters", type=int, default=20)

@@ -17,24 +17,84 @@ SUPPORTED_HEAD_DIMS = tuple(range(16, 513, 16))
 _DTYPE = {torch.float32: 0, torch.bfloat16: 1}
 
 _launches = 0
-#: bfloat16 matrix products: "tcgen05" (this package's TMA + tcgen05 kernel for up to
-#: TCGEN05_MAX_TOKENS rows, cuBLAS above), "cublas" (torch.mm) or "simt" (the FMA kernel)
-BF16_GEMM = "tcgen05"
-#: measured on B200 at Qwen3-8B shapes, whole decode steps: 32 tokens +8 %, 48 +4 %, 64 +2 % over cuBLAS
-TCGEN05_MAX_TOKENS = int(os.environ.get("TINYSERVE_TCGEN05_MAX_TOKENS", "64"))
-#: bfloat16 attention: "tcgen05" (prefill of head sizes 64 and 128 on the tcgen05 kernel, the rest
-#: as "mma"), "mma" (mma.sync kernels, head sizes up to 256) or "simt" (32-bit FMA kernel)
-BF16_ATTENTION = os.environ.get("TINYSERVE_BF16_ATTENTION", "tcgen05")
+#: bfloat16 matrix products of up to this many rows run on this package's TMA + tcgen05 kernel,
+#: larger ones go to cuBLAS (measured on B200 at Qwen3-8B shapes, whole decode steps: 32 tokens
+#: +8 %, 48 +4 %, 64 +2 % over cuBLAS)
+TCGEN05_MAX_TOKENS = 64
+#: bfloat16 attention is chosen by head size: the tcgen05 prefill kernel for these head sizes, the
+#: mma.sync kernels (prefill of other head sizes, every decode) up to MMA_MAX_HEAD_DIM, the 32-bit
+#: kernel above that
 TCGEN05_HEAD_DIMS = (64, 128)
 MMA_MAX_HEAD_DIM = 256
 MMA_PREFILL_ROWS = 64           # query rows of a block of the mma prefill kernel (4 warps of 16)
-#: how the key ranges of split-KV decode are merged: "cluster" (the ranges of a (request, KV group)
-#: are the blocks of a thread-block cluster and merge through distributed shared memory; up to 8
-#: ranges, more fall back to "launch"), "launch" (a second, tiny kernel) or "kernel" (inside the
-#: decode kernel, through global memory, by the block that finishes last).  Measured on B200 from
-#: CUDA graphs, 8 requests x 640 keys: 14.4 us with the second launch, 18.9 us merged in the kernel.
-DECODE_MERGE = os.environ.get("TINYSERVE_DECODE_MERGE", "cluster")
+#: the key ranges of a split-KV decode are the blocks of a thread-block cluster and merge through
+#: distributed shared memory when there are at most this many; more are merged by a second kernel
+#: (measured on B200 from CUDA graphs, 8 requests x 640 keys: 14.4 us with the second launch,
+#: less in the cluster)
 CLUSTER_MERGE_MAX_SPLITS = 8
+#: the SM count all split heuristics were measured at; the device's own count is used at run time
+MEASURED_NUM_SMS = 148
+_num_sms = None
+
+
+def num_sms() -> int:
+    """Multiprocessors of the current device (148 where no device is visible)."""
+    global _num_sms
+    if _num_sms is None:
+        if torch.cuda.is_available():
+            _num_sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        else:
+            return MEASURED_NUM_SMS
+    return _num_sms
+
+
+# ----------------------------------------------------------------------------- device status
+# Kernels never trap: a bounded wait that ran out, or (in a bounds-checking build) an index outside
+# its buffer, stores a code into a few words of pinned host memory; see common.cuh.
+STATUS_WORDS = 8
+_BOUNDS_CODES = {1: "a token id outside the vocabulary", 2: "a cache slot outside the pool",
+                 3: "a page number outside the pool", 4: "a position outside the tables",
+                 5: "a row outside the batch", 6: "a state slot outside the pool",
+                 7: "a request index outside the batch"}
+_status = None
+
+
+def status_words():
+    """The int32 status words (a numpy view): pinned host memory that every loaded library writes."""
+    global _status
+    if _status is None:
+        t = torch.zeros(STATUS_WORDS, dtype=torch.int32)
+        if torch.cuda.is_available():
+            t = t.pin_memory()
+        _status = (t, t.numpy())
+    return _status[1]
+
+
+def _register_status(lib):
+    if hasattr(lib, "ts_set_status_words") and torch.cuda.is_available():
+        status_words()
+        if lib.ts_set_status_words(c_void_p(_status[0].data_ptr())) != 0:
+            raise RuntimeError("a kernel library did not take the status words")
+
+
+build.on_load.append(_register_status)
+
+
+class DeviceError(RuntimeError):
+    """A kernel reported that it gave up (a wait ran out) or met an index out of range."""
+
+
+def raise_on_device_error() -> None:
+    """Raise if any kernel has stored a status code since the process started.  Reads host memory
+    only; call it after a synchronisation that covers the kernels in question.  The codes stay: an
+    engine that has seen one does not go on."""
+    w = status_words()
+    if w[0]:
+        raise DeviceError("a kernel gave up on a bounded wait (mbarrier): its results are not valid; "
+                          "the engine stops")
+    if w[1]:
+        raise DeviceError(f"a kernel met {_BOUNDS_CODES.get(int(w[1]), 'an index out of range')}; "
+                          "the access was skipped and the engine stops")
 
 
 class SplitPartials:
@@ -63,8 +123,9 @@ class SplitPartials:
 
 _NO_PARTIALS = (c_void_p(0), c_int(0), c_int(0), c_int(0), c_int(0))
 
-#: let the product before a residual add + norm do the add itself (PendingProduct, ScaledRows)
-FUSED_RESIDUAL = os.environ.get("TINYSERVE_FUSED_RESIDUAL", "1") != "0"
+#: up to this many tokens the product before a residual add + norm does the add itself
+#: (PendingProduct, ScaledRows), the gate/up product applies the activation in its epilogue and the
+#: decode attention kernel takes the q/k/v projection as it is
 FUSED_MAX_TOKENS = 16
 FUSED_MAX_SPLITS = 8
 
@@ -87,7 +148,7 @@ class PendingProduct:
         return min(gemm_splits(M, self.weight.shape[0], K, partials=True), FUSED_MAX_SPLITS)
 
     def partials(self):
-        if SPLIT_PARTIALS and self.splits() > 1:
+        if self.splits() > 1:
             return _linear_tcgen05(self.x, self.weight, False, partials_only=True)
         return self.materialize()
 
@@ -208,10 +269,7 @@ def _gemm():
 
 
 def _gemm_tcgen05():
-    defines = {}
-    if "TINYSERVE_GEMM_RING_KB" in os.environ:
-        defines["TS_GEMM_RING_KB"] = int(os.environ["TINYSERVE_GEMM_RING_KB"])
-    return build.load_unit("gemm_tcgen05.cu", defines)
+    return build.load_unit("gemm_tcgen05.cu")
 
 
 _counters: dict = {}
@@ -234,10 +292,10 @@ def gemm_splits(M, N, K, partials=False):
     tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
     tiles = -(-N // 128) * -(-M // tile_t)
     slices = -(-K // 64)
-    if tiles >= NUM_SMS:
+    if tiles >= num_sms():
         return 1
     if partials:
-        splits = max(1, min(2 * NUM_SMS // tiles, slices // 4, 8))
+        splits = max(1, min(2 * num_sms() // tiles, slices // 4, 8))
     else:
         splits = max(1, min(-(-160 // tiles), slices // 4, 16))
         if tile_t >= 64:
@@ -251,45 +309,25 @@ def gemm_tcgen05_error() -> int:
     return _gemm_tcgen05().ts_gemm_tcgen05_error()
 
 
-def _tcgen05_ok(x, weight, bias):
-    return (bias is None and x.shape[0] <= TCGEN05_MAX_TOKENS and x.shape[1] % 8 == 0
+def _tcgen05_ok(x, weight):
+    return (x.shape[0] <= TCGEN05_MAX_TOKENS and x.shape[1] % 8 == 0
             and x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0
             and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-#: "persistent" (stream-K: one block per SM takes an equal stretch of the work) or "tiled" (one
-#: block per row tile and K cut)
-TCGEN05_FORM = os.environ.get("TINYSERVE_GEMM_FORM", "tiled")
-#: let a product cut along K hand its partial tiles to the next kernel instead of adding them up
-SPLIT_PARTIALS = os.environ.get("TINYSERVE_SPLIT_PARTIALS", "1") != "0"
-_partials: dict = {}
+def _tile_t(M):
+    return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
 
 
-def _persistent_scratch(device):
-    key = str(device)
-    if key not in _partials:
-        _partials[key] = torch.empty(2 * NUM_SMS * 128 * 128, dtype=torch.float32, device=device)
-    return _partials[key]
-
-
-def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None, partials_only=False, scale=None,
-                    gated=0):
+def _linear_tcgen05(x, weight, out_float32, splits=None, partials_only=False, scale=None, gated=0, bias=None):
     """``scale``: the ScaledRows whose ``data`` is ``x``; ``gated``: activation code + 1 of the
-    gated epilogue (out [M, N / 2]); both tiled form only."""
+    gated epilogue (out [M, N / 2]); ``bias`` [N]: added in the epilogue (not with the others)."""
     M, K = x.shape
     N = weight.shape[0]
     out_cols = N // 2 if gated else N
     out = None if partials_only else torch.empty(
         M, out_cols, dtype=torch.float32 if out_float32 else torch.bfloat16, device=x.device)
-    form = "tiled" if partials_only or scale is not None or gated else (form or TCGEN05_FORM)
     lib = _gemm_tcgen05()
-    if form == "persistent":
-        blocks = min(blocks or NUM_SMS, NUM_SMS)
-        _check(lib, lib.ts_gemm_tcgen05_persistent(
-            _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
-            c_longlong(weight.stride(0)), c_longlong(N), c_int(1 if out_float32 else 0), c_int(blocks),
-            _ptr(_persistent_scratch(x.device)), _ptr(_tile_counters(x.device)), _stream()))
-        return out
     lib.ts_gemm_tcgen05_scratch.restype = c_longlong
     if splits is None:
         splits = gemm_splits(M, N, K, partials=partials_only)
@@ -301,6 +339,8 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None,
         partials = torch.empty(need, dtype=torch.float32, device=x.device)
         counters = None if partials_only else _tile_counters(x.device)
     if scale is not None or gated:
+        if bias is not None:
+            raise ValueError("the scaled-rows and gated products take no bias")
         _check(lib, lib.ts_gemm_tcgen05_fused(
             _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
             c_longlong(weight.stride(0)), c_longlong(out_cols), c_int(1 if out_float32 else 0), c_int(splits),
@@ -310,10 +350,10 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, form=None, blocks=None,
         _check(lib, lib.ts_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K),
                                         c_longlong(x.stride(0)), c_longlong(weight.stride(0)), c_longlong(N),
                                         c_int(1 if out_float32 else 0), c_int(splits), _ptr(partials),
-                                        _ptr(counters), _stream()))
+                                        _ptr(counters), _ptr(bias),
+                                        c_int(_vec_flag(bias, torch.bfloat16) if bias is not None else 0), _stream()))
     if partials_only:
-        tile_t = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
-        return SplitPartials(partials, splits, M, N, tile_t, torch.bfloat16)
+        return SplitPartials(partials, splits, M, N, _tile_t(M), torch.bfloat16)
     return out
 
 
@@ -325,10 +365,7 @@ def _attention(head_dim: int):
 
 
 def _attention_mma(head_dim: int):
-    defines = {"TS_HEAD_DIM": head_dim}
-    if os.environ.get("TINYSERVE_PREFILL_WARPS"):
-        defines["TS_PREFILL_WARPS"] = int(os.environ["TINYSERVE_PREFILL_WARPS"])
-    return build.load_unit("attention_mma.cu", defines)
+    return build.load_unit("attention_mma.cu", {"TS_HEAD_DIM": head_dim})
 
 
 def _attention_tcgen05(head_dim: int):
@@ -338,6 +375,11 @@ def _attention_tcgen05(head_dim: int):
 def attention_tcgen05_error(head_dim: int) -> int:
     """1 if a block of the tcgen05 attention kernel ever gave up on a wait (synchronises)."""
     return _attention_tcgen05(head_dim).ts_attention_tcgen05_error()
+
+
+def attention_mma_error(head_dim: int) -> int:
+    """1 if a block of the TMA decode kernel ever gave up on a wait (synchronises)."""
+    return _attention_mma(head_dim).ts_attention_mma_error()
 
 
 def _sampler():
@@ -446,8 +488,6 @@ def gated_activation(gate_up, activation="silu", block=0):
 #: rows of gate and up alternate in blocks of this many in a fused gate/up weight: half a 128-row
 #: tile of the tcgen05 product
 GATED_BLOCK = 64
-#: let the tcgen05 product apply the gated activation in its epilogue
-GATED_EPILOGUE = os.environ.get("TINYSERVE_GATED_EPILOGUE", "1") != "0"
 
 
 def gated_linear(x, weight, activation="silu", block=0):
@@ -458,9 +498,8 @@ def gated_linear(x, weight, activation="silu", block=0):
     ScaledRows that add_rmsnorm returned."""
     rows = x.data if isinstance(x, ScaledRows) else x
     N, K = weight.shape
-    if (GATED_EPILOGUE and block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
-            and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05"
-            and TCGEN05_FORM == "tiled" and _tcgen05_ok(rows, weight, None)
+    if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
+            and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _tcgen05_ok(rows, weight)
             and rows.shape[0] <= FUSED_MAX_TOKENS          # measured: at 64 tokens the epilogue costs 9 % of the step
             and gemm_splits(rows.shape[0], N, K) == 1):
         _cuda(rows, weight)
@@ -509,18 +548,15 @@ def qk_norm_rope_kvwrite(qkv, positions, num_heads, num_kv_heads, head_dim, rota
     return q
 
 
-NUM_SMS = 148
-
-
 def attention_splits(num_requests, max_q_len, max_kv_len, num_heads, num_kv_heads):
     """How many key ranges a launch is cut into so that a small batch still fills the SMs
     (tinykernels.py:865-889, for 148 SMs)."""
     group = num_heads // num_kv_heads
     per_tile = 32 // group if group < 32 else 1
     blocks = -(-max_q_len // per_tile) * num_kv_heads * -(-group // 32) * num_requests
-    if blocks >= 2 * NUM_SMS or max_kv_len < 256:
+    if blocks >= 2 * num_sms() or max_kv_len < 256:
         return 1
-    want = -(-2 * NUM_SMS // blocks)
+    want = -(-2 * num_sms() // blocks)
     return max(1, min(want, max_kv_len // 128, 32))
 
 
@@ -599,7 +635,7 @@ def decode_splits(num_requests, max_kv_len, num_heads, num_kv_heads):
     """Key ranges for the tensor-core decode kernel: as many as fit in one wave of blocks (two
     per SM), with at least two tiles of 64 keys per range."""
     blocks = num_kv_heads * -(-(num_heads // num_kv_heads) // 16) * num_requests
-    return max(1, min(2 * NUM_SMS // blocks, max_kv_len // 128, 32))
+    return max(1, min(2 * num_sms() // blocks, max_kv_len // 128, 32))
 
 
 def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
@@ -609,7 +645,7 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
     n = work.num_decode
     num_splits = decode_splits(n, work.max_decode_kv, H, Hkv)
     part_o = part_ml = None
-    cluster = DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    cluster = 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
     if num_splits > 1 and not cluster:
         part_o = torch.empty(n * H * num_splits * D, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n * H * num_splits * 2, dtype=torch.float32, device=q.device)
@@ -618,29 +654,57 @@ def _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work):
         _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
         _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(1), c_int(H), c_int(Hkv),
         c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale), c_int(window),
-        c_int(num_splits), _ptr(part_o), _ptr(part_ml), None, c_int(2 if cluster else 1), _ptr(work.dec_req),
+        c_int(num_splits), _ptr(part_o), _ptr(part_ml), c_int(2 if cluster else 1), _ptr(work.dec_req),
         _ptr(work.dec_tok), c_int(n), c_int(0), c_int(_tma_pages(k_cache, v_cache)), _stream()),
         2 if num_splits > 1 and not cluster else 1)
 
 
-def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None):
+def attention_backend(dtype, head_dim, page_size=16) -> str:
+    """Which kernels attend for this element type and head size: "tcgen05" (prefill on the
+    tcgen05 kernel, decode on the mma.sync decode kernel), "mma" (both on the mma.sync kernels) or
+    "simt" (the 32-bit kernel: float32, and bfloat16 heads wider than MMA_MAX_HEAD_DIM)."""
+    if dtype != torch.bfloat16 or head_dim > MMA_MAX_HEAD_DIM or head_dim not in SUPPORTED_HEAD_DIMS:
+        return "simt"
+    if head_dim in TCGEN05_HEAD_DIMS and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0:
+        return "tcgen05"
+    return "mma"
+
+
+def prefill_tile_queries(dtype, num_heads, num_kv_heads, head_dim, page_size=16) -> int:
+    """Queries per block of the prefill kernel that ``attention_backend`` names (0: the kernel
+    takes no work list)."""
+    group = num_heads // num_kv_heads
+    backend = attention_backend(dtype, head_dim, page_size)
+    if backend == "tcgen05":
+        return 2 * (128 // group if group < 128 else 1)      # two query tiles of 128 rows a block
+    if backend == "mma":
+        return MMA_PREFILL_ROWS // group if group < MMA_PREFILL_ROWS else 1
+    return 0
+
+
+def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=None, backend=None):
     """Attention of this step's queries over their requests' cached keys and values.
     q [T, H, D]; caches [pages, Hkv, page_size, D]; ``view`` a GroupView; ``ctx`` gives cu_q,
     kv_lens and the batch's maxima.  bfloat16 runs on the tensor cores (a decode kernel when
-    every request brings one token, else the prefill kernel); float32 on the 32-bit kernel."""
+    every request brings one token, else a prefill kernel); float32 on the 32-bit kernel.
+    ``backend`` overrides ``attention_backend`` (tests run the slower kernels at every size)."""
     _cuda(q, k_cache, v_cache)
     T, H, D = q.shape
     Hkv = k_cache.shape[1]
-    mma = q.dtype == torch.bfloat16 and BF16_ATTENTION in ("mma", "tcgen05") and D <= MMA_MAX_HEAD_DIM \
-        and D in SUPPORTED_HEAD_DIMS
-    decode = mma and ctx.max_q_len == 1
     page = view.page_size
-    if (mma and not decode and BF16_ATTENTION == "tcgen05" and D in TCGEN05_HEAD_DIMS
-            and 8 <= page <= 128 and page & (page - 1) == 0 and k_cache.is_contiguous() and v_cache.is_contiguous()):
+    chosen = attention_backend(q.dtype, D, page)
+    if backend is not None and backend != chosen:
+        if q.dtype != torch.bfloat16 or (backend == "tcgen05") or (backend == "mma" and chosen == "simt"):
+            raise ValueError(f"attention backend {backend!r} does not take {q.dtype}, head size {D}, pages of {page}")
+        chosen = backend
+    if chosen == "tcgen05" and not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        chosen = "mma"
+    mma = chosen in ("tcgen05", "mma")
+    decode = mma and ctx.max_q_len == 1
+    if chosen == "tcgen05" and not decode:
         out = torch.empty_like(q)
         lib = _attention_tcgen05(D)
-        group = H // Hkv
-        tile_queries = 2 * (128 // group if group < 128 else 1)      # two query tiles of 128 rows a block
+        tile_queries = prefill_tile_queries(q.dtype, H, Hkv, D, page)
         work = attention_work(ctx, tile_queries, q.device)
         if work.num_decode:
             _decode_listed(q, out, k_cache, v_cache, view, ctx, scale, window, work)
@@ -663,16 +727,13 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
         num_splits = 1
     out = torch.empty_like(q)
     part_o = part_ml = None
-    cluster = mma and decode and DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    cluster = mma and decode and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
     if num_splits > 1 and not cluster:
         part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(T * H * num_splits * 2, dtype=torch.float32, device=q.device)
     launches = 2 if num_splits > 1 and not cluster else 1
     if mma:
         lib = _attention_mma(D)
-        counters = None
-        if num_splits > 1 and DECODE_MERGE == "kernel" and ctx.num_requests * Hkv * -(-(H // Hkv) // 16) <= 16384:
-            counters, launches = _tile_counters(q.device), 1
         tile_req = tile_q0 = None
         num_tiles = tile_queries = 0
         if not decode:
@@ -688,7 +749,7 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
             _ptr(q), _ptr(out), _ptr(k_cache), _ptr(v_cache), _ptr(view.block_table), _ptr(ctx.cu_q),
             _ptr(ctx.kv_lens), c_int(T), c_int(ctx.num_requests), c_int(ctx.max_q_len), c_int(H),
             c_int(Hkv), c_int(view.page_size), c_int(view.block_table.stride(0)), c_float(scale),
-            c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml), _ptr(counters),
+            c_int(window), c_int(num_splits), _ptr(part_o), _ptr(part_ml),
             c_int((2 if cluster else 1) if decode else 0), _ptr(tile_req), _ptr(tile_q0), c_int(num_tiles), c_int(tile_queries),
             c_int(_tma_pages(k_cache, v_cache)), _stream()), launches)
         return out
@@ -702,27 +763,23 @@ def paged_attention(q, k_cache, v_cache, view, ctx, scale, window=0, num_splits=
     return out
 
 
-#: decode steps: let the attention kernel take the fused q/k/v projection itself (per-head norm,
-#: rotary and the cache write happen inside it; one kernel fewer per layer)
-FUSED_DECODE_QKV = os.environ.get("TINYSERVE_FUSED_DECODE_QKV", "1") != "0"
-
-
 def attention_from_qkv(qkv, positions, num_heads, num_kv_heads, head_dim, rotary, q_weight, k_weight, eps,
-                       k_cache, v_cache, view, ctx, scale, window=0, write_cache=True):
+                       k_cache, v_cache, view, ctx, scale, window=0, write_cache=True, fused=True):
     """Per-head norm of q and k, rotary encoding, cache write of k and v, attention over the cache:
     qkv [T, (H + 2 Hkv) * D] (a tensor, or the SplitPartials of the projection) -> [T, H, D].
     Two kernels (qk_norm_rope_kvwrite, paged_attention), or, when every request brings one token
     (bfloat16, full-width rotary with the (j, j + D/2) pairing), the decode kernel alone: it makes
-    its query rows and the newest key and value itself."""
+    its query rows and the newest key and value itself (one kernel fewer per layer; ``fused``
+    False keeps the two kernels, for comparison)."""
     dtype = qkv.dtype
     H, Hkv, D = num_heads, num_kv_heads, head_dim
     plain = isinstance(qkv, torch.Tensor)
     # (up to FUSED_MAX_TOKENS requests: measured, at 64 the separate kernel is 4 % of the step faster)
-    fused = (FUSED_DECODE_QKV and write_cache and dtype == torch.bfloat16 and ctx.max_q_len == 1
+    fused = (fused and write_cache and dtype == torch.bfloat16 and ctx.max_q_len == 1
              and qkv.shape[0] <= FUSED_MAX_TOKENS
-             and BF16_ATTENTION in ("mma", "tcgen05") and D in SUPPORTED_HEAD_DIMS and D <= MMA_MAX_HEAD_DIM
+             and D in SUPPORTED_HEAD_DIMS and D <= MMA_MAX_HEAD_DIM
              and rotary is not None and rotary.rotary_dim == D and not rotary.interleaved
-             and DECODE_MERGE != "kernel" and (q_weight is None) == (k_weight is None)
+             and (q_weight is None) == (k_weight is None)
              and k_cache is not None and k_cache.dtype == torch.bfloat16
              and (isinstance(qkv, SplitPartials) or (plain and qkv.is_contiguous()))
              and (q_weight is None or q_weight.dtype == k_weight.dtype))
@@ -738,7 +795,7 @@ def attention_from_qkv(qkv, positions, num_heads, num_kv_heads, head_dim, rotary
     _cuda(qkv if plain else None, positions, k_cache, v_cache, view.slot_mapping, view.block_table, rotary.cos, rotary.sin)
     out = torch.empty(T, H, D, dtype=dtype, device=qkv.device)
     num_splits = decode_splits(ctx.num_requests, ctx.max_kv_len, H, Hkv)
-    cluster = DECODE_MERGE == "cluster" and 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
+    cluster = 1 < num_splits <= CLUSTER_MERGE_MAX_SPLITS
     part_o = part_ml = None
     if num_splits > 1 and not cluster:
         part_o = torch.empty(T * H * num_splits * D, dtype=torch.float32, device=qkv.device)
@@ -757,12 +814,12 @@ def attention_from_qkv(qkv, positions, num_heads, num_kv_heads, head_dim, rotary
 
 def linear(x, weight, bias=None, out_float32=False, allow_partials=False, allow_pending=False):
     """x [M, K] @ weight[N, K]^T (+ bias).  float32 operands: this package's 32-bit FMA kernel
-    (no tensor cores, no reduced precision).  bfloat16 operands: cuBLAS through torch.mm, or
-    the FMA kernel when BF16_GEMM == "simt"; with BF16_GEMM == "tcgen05" products of up to
-    TCGEN05_MAX_TOKENS rows run on this package's TMA + tcgen05 kernel.  With ``allow_partials``
-    the result may be a SplitPartials (the caller hands it to add_rmsnorm, qk_norm_rope_kvwrite,
-    or calls materialize); with ``allow_pending`` a PendingProduct (for add_rmsnorm, or
-    materialize).  x may be the ScaledRows that add_rmsnorm returned."""
+    (no tensor cores, no reduced precision).  bfloat16 operands: this package's TMA + tcgen05
+    kernel for up to TCGEN05_MAX_TOKENS rows (K and the leading dimensions multiples of 8), cuBLAS
+    through torch above that, as in tinyserve (serve.py:828-829).  With ``allow_partials`` the
+    result may be a SplitPartials (the caller hands it to add_rmsnorm, qk_norm_rope_kvwrite, or
+    calls materialize); with ``allow_pending`` a PendingProduct (for add_rmsnorm, or materialize).
+    x may be the ScaledRows that add_rmsnorm returned."""
     scale = None
     if isinstance(x, ScaledRows):
         scale, x = x, x.data
@@ -771,30 +828,43 @@ def linear(x, weight, bias=None, out_float32=False, allow_partials=False, allow_
     N = weight.shape[0]
     if weight.shape[1] != K or x.dtype != weight.dtype:
         raise ValueError(f"linear: x {tuple(x.shape)} {x.dtype} does not fit weight {tuple(weight.shape)} {weight.dtype}")
+    if bias is not None and tuple(bias.shape) != (N,):
+        raise ValueError(f"linear: bias {tuple(bias.shape)} does not fit {N} outputs")
     x = materialize(x)
-    tiled = TCGEN05_FORM == "tiled"
-    if x.dtype == torch.bfloat16 and BF16_GEMM == "tcgen05" and _tcgen05_ok(x, weight, bias) \
-            and (scale is None or M <= FUSED_MAX_TOKENS):
-        if allow_pending and FUSED_RESIDUAL and scale is None and tiled and not out_float32 and M <= FUSED_MAX_TOKENS:
+    if x.dtype == torch.bfloat16 and _tcgen05_ok(x, weight) and (scale is None or M <= FUSED_MAX_TOKENS):
+        if bias is not None:
+            if scale is not None:
+                x, scale = scale.materialize(), None
+            return _linear_tcgen05(x, weight, out_float32, bias=bias)
+        if allow_pending and scale is None and not out_float32 and M <= FUSED_MAX_TOKENS:
             return PendingProduct(x, weight)
-        if (allow_partials or allow_pending) and SPLIT_PARTIALS and not out_float32 and tiled \
+        if (allow_partials or allow_pending) and not out_float32 \
                 and gemm_splits(x.shape[0], weight.shape[0], x.shape[1], partials=True) > 1:
             return _linear_tcgen05(x, weight, False, partials_only=True, scale=scale)
         return _linear_tcgen05(x, weight, out_float32, scale=scale)
     if scale is not None:
         x = scale.materialize()
-    if x.dtype == torch.bfloat16 and BF16_GEMM in ("cublas", "tcgen05"):
-        if out_float32:
-            out = torch.mm(x, weight.t(), out_dtype=torch.float32)
-        else:
-            out = torch.mm(x, weight.t())
+    if x.dtype == torch.bfloat16:
+        # a plain library product (and its bias epilogue), as in tinyserve
         if bias is not None:
-            out += bias
-        return out
+            out = torch.addmm(bias.to(torch.bfloat16), x, weight.t())
+            return out.float() if out_float32 else out
+        if out_float32:
+            return torch.mm(x, weight.t(), out_dtype=torch.float32)
+        return torch.mm(x, weight.t())
+    return _linear_simt(x, weight, bias, out_float32)
+
+
+def _linear_simt(x, weight, bias=None, out_float32=False):
+    """The 32-bit FMA product (float32 operands; it takes bfloat16 operands too)."""
+    M, K = x.shape
+    N = weight.shape[0]
     out_dtype = torch.float32 if out_float32 else x.dtype
     out = torch.empty(M, N, dtype=out_dtype, device=x.device)
     if x.stride(1) != 1 or weight.stride(1) != 1:
         raise ValueError("linear: operands must be contiguous along K")
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
     lib = _gemm()
     _check(lib, lib.ts_gemm_simt(c_int(_dt(x)), c_int(_DTYPE[out_dtype]), _ptr(x), _ptr(weight),
                                  _ptr(bias), _ptr(out), c_int(M), c_int(N), c_int(K),
