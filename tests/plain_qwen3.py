@@ -127,7 +127,9 @@ def layer_window(cfg, i):
     return cfg["sliding_window"] if i >= mwl else 0
 
 
-def load_folder(model_dir, dtype=torch.float64):
+def load_folder(model_dir, dtype=torch.float64, device="cpu"):
+    """config.json and every tensor of the folder's safetensors files, as ``dtype`` on ``device``
+    (each tensor moves before it is converted, so that a large model is widened on the device)."""
     with open(os.path.join(model_dir, "config.json")) as fh:
         cfg = normalise_config(json.load(fh))
     weights = {}
@@ -135,7 +137,7 @@ def load_folder(model_dir, dtype=torch.float64):
         if name.endswith(".safetensors"):
             with safe_open(os.path.join(model_dir, name), "pt", device="cpu") as fh:
                 for key in fh.keys():
-                    weights[key] = fh.get_tensor(key).to(dtype)
+                    weights[key] = fh.get_tensor(key).to(device).to(dtype)
     return cfg, weights
 
 

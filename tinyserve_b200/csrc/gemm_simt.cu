@@ -1,9 +1,13 @@
 // C[M, N] = A[M, K] * W[N, K]^T (+ bias[N]) with 32-bit FMA on the CUDA cores.
 //
 // This is the matrix product of the true 32-bit path: no tensor cores, no reduced
-// precision mode.  Every output element is one chain of fmaf over k = 0..K-1 in order,
-// whatever the tile shape or M is, so a row's result does not depend on what else is in
-// the batch.  Inputs may also be bfloat16 (products and sums still 32-bit).
+// precision mode.  Every output element is summed in the same order whatever the tile shape
+// or M is, so a row's result does not depend on what else is in the batch: k runs in order,
+// in chains of fmaf over SUM_BLOCK = 64 consecutive k, and the chains' results are added in
+// order.  (One chain over all of K loses about sqrt(K) roundings of the running sum; two levels
+// lose sqrt(64) + sqrt(K / 64): at K = 4,096 an eighth of the error, which 36 layers of four
+// products each need to stay within 1e-4 of a float64 reference.)  Inputs may also be bfloat16
+// (products and sums still 32-bit).
 // tinyserve uses cuBLAS through nn.Linear for all of these (serve.py:828-829, 912-913, 1263).
 #include "common.cuh"
 
@@ -12,6 +16,7 @@ TS_DEFINE_LAST_ERROR()
 namespace {
 
 constexpr int BK = 16;
+constexpr int SUM_BLOCK = 64;        // k of one fmaf chain
 constexpr int THREADS = 256;
 
 template <typename T> struct Load4;
@@ -69,11 +74,11 @@ gemm_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, const TI* __r
   pdl_wait();
   const int tx = threadIdx.x % (BN / TN), ty = threadIdx.x / (BN / TN);
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  float acc[TM][TN];
+  float acc[TM][TN], part[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; ++i)
 #pragma unroll
-    for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; ++j) acc[i][j] = part[i][j] = 0.f;
 
   for (int k0 = 0; k0 < K; k0 += BK) {
     load_tile<TI, BM, VEC>(A, m0, M, k0, K, lda, As);
@@ -89,7 +94,16 @@ gemm_nt_kernel(const TI* __restrict__ A, const TI* __restrict__ W, const TI* __r
 #pragma unroll
       for (int i = 0; i < TM; ++i)
 #pragma unroll
-        for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
+    }
+    if ((k0 + BK) % SUM_BLOCK == 0 || k0 + BK >= K) {
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+          acc[i][j] += part[i][j];
+          part[i][j] = 0.f;
+        }
     }
     __syncthreads();
   }
