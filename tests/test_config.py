@@ -7,7 +7,7 @@ from helpers import TINY, tiny_config, tiny_config_dict
 from tinyserve_b200.config import (ConfigError, EngineConfig, ModelConfig, Qwen3Config,
                                    config_from_dict, load_model_config, register_architecture)
 from tinyserve_b200.config.registry import ARCHITECTURES
-from tinyserve_b200.engine.build import build_model
+from tinyserve_b200.parts import build_model
 
 
 @pytest.mark.parametrize("name", sorted(TINY))

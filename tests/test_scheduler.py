@@ -135,3 +135,70 @@ def test_random_load_keeps_every_rule(seed):
     assert not sched.has_work() and not pending
     assert all(r.finished for r in everyone)
     assert all(p.num_free == p.num_usable for p in mgr.pools)
+
+
+# ----------------------------------------------------------------------------- against tinyserve
+def _reference_module():
+    """tinyserve's own serve.py, unmodified, from baseline/_ref (not tracked); None if absent."""
+    import importlib
+    import os
+    import sys
+    ref = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isfile(os.path.join(ref, "serve.py")):
+        return None
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        return importlib.import_module("serve")
+    except Exception:           # an import of its dependencies that fails here
+        return None
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3])
+def test_same_decisions_as_tinyserves_scheduler(seed):
+    """The same arrivals given to tinyserve's Scheduler + KVCacheManager (serve.py:188-625, on the
+    host, prefix cache off) and to this engine's: every step the same requests run with the same
+    token counts from the same offsets, and the same requests are preempted."""
+    serve = _reference_module()
+    if serve is None:
+        pytest.skip("tinyserve's serve.py is not under baseline/_ref (or does not import here)")
+    from types import SimpleNamespace
+    rng = random.Random(seed)
+    pages, page, seqs, budget = rng.choice([(14, 8, 4, 32), (40, 16, 6, 64), (9, 4, 3, 16)])
+    ours, _ = make(pages=pages, page=page, seqs=seqs, budget=budget)
+    kv = serve.KVCacheManager(pages + 1, page, False)
+    theirs = serve.Scheduler(SimpleNamespace(max_num_seqs=seqs, max_num_batched_tokens=budget, block_size=page), kv)
+    longest = pages * page - 1                      # every request fits the pool when it is alone
+    arrivals = []
+    for i in range(30):
+        n = rng.randint(1, min(longest - 12, 5 * budget))
+        arrivals.append((rng.randint(0, 40), f"r{i}", n, rng.randint(1, 12)))
+    arrivals.sort()
+    mine, his = {}, {}
+    step = 0
+    preempted_mine, preempted_his = [], []
+    while arrivals or ours.has_work() or theirs.has_work():
+        while arrivals and arrivals[0][0] <= step:
+            _, rid, n, max_tokens = arrivals.pop(0)
+            mine[rid] = Request(rid, list(range(n)), SamplingParams(max_tokens=max_tokens))
+            his[rid] = serve.Request(rid, list(range(n)), serve.SamplingParams(max_tokens=max_tokens))
+            ours.add(mine[rid])
+            theirs.add(his[rid])
+        a, b = ours.schedule(), theirs.schedule()
+        assert [(s.req.request_id, s.num_computed, s.num_new) for s in a] == \
+               [(s.req.request_id, s.num_computed, s.num_new) for s in b], f"step {step}"
+        assert [r.request_id for r in ours.running] == [r.request_id for r in theirs.running]
+        assert [r.request_id for r in ours.waiting] == [r.request_id for r in theirs.waiting]
+        preempted_mine.append(sorted(r for r, q in mine.items() if q.was_preempted))
+        preempted_his.append(sorted(r for r, q in his.items() if q.was_preempted))
+        run_step(ours, a)
+        for s in b:                                 # what serve.Engine.step does with a batch
+            if s.completes_prompt:
+                s.req.token_ids.append(7)
+                if len(s.req.output_ids) >= s.req.params.max_tokens:
+                    theirs.finish(s.req, "length")
+        assert not ours.dropped
+        step += 1
+        assert step < 5000
+    assert preempted_mine == preempted_his
+    assert any(preempted_mine[-1]) or pages > 30, "the small pools force preemption"

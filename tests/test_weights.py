@@ -7,7 +7,7 @@ import torch
 from safetensors.torch import load_file, save_file
 
 from helpers import make_model_dir, tiny_config
-from tinyserve_b200.engine.build import build_model
+from tinyserve_b200.parts import build_model
 from tinyserve_b200.weights import WeightError, expected_tensors, load_weights, write_random_model
 
 

@@ -1,9 +1,10 @@
-"""Device memory of the cache: one tensor per group, and the state-slot tensors.
+"""Device memory of the cache: per group one tensor for each thing its mixers keep per token,
+and the state-slot tensors.
 
-Layout of a group: [entry, 2 (keys, values), page, kv_head, slot, head_dim], so the
-share of one KV head in one page is one contiguous run of page_size * head_dim
-elements.  tinyserve keeps [2, page, slot, kv_head, head_dim] per layer
-(serve.py:1791-1796)."""
+Layout of a cache tensor: [entry, page, head, slot, width], so the share of one head in one page
+is one contiguous run of page_size * width elements (attention: "k" and "v" of kv_heads heads of
+head_dim; a mixer may keep other tensors, see ``parts.CacheSpec``).  tinyserve keeps
+[2, page, slot, kv_head, head_dim] per layer (serve.py:1791-1796)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -14,29 +15,41 @@ import torch
 @dataclass
 class CacheEntry:
     group: int
-    k: torch.Tensor      # [page, kv_head, slot, head_dim]
-    v: torch.Tensor
+    tensors: dict        # name -> [page, head, slot, width]
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.tensors["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors["v"]
 
 
 class DeviceCache:
     def __init__(self, model, num_pages, page_size: int, num_slots: int, dtype, device):
         counts = [num_pages] * len(model.cache_groups) if isinstance(num_pages, int) else list(num_pages)
         self.page_size = page_size
-        self.pools = []
+        self.pools = []          # per group: {tensor name: [entry, page, head, slot, width]}
         for spec, entries, pages in zip(model.cache_groups, model.group_sizes, counts):
-            self.pools.append(torch.zeros(entries, 2, pages, spec.num_kv_heads, page_size,
-                                          spec.head_dim, dtype=dtype, device=device))
-        self.entries = [CacheEntry(info.group, self.pools[info.group][info.index_in_group, 0],
-                                   self.pools[info.group][info.index_in_group, 1])
+            self.pools.append({t.name: torch.zeros(entries, pages, t.heads, page_size, t.width,
+                                                   dtype=dtype, device=device) for t in spec.tensors})
+        self.entries = [CacheEntry(info.group, {name: pool[info.index_in_group]
+                                                for name, pool in self.pools[info.group].items()})
                         for info in model.cache_entries]
         self.states = [torch.zeros((num_slots,) + tuple(s.shape), dtype=getattr(torch, s.dtype),
                                    device=device) for s in model.state_entries]
 
     @staticmethod
     def bytes_per_page(model, page_size: int, element_size: int) -> list:
-        return [2 * n * spec.num_kv_heads * page_size * spec.head_dim * element_size
+        return [n * spec.elements_per_token() * page_size * element_size
                 for spec, n in zip(model.cache_groups, model.group_sizes)]
 
-    def zero_state(self, slot: int) -> None:
+    def zero_state(self, slots) -> None:
+        """Zero the state of the given slots (a request that starts there finds no trace of the
+        one before)."""
+        if not self.states or not len(slots):
+            return
+        index = torch.as_tensor(slots, dtype=torch.long, device=self.states[0].device)
         for s in self.states:
-            s[slot].zero_()
+            s.index_fill_(0, index, 0)

@@ -34,14 +34,28 @@ class PartSpec:
         return self.params.get(key, default)
 
 
+#: names of a block's parts inside checkpoint tensor names; "mixer" and "ffn" default to the
+#: part's own ``tree_name``
+LAYER_NAMES = {"input_norm": "input_layernorm", "post_mixer_norm": "post_attention_layernorm"}
+#: names of the model's own tensors and of its layers ("{i}" is the layer's index)
+MODEL_NAMES = {"embed": "{prefix}embed_tokens", "layers": "{prefix}layers.{i}", "final_norm": "{prefix}norm",
+               "lm_head": "lm_head", "embed_position": "{prefix}embed_positions"}
+
+
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: its mixer, its feed-forward, the norm kind and the arrangement."""
+    """One block: its mixer, its feed-forward, the norm kind and the arrangement.  ``names``
+    overrides entries of LAYER_NAMES (and "mixer" / "ffn"): how the block's parts are called in
+    the checkpoint's tensor names."""
 
     mixer: PartSpec
     ffn: PartSpec
     norm: PartSpec
     arrangement: str = "pre_norm"
+    names: dict = field(default_factory=dict)
+
+    def name_of(self, key: str, default: str = "") -> str:
+        return self.names.get(key, LAYER_NAMES.get(key, default))
 
 
 @dataclass(frozen=True)
@@ -70,6 +84,15 @@ class ModelSpec:
     tie_word_embeddings: bool
     # prefix of every tensor name of the decoder stack in a checkpoint
     weight_prefix: str = "model."
+    # overrides of MODEL_NAMES: the checkpoint's names of the embedding table, the layers
+    # ("{i}" = index), the final norm and the output projection
+    names: dict = field(default_factory=dict)
+    # a position encoding that adds to the embeddings before the first block (learned or
+    # absolute positions); None: positions enter inside the mixers only
+    embedding_position: PartSpec = None
+
+    def name_of(self, key: str, **fmt) -> str:
+        return self.names.get(key, MODEL_NAMES[key]).format(prefix=self.weight_prefix, **fmt)
 
 
 @dataclass(frozen=True)

@@ -23,8 +23,8 @@ from ..config.engine_config import EngineConfig
 from ..config.registry import load_model_config
 from ..kernels import ops
 from ..weights import fill_random_on_device, load_weights
+from ..parts.model import build_model
 from .batch import GroupView, StepContext, StepEntry
-from .build import build_model
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -40,8 +40,11 @@ class Prepared:
 
 
 class _Runtime:
+    """What parts may ask of the engine when they build their constants (``Part.prepare``)."""
+
     def __init__(self, device, max_positions, dtype):
         self.device, self.max_positions, self.dtype = device, max_positions, dtype
+        self.shared: dict = {}       # tables that several parts of this engine share
 
 
 class ModelRunner:
@@ -270,6 +273,10 @@ class ModelRunner:
             if self._copied[prep.buf] is None:
                 self._copied[prep.buf] = torch.cuda.Event()
             self._copied[prep.buf].record()
+        if self.device_cache.states:
+            # a request that starts in this step finds its state slot zeroed, whoever held it before
+            host = prep.ctx.host
+            self.device_cache.zero_state([s for s, f in zip(host["state_slots"], host["fresh"]) if f])
         if prep.graph is not None:
             graph, out, size, launches = prep.graph
             graph.replay()
@@ -307,7 +314,7 @@ class ModelRunner:
         return sorted(set(sizes))
 
     def _graph_for(self, entries):
-        if not self.graphs:
+        if not self.graphs or not self.model.capturable:
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None
@@ -319,7 +326,11 @@ class ModelRunner:
     @torch.inference_mode()
     def capture_decode_graphs(self, sizes=None):
         """Capture one graph per decode batch size: every request brings one token and
-        wants its logits.  Smaller batches run the next larger graph with empty requests."""
+        wants its logits.  Smaller batches run the next larger graph with empty requests.
+        A model with a part that is not ``capturable`` (it reads host-side lists of the step,
+        which a replay would not refresh) is not captured: every step then runs eagerly."""
+        if not self.model.capturable:
+            return 0
         sizes = sorted(sizes or self.decode_buckets(), reverse=True)
         pool = None
         dummy = "__capture__"

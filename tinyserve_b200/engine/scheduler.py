@@ -59,6 +59,15 @@ class ScheduledRequest:
 
 
 class Scheduler:
+    """Decides, step by step, which requests run and with how many tokens.
+
+    ``running`` holds the requests that own pages and a state slot, oldest first; ``waiting``
+    those that do not, in arrival order, preempted ones in front.  A step's grants are built in
+    running order: first the running requests take what they owe from the token budget (pushing
+    out the newest ones when the cache manager has no pages for them), then, if nobody was
+    pushed out, the head of the waiting queue is let in for as long as budget, ``max_num_seqs``,
+    state slots and pages last."""
+
     def __init__(self, manager, max_num_seqs: int, max_num_batched_tokens: int):
         self.manager = manager
         self.max_num_seqs = max_num_seqs
@@ -73,70 +82,81 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
-    def _preempt(self, victim: Request) -> None:
-        victim.was_preempted = True
-        self.manager.free(victim.request_id)
-        victim.num_computed_tokens = 0
-        self.waiting.appendleft(victim)
-
+    # ------------------------------------------------------------------ one step
     def schedule(self) -> list:
-        mgr = self.manager
-        budget = self.max_num_batched_tokens
-        plan: dict = {}
-        preempted = False
-        i = 0
-        while i < len(self.running) and budget > 0:
-            req = self.running[i]
-            n = min(req.num_tokens - req.num_computed_tokens, budget)
-            stop = False
-            while not mgr.allocate(req.request_id, n):
-                victim = self.running.pop()
-                if victim is req and not self.running:
-                    # nobody else holds pages: this request can never fit
-                    mgr.free(req.request_id)
-                    req.finished, req.finish_reason = True, "cache_full"
-                    self.dropped.append(req)
-                    stop = True
-                    break
-                self._preempt(victim)
-                budget += plan.pop(victim.request_id, 0)
-                preempted = True
-                if victim is req:
-                    stop = True
-                    break
-            if stop:
-                break
-            plan[req.request_id] = n
-            budget -= n
-            i += 1
+        grants: list = []                      # (request, tokens), in running order
+        left = self.max_num_batched_tokens
+        pushed_out = False
+        at = 0
+        while at < len(self.running) and left > 0:
+            req = self.running[at]
+            owed = min(req.num_tokens - req.num_computed_tokens, left)
+            kept, evicted = self._room_for(req, owed)
+            pushed_out = pushed_out or evicted
+            if not kept:
+                break                          # the request itself had to go: nobody after it runs
+            grants.append((req, owed))
+            left -= owed
+            at += 1
+        if not pushed_out:
+            left = self._admit(grants, left)
+        batch = []
+        for req, n in grants:
+            batch.append(ScheduledRequest(req, req.num_computed_tokens, n))
+            req.num_computed_tokens += n       # counted before the device has run them
+        return batch
 
-        while (not preempted and self.waiting and budget > 0
-               and len(self.running) < self.max_num_seqs and mgr.can_begin()):
-            req = self.waiting[0]
-            mgr.begin(req.request_id)
-            n = min(req.num_tokens, budget)
-            if not mgr.allocate(req.request_id, n):
+    def _room_for(self, req: Request, tokens: int) -> tuple:
+        """Pages for ``tokens`` more tokens of a running request.  While the pools cannot give
+        them, the newest running request loses its pages and goes back to the head of the queue
+        (it is never older than ``req``).  Returns (req still runs, somebody was pushed out)."""
+        mgr, evicted = self.manager, False
+        while not mgr.allocate(req.request_id, tokens):
+            newest = self.running.pop()
+            if newest is req:
+                if self.running:
+                    self._back_to_queue(req)
+                    return False, True
+                # no other request holds a page and it still does not fit: it never will
                 mgr.free(req.request_id)
-                if not self.running:
-                    # the pool is empty and the portion still does not fit
-                    self.waiting.popleft()
-                    req.finished, req.finish_reason = True, "cache_full"
-                    self.dropped.append(req)
-                    continue
-                break
+                self._drop(req)
+                return False, evicted
+            self._back_to_queue(newest)
+            evicted = True
+        return True, evicted
+
+    def _admit(self, grants: list, left: int) -> int:
+        """Let waiting requests in, strictly in order: the head of the queue or nobody."""
+        mgr = self.manager
+        while self.waiting and left > 0 and len(self.running) < self.max_num_seqs and mgr.can_begin():
+            req = self.waiting[0]
+            first = min(req.num_tokens, left)
+            mgr.begin(req.request_id)
+            if not mgr.allocate(req.request_id, first):
+                mgr.free(req.request_id)
+                if self.running:
+                    break                      # it waits for pages that running requests hold
+                # the whole pool is free and the portion still does not fit
+                self.waiting.popleft()
+                self._drop(req)
+                continue
             self.waiting.popleft()
             req.num_computed_tokens = 0
             self.running.append(req)
-            plan[req.request_id] = n
-            budget -= n
+            grants.append((req, first))
+            left -= first
+        return left
 
-        batch = []
-        for req in self.running:
-            n = plan.get(req.request_id)
-            if n:
-                batch.append(ScheduledRequest(req, req.num_computed_tokens, n))
-                req.num_computed_tokens += n
-        return batch
+    def _back_to_queue(self, req: Request) -> None:
+        """Preemption by recomputation: pages and slot go back, the request starts over."""
+        req.was_preempted = True
+        self.manager.free(req.request_id)
+        req.num_computed_tokens = 0
+        self.waiting.appendleft(req)
+
+    def _drop(self, req: Request) -> None:
+        req.finished, req.finish_reason = True, "cache_full"
+        self.dropped.append(req)
 
     def finish(self, req: Request, reason: str) -> None:
         """End a request and give back what it holds (serve.py:619-625)."""

@@ -18,27 +18,31 @@ def load_tokenizer(model_dir: str):
 
 
 class Detokenizer:
-    """Turns a growing list of generated ids into text piece by piece.  A piece that ends
-    in U+FFFD is held back unless the request is over: the bytes of one character may be
-    spread over several tokens (serve.py:2309-2341)."""
+    """Turns a growing list of generated ids into text piece by piece.
+
+    Every call decodes the request's whole output again and hands out what is new beyond the
+    text already given (a tokenizer may join or space a token differently once its neighbour is
+    known, so only the whole sequence decodes reliably; the cost is linear in the output so far).
+    Text that ends in U+FFFD is held back unless the request is over: the bytes of one character
+    may be spread over several tokens.  tinyserve decodes a sliding window instead
+    (serve.py:2309-2341); the pieces are the same."""
 
     def __init__(self, tok):
         self.tok = tok
         self.text = ""
         self.released = 0      # characters already handed out when stop strings hold text back
-        self._context_start = 0
-        self._emitted_upto = 0
 
     def update(self, ids, final: bool) -> str:
         if self.tok is None:
             return ""
-        before = self.tok.decode(ids[self._context_start:self._emitted_upto], skip_special_tokens=True)
-        now = self.tok.decode(ids[self._context_start:], skip_special_tokens=True)
-        if len(now) <= len(before) or (now.endswith("�") and not final):
+        whole = self.tok.decode(list(ids), skip_special_tokens=True)
+        if not final and whole.endswith("\ufffd"):
             return ""
-        piece = now[len(before):]
-        self.text += piece
-        self._context_start, self._emitted_upto = self._emitted_upto, len(ids)
+        if not whole.startswith(self.text):
+            # the tokenizer rewrote earlier text (rare): keep what was given, add only what is longer
+            whole = self.text + whole[len(self.text):]
+        piece = whole[len(self.text):]
+        self.text = whole
         return piece
 
 

@@ -1,4 +1,4 @@
-from .base import (CacheSpec, FeedForward, Mixer, Norm, ParamSpec, Part, PositionEncoding, Source,
+from .base import (CacheSpec, CacheTensor, FeedForward, Mixer, Norm, ParamSpec, Part, PositionEncoding, Source,
                    StateSpec, build_feed_forward, build_mixer, build_norm,
                    build_position_encoding, register_feed_forward, register_mixer, register_norm,
                    register_position_encoding)
@@ -7,4 +7,4 @@ from .rotary import Rotary
 from .attention import Attention
 from .mlp import GatedMLP
 from .block import ARRANGEMENTS, PreNormBlock, build_block
-from .model import BoundCall, DecoderModel, Embedding, LMHead
+from .model import BoundCall, DecoderModel, Embedding, LMHead, build_model

@@ -5,7 +5,8 @@ optional per-head norm of q and k before the position encoding (serve.py:873-876
 keys and values written to the cache pages of this step's tokens (serve.py:897-904),
 attention of every query over its request's cached keys with j <= position and,
 with ``window`` > 0, j > position - window (serve.py:668-680), output projection
-(serve.py:883).  All sizes are parameters."""
+(serve.py:883).  All sizes are parameters, and so are the checkpoint's names of the four
+projections and the two norms (``names``)."""
 from __future__ import annotations
 
 from ..kernels import ops
@@ -13,12 +14,17 @@ from .base import (CacheSpec, Mixer, ParamSpec, Source, build_norm, build_positi
                    register_mixer)
 
 
+DEFAULT_NAMES = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj", "q_norm": "q_norm", "k_norm": "k_norm"}
+
+
 class Attention(Mixer):
     tree_name = "self_attn"
+    capturable = True
 
     def __init__(self, hidden_size, num_heads, num_kv_heads, head_dim, bias=False, qk_norm=None,
-                 position=None, window=0, scale=None):
+                 position=None, window=0, scale=None, names=None):
         super().__init__()
+        self.names = dict(DEFAULT_NAMES, **(names or {}))
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
@@ -33,21 +39,23 @@ class Attention(Mixer):
     def children(self):
         out = {}
         if self.q_norm is not None:
-            out["q_norm"], out["k_norm"] = self.q_norm, self.k_norm
+            out[self.names["q_norm"]], out[self.names["k_norm"]] = self.q_norm, self.k_norm
         if self.position is not None:
             out["position"] = self.position
         return out
 
     def param_specs(self):
         q, kv = self.q_size, self.kv_size
-        rows = (("q_proj", 0, q), ("k_proj", q, q + kv), ("v_proj", q + kv, q + 2 * kv))
+        nm = self.names
+        rows = ((nm["q"], 0, q), (nm["k"], q, q + kv), (nm["v"], q + kv, q + 2 * kv))
         specs = {
             "qkv_proj.weight": ParamSpec((q + 2 * kv, self.hidden_size), sources=tuple(
                 Source(f"{n}.weight", a, b) for n, a, b in rows)),
-            "o_proj.weight": ParamSpec((self.hidden_size, q)),
+            "o_proj.weight": ParamSpec((self.hidden_size, q), sources=(Source(f"{nm['o']}.weight", 0, self.hidden_size),)),
         }
         if self.bias:
-            specs["qkv_proj.bias"] = ParamSpec((q + 2 * kv,), role="matrix", init="zeros", sources=tuple(
+            # drawn like a matrix in the random-weights mode: a bias of zeros would hide a fault
+            specs["qkv_proj.bias"] = ParamSpec((q + 2 * kv,), role="matrix", init="normal", sources=tuple(
                 Source(f"{n}.bias", a, b) for n, a, b in rows))
         return specs
 

@@ -59,14 +59,37 @@ def interleave_halves(tensor, block: int):
 
 
 @dataclass(frozen=True)
+class CacheTensor:
+    """One tensor that a mixer keeps per token: ``heads`` vectors of ``width`` elements."""
+
+    name: str
+    heads: int
+    width: int
+
+
+@dataclass(frozen=True)
 class CacheSpec:
-    """What a mixer keeps per token: ``kind`` "full" keeps every key, "window"
-    only the last ``window``.  Calls whose specs are equal share a page pool."""
+    """What a mixer keeps per token, in pages: ``kind`` "full" keeps every token, "window" only
+    the last ``window``; ``tensors`` lists what is kept (attention: keys and values of
+    ``num_kv_heads`` heads of ``head_dim``, which is the default; a mixer that caches one latent
+    vector per token lists that alone).  Calls whose specs are equal share a page pool."""
 
     kind: str
-    num_kv_heads: int
-    head_dim: int
+    num_kv_heads: int = 0
+    head_dim: int = 0
     window: int = 0
+    tensors: tuple = ()
+
+    def __post_init__(self):
+        if not self.tensors:
+            object.__setattr__(self, "tensors", (CacheTensor("k", self.num_kv_heads, self.head_dim),
+                                                 CacheTensor("v", self.num_kv_heads, self.head_dim)))
+        names = [t.name for t in self.tensors]
+        if len(set(names)) != len(names) or any(t.heads <= 0 or t.width <= 0 for t in self.tensors):
+            raise ValueError(f"cache tensors need distinct names and positive sizes: {self.tensors}")
+
+    def elements_per_token(self) -> int:
+        return sum(t.heads * t.width for t in self.tensors)
 
 
 @dataclass(frozen=True)
@@ -80,8 +103,13 @@ class StateSpec:
 class Part:
     """Base of all parts: a checkpoint path, parameter specs, bound tensors."""
 
-    #: name of the part inside its block in checkpoint tensor names
+    #: name of the part inside its block in checkpoint tensor names (a LayerSpec may override it)
     tree_name = ""
+    #: True if ``forward`` reads nothing on the host that changes from step to step (everything
+    #: it needs of the batch comes from the device tensors of the StepContext), so that a captured
+    #: CUDA graph of it can be replayed.  A part that reads ``ctx.host`` leaves it False; a model
+    #: with such a part is never captured.
+    capturable = False
 
     def __init__(self):
         self.path = ""
@@ -112,24 +140,33 @@ class Part:
 
 
 class Norm(Part):
+    """y = norm(x) over the last dimension.  ``forward`` and ``add_forward`` get and return plain
+    tensors; which kernels fuse a norm with the products around it is decided below this
+    interface (a norm that is exactly x * rsqrt(mean(x^2) + eps) * weight says so with
+    ``rms_parameters`` and the block then uses the fused kernels)."""
+
     def forward(self, x, out=None):
         raise NotImplementedError
 
-    #: add_forward takes ``scaled_ok`` (see there); a norm without it is never asked for it
-    supports_scaled_rows = False
-
     def add_forward(self, x, residual, rows=None):
-        """residual += x (x may be None), return norm(residual) in the compute dtype.  x is what
-        a mixer or feed-forward returned: a tensor, or a ``kernels.ops.SplitPartials`` or
-        ``PendingProduct`` (pass it to ops.add_rmsnorm as it is, or turn it into a tensor with
-        ops.materialize).  A norm with ``supports_scaled_rows`` also takes ``scaled_ok``: when the
-        block sets it, the part that reads the result hands it to ops.linear only, and the norm may
-        return a ``kernels.ops.ScaledRows`` in place of a tensor."""
+        """residual (float32, in place) += x (a tensor of the compute dtype, or None); returns
+        norm(residual) in the compute dtype.  With ``rows`` (int32) only those rows are normalised
+        and returned, and the residual is left as it is."""
         raise NotImplementedError
+
+    def rms_parameters(self):
+        """(weight, eps) if this norm is a plain RMSNorm, else None."""
+        return None
 
 
 class PositionEncoding(Part):
-    pass
+    """Where positions enter.  Inside a mixer: the attention part hands its position encoding to
+    the fused q/k kernel, which reads ``rotary_dim``, ``interleaved``, ``cos`` and ``sin`` off it.
+    At the embeddings (``ModelSpec.embedding_position``): ``add_to_embeddings`` is called once per
+    step, after the lookup and before the first block."""
+
+    def add_to_embeddings(self, residual, ctx) -> None:
+        """residual float32 [T, hidden] (in place) += this encoding of ``ctx.positions``."""
 
 
 class Mixer(Part):

@@ -9,11 +9,16 @@ from ..kernels import ops
 from .base import FeedForward, ParamSpec, Source, register_feed_forward
 
 
+DEFAULT_NAMES = {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
+
+
 class GatedMLP(FeedForward):
     tree_name = "mlp"
+    capturable = True
 
-    def __init__(self, hidden_size, intermediate_size, activation="silu"):
+    def __init__(self, hidden_size, intermediate_size, activation="silu", names=None):
         super().__init__()
+        self.names = dict(DEFAULT_NAMES, **(names or {}))
         if activation not in ops.ACTIVATIONS:
             raise ValueError(f"unknown activation {activation!r}; known: {sorted(ops.ACTIVATIONS)}")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -21,12 +26,13 @@ class GatedMLP(FeedForward):
         self.block = ops.GATED_BLOCK if intermediate_size % ops.GATED_BLOCK == 0 else 0
 
     def param_specs(self):
-        i = self.intermediate_size
+        i, nm = self.intermediate_size, self.names
         return {
             "gate_up_proj.weight": ParamSpec((2 * i, self.hidden_size), sources=(
-                Source("gate_proj.weight", 0, i), Source("up_proj.weight", i, 2 * i)),
+                Source(f"{nm['gate']}.weight", 0, i), Source(f"{nm['up']}.weight", i, 2 * i)),
                 interleave_halves=self.block),
-            "down_proj.weight": ParamSpec((self.hidden_size, i)),
+            "down_proj.weight": ParamSpec((self.hidden_size, i), sources=(
+                Source(f"{nm['down']}.weight", 0, self.hidden_size),)),
         }
 
     accepts_scaled_rows = True

@@ -8,13 +8,15 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
-from ..config.model_config import ModelSpec
+from ..config.model_config import ModelConfig, ModelSpec
 from ..kernels import ops
-from .base import CacheSpec, ParamSpec, Part, StateSpec, build_norm
-from .block import build_block
+from .base import CacheSpec, ParamSpec, Part, StateSpec, build_norm, build_position_encoding
+from .block import add_and_norm, build_block
 
 
 class Embedding(Part):
+    capturable = True
+
     def __init__(self, vocab_size, hidden_size):
         super().__init__()
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -24,6 +26,8 @@ class Embedding(Part):
 
 
 class LMHead(Part):
+    capturable = True
+
     def __init__(self, vocab_size, hidden_size):
         super().__init__()
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
@@ -59,14 +63,20 @@ class DecoderModel(Part):
         self.blocks = [build_block(layer, spec.hidden_size) for layer in spec.layers]
         self.norm = build_norm(spec.final_norm, spec.hidden_size)
         self.lm_head = None if spec.tie_word_embeddings else LMHead(spec.vocab_size, spec.hidden_size)
-        prefix = spec.weight_prefix
-        self.embed_tokens.set_path(prefix + "embed_tokens")
+        self.embed_position = (build_position_encoding(spec.embedding_position)
+                               if spec.embedding_position is not None else None)
+        # checkpoint names are data of the specification
+        self.embed_tokens.set_path(spec.name_of("embed"))
         for i, block in enumerate(self.blocks):
-            block.set_path(f"{prefix}layers.{i}")
-        self.norm.set_path(prefix + "norm")
+            block.set_path(spec.name_of("layers", i=i))
+        self.norm.set_path(spec.name_of("final_norm"))
         if self.lm_head is not None:
-            self.lm_head.set_path("lm_head")
+            self.lm_head.set_path(spec.name_of("lm_head"))
+        if self.embed_position is not None:
+            self.embed_position.set_path(spec.name_of("embed_position"))
         self._resolve_order()
+        #: every part allows a captured graph of its forward pass to be replayed
+        self.capturable = all(part.capturable for part in self.named_parts())
 
     # ------------------------------------------------------------------ structure
     def _resolve_order(self):
@@ -91,7 +101,7 @@ class DecoderModel(Part):
                 if call.cache not in writers:
                     raise ValueError(f"cache entry {call.cache} is read but never written")
                 wspec = self.blocks[writers[call.cache].layer].mixer.cache_spec()
-                if (wspec.num_kv_heads, wspec.head_dim) != (cspec.num_kv_heads, cspec.head_dim):
+                if wspec.tensors != cspec.tensors:
                     raise ValueError(f"cache entry {call.cache}: reader and writer differ in geometry")
                 if call.cache not in cache_ids:
                     if wspec not in self.cache_groups:
@@ -110,16 +120,10 @@ class DecoderModel(Part):
             self.calls.append(BoundCall(call.layer, cache_index, state_index, call.writes_cache))
         self.group_sizes = group_sizes
 
-    def children(self):
-        out = {"embed_tokens": self.embed_tokens, "norm": self.norm}
-        for i, block in enumerate(self.blocks):
-            out[f"layers.{i}"] = block
-        if self.lm_head is not None:
-            out["lm_head"] = self.lm_head
-        return out
-
     def named_parts(self):
         yield self.embed_tokens
+        if self.embed_position is not None:
+            yield from self.embed_position.named_parts()
         for block in self.blocks:
             yield from block.named_parts()
         yield self.norm
@@ -134,11 +138,19 @@ class DecoderModel(Part):
     def forward(self, ctx):
         """Run this step's tokens; returns 32-bit logits [len(ctx.logit_rows), vocab]."""
         residual = ops.embed_lookup(self.embed_tokens.w["weight"], ctx.token_ids, ctx.slot_tokens)
+        if self.embed_position is not None:
+            self.embed_position.add_to_embeddings(residual, ctx)
         x = None
         for call in self.calls:
             x = self.blocks[call.layer].forward(x, residual, ctx, call)
         if ctx.num_logit_rows == 0:
             return None
-        hidden = self.norm.add_forward(x, residual, rows=ctx.logit_rows)
+        hidden = add_and_norm(self.norm, x, residual, rows=ctx.logit_rows, compute_dtype=ctx.dtype)
         head = self.lm_head.w["weight"] if self.lm_head is not None else self.embed_tokens.w["weight"]
         return ops.linear(hidden, head, out_float32=True)
+
+
+def build_model(config: ModelConfig) -> DecoderModel:
+    """From an architecture's configuration to a model made of parts: the configuration names
+    the parts, layer by layer, and the run order; nothing else of it reaches the parts."""
+    return DecoderModel(config.model_spec())

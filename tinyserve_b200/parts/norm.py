@@ -9,6 +9,8 @@ from .base import Norm, ParamSpec, register_norm
 
 
 class RMSNorm(Norm):
+    capturable = True
+
     def __init__(self, dim: int, eps: float):
         super().__init__()
         self.dim = dim
@@ -24,11 +26,11 @@ class RMSNorm(Norm):
     def forward(self, x, out=None):
         return ops.rmsnorm(x, self.w["weight"], self.eps, out=out)
 
-    supports_scaled_rows = True
+    def add_forward(self, x, residual, rows=None):
+        return ops.add_rmsnorm(x, residual, self.w["weight"], self.eps, self.compute_dtype, rows=rows)
 
-    def add_forward(self, x, residual, rows=None, scaled_ok=False):
-        return ops.add_rmsnorm(x, residual, self.w["weight"], self.eps, self.compute_dtype, rows=rows,
-                               scaled_ok=scaled_ok)
+    def rms_parameters(self):
+        return self.w["weight"], self.eps
 
 
 register_norm("rmsnorm", RMSNorm)

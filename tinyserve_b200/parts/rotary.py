@@ -10,10 +10,9 @@ import torch
 
 from .base import PositionEncoding, register_position_encoding
 
-_TABLES: dict = {}
-
-
 class Rotary(PositionEncoding):
+    capturable = True
+
     def __init__(self, rotary_dim: int, theta: float, pairing: str = "half"):
         super().__init__()
         if rotary_dim % 2:
@@ -32,12 +31,12 @@ class Rotary(PositionEncoding):
         return freqs.cos().float(), freqs.sin().float()
 
     def prepare(self, runtime):
-        key = (self.rotary_dim, self.theta, runtime.max_positions, str(runtime.device))
-        if key not in _TABLES:
+        # one table per (sizes, base) and engine: the layers of a model share it
+        key = ("rotary", self.rotary_dim, self.theta)
+        if key not in runtime.shared:
             cos, sin = self.tables(self.rotary_dim, self.theta, runtime.max_positions)
-            _TABLES.clear()           # one engine's tables at a time
-            _TABLES[key] = (cos.to(runtime.device).contiguous(), sin.to(runtime.device).contiguous())
-        self.cos, self.sin = _TABLES[key]
+            runtime.shared[key] = (cos.to(runtime.device).contiguous(), sin.to(runtime.device).contiguous())
+        self.cos, self.sin = runtime.shared[key]
 
 
 register_position_encoding("rotary", Rotary)

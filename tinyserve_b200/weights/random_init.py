@@ -34,7 +34,7 @@ def write_random_model(config, out_dir: str, seed: int = 0, store_dtype: str = "
     Tensors are drawn on the CPU from one generator seeded with ``seed``, in the model's
     fixed tensor order, in 32-bit, then stored as ``store_dtype``; ``vector_dtype`` (default:
     the same) is the storage type of norm weights and other vectors."""
-    from ..engine.build import build_model
+    from ..parts.model import build_model
     model = build_model(config)
     gen = torch.Generator(device="cpu")
     gen.manual_seed(int(seed))
