@@ -8,9 +8,10 @@ fused Triton ops off (``serve.TRITON_KERNELS = False``) and the attention to the
 ``serve.torch_ref_attention`` (serve.py:639), gives every layer a paged cache, loads the
 weights of a folder written by ``write_random_model`` with q/k/v and gate/up fused as
 ``load_model`` does (serve.py:1352-1358), and runs ``Model.forward`` + ``Model.logits`` over a
-prompt, whole and cut in two portions.  ``tests/test_plain.py`` compares the plain
-implementation with the stored logits; the stored checksum tells whether the random
-weights of this torch version are still the ones the logits belong to.
+prompt, whole and cut in two portions.  The weights are bfloat16 numbers (exact in the
+reference's float32 model) and are stored beside the logits, as their 16-bit patterns, so that
+``tests/test_plain.py`` holds the plain implementation to the stored logits with exactly the
+tensors the reference ran on, whatever random numbers a torch version draws.
 """
 import argparse
 import importlib.util
@@ -31,10 +32,6 @@ from helpers import make_model_dir, random_ids, tiny_config_dict  # noqa: E402
 
 PROMPT_LEN = 37
 BLOCK = 8
-
-
-def checksum(tensors) -> float:
-    return float(sum(t.double().abs().sum().item() for _, t in sorted(tensors.items())))
 
 
 def reference_logits(serve, raw, tensors, ids, cuts):
@@ -91,14 +88,15 @@ def main():
     for name in ("A", "B"):
         raw = tiny_config_dict(name)
         with tempfile.TemporaryDirectory() as folder:
-            make_model_dir(folder, name, seed=11, store_dtype="float32")
+            make_model_dir(folder, name, seed=11, store_dtype="bfloat16")
             tensors = load_file(os.path.join(folder, "model.safetensors"))
         ids = random_ids(raw["vocab_size"], PROMPT_LEN, seed=5)
         whole = reference_logits(serve, raw, tensors, ids, [PROMPT_LEN])
         cut = reference_logits(serve, raw, tensors, ids, [20, PROMPT_LEN - 20])
         print(name, "reference whole vs two portions:", (whole - cut).abs().max().item())
-        np.savez(os.path.join(HERE, f"reference_logits_{name}.npz"), ids=np.array(ids),
-                 logits=whole.numpy().astype(np.float32), checksum=np.float64(checksum(tensors)))
+        stored = {"w:" + k: t.to(torch.bfloat16).view(torch.int16).numpy() for k, t in tensors.items()}
+        np.savez_compressed(os.path.join(HERE, f"reference_logits_{name}.npz"), ids=np.array(ids),
+                            logits=whole.numpy().astype(np.float32), **stored)
         print("wrote", f"reference_logits_{name}.npz", whole.shape)
 
 

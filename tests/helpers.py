@@ -5,7 +5,7 @@ import json
 
 import torch
 
-# Three tiny Qwen3 configurations that differ in every size and option.
+# Four tiny Qwen3 configurations that differ in every size and option.
 TINY = {
     # MHA, head_dim * heads == hidden, tied embeddings
     "A": dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
@@ -20,6 +20,10 @@ TINY = {
               head_dim=48, intermediate_size=100, vocab_size=301, rms_norm_eps=3e-6, rope_theta=5e5,
               tie_word_embeddings=False, max_position_embeddings=512, use_sliding_window=True,
               sliding_window=40, max_window_layers=2),
+    # biases on q, k and v (drawn non-zero), widths that are multiples of 8 but fill no tile
+    "D": dict(hidden_size=88, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              head_dim=16, intermediate_size=136, vocab_size=211, rms_norm_eps=2e-6, rope_theta=2e5,
+              tie_word_embeddings=False, max_position_embeddings=256, attention_bias=True),
 }
 
 

@@ -22,7 +22,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # float32: rounding of 32-bit sums only (the plain side is float64).  bfloat16: activations
 # carry 8 bits of mantissa (2^-8 = 0.4 %) through a few layers.
 TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
-LENGTHS = {"A": [5, 17, 31, 70, 2], "B": [1, 9, 40, 63, 100], "C": [90, 130, 57, 3, 75]}
+LENGTHS = {"A": [5, 17, 31, 70, 2], "B": [1, 9, 40, 63, 100], "C": [90, 130, 57, 3, 75], "D": [33, 2, 80, 19, 64]}
 
 
 @pytest.fixture(scope="module", params=sorted(TINY))
@@ -36,9 +36,9 @@ def model(request, tmp_path_factory):
     return {"name": name, "folder": folder, "cfg": cfg, "weights": weights, "requests": reqs, "ref": ref}
 
 
-def run_replay(folder, dtype, steps, out_dir, max_tokens=None):
+def run_replay(folder, dtype, steps, out_dir, max_tokens=None, page=16):
     from tinyserve_b200.engine import replay
-    runner = replay.make_runner(folder, dtype, max_tokens or max_live_tokens(steps))
+    runner = replay.make_runner(folder, dtype, max_tokens or max_live_tokens(steps), block_size=page)
     done = []
     replay.replay(runner, lines_of(steps), str(out_dir), done.append)
     assert done == [f"done {s['step']}" for s in steps]
@@ -56,8 +56,8 @@ def run_replay(folder, dtype, steps, out_dir, max_tokens=None):
     return outputs, runner
 
 
-def check(model, dtype, steps, out_dir, max_tokens=None):
-    outputs, runner = run_replay(model["folder"], dtype, steps, out_dir, max_tokens)
+def check(model, dtype, steps, out_dir, max_tokens=None, page=16):
+    outputs, runner = run_replay(model["folder"], dtype, steps, out_dir, max_tokens, page)
     got = collect_logits(steps, outputs, model["cfg"]["vocab_size"])
     worst = 0.0
     for rid, ref in model["ref"].items():
@@ -104,6 +104,28 @@ def test_mixed_with_pages_used_again(model, dtype, seed, tmp_path):
     _, runner = check(model, dtype, steps, tmp_path)
     total = sum(-(-len(i) // 16) for i in {**reqs, **more}.values())
     assert total > runner.manager.pools[0].num_usable, "the pool is too small to avoid reuse"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_four_schedules_at_pages_of_8(model, dtype, tmp_path):
+    """The page size of the second tiny configuration's workload: page edges fall elsewhere, a
+    64-key tile of the attention kernels spans eight pages."""
+    reqs = model["requests"]
+    for name, steps in (("whole", schedule_whole(reqs)), ("tail", schedule_tail_decode(reqs, 32)),
+                        ("portions", schedule_portions(reqs)), ("mixed", schedule_mixed(reqs, max_live=4, seed=2))):
+        check(model, dtype, steps, tmp_path / name, page=8)
+
+
+def test_a_bias_that_is_not_zero_reaches_the_logits(tmp_path):
+    """The configuration with attention_bias draws its biases like matrices; without them the
+    logits differ by far more than rounding, so a test that passes has used them."""
+    folder = make_model_dir(tmp_path / "m", "D", seed=21)
+    cfg, weights = plain.load_folder(folder)
+    assert any(k.endswith("q_proj.bias") and v.abs().max() > 0 for k, v in weights.items())
+    ids = random_ids(cfg["vocab_size"], 40, seed=1)
+    with_bias = plain.logits(cfg, weights, ids)
+    without = plain.logits(cfg, {k: v for k, v in weights.items() if not k.endswith(".bias")}, ids)
+    assert (with_bias - without).abs().max().item() > 0.05 * with_bias.abs().max().item()
 
 
 def test_schedules_agree_with_each_other_in_32_bit(model, tmp_path):

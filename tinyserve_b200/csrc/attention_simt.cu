@@ -305,9 +305,12 @@ TS_EXPORT int ts_paged_attention(int dtype, const void* q, void* out, const void
 
 static __device__ __align__(256) float ts_static_scratch[TS_STATIC_SCRATCH_FLOATS];
 
+#include <mutex>
+
 namespace {
 constexpr int MAX_DEVICES = 64;
 float* static_scratch_address[MAX_DEVICES] = {nullptr};
+std::mutex static_scratch_mutex;       // guards the table above (first calls from several threads)
 }  // namespace
 
 TS_EXPORT int ts_paged_attention_static_scratch(
@@ -317,7 +320,8 @@ TS_EXPORT int ts_paged_attention_static_scratch(
     int num_splits, cudaStream_t stream) {
   TS_REQUIRE(num_tokens > 0 && H > 0 && num_splits >= 1, "paged_attention_static_scratch: empty batch");
   const long long rows = (long long)num_tokens * H * num_splits;
-  const long long need = rows * (D + 2);
+  // one key range needs no scratch at all: the kernel writes its output directly
+  const long long need = num_splits > 1 ? rows * (D + 2) : 0;
   TS_REQUIRE(need <= (long long)TS_STATIC_SCRATCH_FLOATS,
              "paged_attention_static_scratch: %d tokens x %d heads x %d splits need %lld floats of "
              "scratch, the static array holds %d",
@@ -326,14 +330,18 @@ TS_EXPORT int ts_paged_attention_static_scratch(
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return ts_fail("paged_attention_static_scratch: %s", cudaGetErrorString(e));
   TS_REQUIRE(device >= 0 && device < MAX_DEVICES, "paged_attention_static_scratch: device %d out of range", device);
-  if (static_scratch_address[device] == nullptr) {
-    float* address = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), ts_static_scratch);
-    if (e != cudaSuccess || address == nullptr)
-      return ts_fail("paged_attention_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    static_scratch_address[device] = address;
+  float* part_o = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(static_scratch_mutex);
+    if (static_scratch_address[device] == nullptr) {
+      float* address = nullptr;
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), ts_static_scratch);
+      if (e != cudaSuccess || address == nullptr)
+        return ts_fail("paged_attention_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      static_scratch_address[device] = address;
+    }
+    part_o = static_scratch_address[device];
   }
-  float* part_o = static_scratch_address[device];
   float* part_ml = part_o + rows * D;
   return ts_paged_attention(dtype, q, out, k_cache, v_cache, block_table, cu_q, kv_lens, num_tokens,
                             num_requests, max_q_len, H, Hkv, page_size, max_blocks, scale, window,

@@ -12,9 +12,10 @@
 //
 // Limits and rules:
 //  * The array holds TS_STATIC_SCRATCH_FLOATS floats (4 MiB).  Every GPU on which a process
-//    loads this library keeps that much memory until the process ends.  A call needs
-//    num_tokens * H * num_splits * (head size + 2) floats; a larger call is refused with an
-//    error message and nothing is launched.
+//    loads this library keeps that much memory until the process ends.  A call with more
+//    than one key range needs num_tokens * H * num_splits * (head size + 2) floats; a larger
+//    call is refused with an error message and nothing is launched.  A call with num_splits
+//    == 1 keeps nothing in the array and is never refused for its size.
 //  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
 //    that device current) and keeps it.  Make that first call before any stream capture begins.
 //  * The function calls no cudaMalloc, cudaFree or other allocating routine.
