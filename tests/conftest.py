@@ -11,6 +11,10 @@ for p in (ROOT, os.path.dirname(os.path.abspath(__file__))):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+    # every engine that a test builds checks the index buffers of every step, on the host and on
+    # the device (serving leaves this off)
+    from tinyserve_b200.config import engine_config
+    engine_config.CHECK_INDICES_DEFAULT = True
 
 
 def pytest_collection_modifyitems(config, items):

@@ -252,3 +252,29 @@ def test_command_line_writes_random_weights_and_generates(tmp_path):
     assert [int(t) for t in out.stdout.strip().splitlines()[-1].split()] == plain.greedy_generate(cfg, weights, prompt, 10)
     assert run("serve").returncode == 2
     assert run("generate").returncode == 2
+
+
+def test_host_index_check_refuses_a_corrupted_step(tmp_path):
+    """The host half of the debug pass: a packed step whose index buffers do not fit the model,
+    the batch or the cache is refused before it is uploaded."""
+    from tinyserve_b200.config import EngineConfig
+    from tinyserve_b200.engine.batch import StepEntry
+    from tinyserve_b200.engine.runner import ModelRunner
+    folder = make_model_dir(tmp_path, "A", seed=3)
+    runner = ModelRunner(EngineConfig(model=folder, dtype="float32", max_model_len=64, block_size=16,
+                                      max_num_seqs=2, max_num_batched_tokens=32, num_blocks=6))
+    assert runner.cfg.check_indices, "tests run with the index check on"
+    runner.manager.begin("a")
+    entries = [StepEntry("a", [1, 2, 3], [2])]
+    runner.step(entries)                                     # a sound step passes
+    h = runner._hosts_np[0]
+    for name, at, value, what in (("token_ids", 1, 256, "token id"), ("positions", 0, 64, "position"),
+                                  ("logit_rows", 0, 3, "wanted row"), ("slot_mapping0", 2, 7 * 16, "cache slot"),
+                                  ("block_table0", 0, 7, "page number"), ("state_slots", 0, 2, "state slot"),
+                                  ("cu_q", 1, 9, "query offsets")):
+        ctx = runner._pack([StepEntry("a", [4, 5, 6], [2])], 0)
+        runner._check_host(ctx, 0)
+        runner._seg(h, name)[at] = value
+        with pytest.raises(ValueError, match=what):
+            runner._check_host(ctx, 0)
+    runner.manager.free("a")

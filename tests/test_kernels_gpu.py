@@ -654,3 +654,55 @@ def test_split_partials_and_their_consumers(M, N, K, splits):
         for a, b in ((q_a, q_b), (caches[0], caches[2]), (caches[1], caches[3])):
             assert (a.float() - b.float()).abs().max().item() <= 2e-2 * b.float().abs().max().item()
     assert o.gemm_tcgen05_error() == 0
+
+
+# ----------------------------------------------------------------------------- index check
+def test_index_check_neutralises_bad_indices_and_reports_them():
+    """The device half of the debug pass: indices outside their buffers are replaced by harmless
+    ones before any kernel uses them, and the status words say what was found.  (Nothing here
+    reads or writes out of bounds: the check kernel only compares and rewrites the indices.)"""
+    o = ops()
+    dev = "cuda"
+    i32 = lambda *v: torch.tensor(v, dtype=torch.int32, device=dev)
+    words = o.status_words()
+    assert not words.any()
+
+    def step(**over):
+        base = dict(token_ids=i32(5, 1, 2, -2), positions=i32(0, 1, 2, 7), logit_rows=i32(2, 3), cu_q=i32(0, 3, 4),
+                    kv_lens=i32(3, 8), state_slots=i32(0, 1), slot_tokens=i32(4, 6, 0), num_tokens=4, num_requests=2,
+                    num_logit_rows=2)
+        base.update(over)
+        view = SimpleNamespace(slot_mapping=over.get("slot_mapping", i32(16, 17, 18, 39)), page_size=8, max_blocks=2,
+                               block_table=over.get("block_table", i32(2, 0, 4, 3).view(2, 2)), num_pages=5)
+        return SimpleNamespace(groups=[view], **{k: v for k, v in base.items() if k not in ("slot_mapping", "block_table")})
+
+    try:
+        good = step()
+        before = {k: v.clone() for k, v in vars(good).items() if isinstance(v, torch.Tensor)}
+        o.sanitize_step(good, vocab_size=10, num_positions=16, max_kv_len=16, num_state_slots=2)
+        torch.cuda.synchronize()
+        assert not words.any(), "a step whose indices are fine is left alone"
+        assert all(torch.equal(v, getattr(good, k)) for k, v in before.items())
+        cases = [
+            (dict(token_ids=i32(5, 10, 2, -2)), 1, lambda c: c.token_ids.tolist() == [5, 0, 2, -2]),
+            (dict(token_ids=i32(5, 1, 2, -4)), 6, lambda c: c.token_ids.tolist() == [5, 1, 2, 0]),
+            (dict(slot_tokens=i32(4, 60, 0)), 1, lambda c: c.slot_tokens.tolist() == [4, 0, 0]),
+            (dict(positions=i32(0, 1, 16, 7)), 4, lambda c: c.positions.tolist() == [0, 1, 0, 7]),
+            (dict(logit_rows=i32(2, 4)), 5, lambda c: c.logit_rows.tolist() == [2, 0]),
+            (dict(state_slots=i32(0, 2)), 6, lambda c: c.state_slots.tolist() == [0, 0]),
+            (dict(cu_q=i32(0, 5, 4)), 7, lambda c: c.cu_q.tolist() == [0, 0, 0] and c.kv_lens.tolist() == [0, 0]),
+            (dict(kv_lens=i32(2, 8)), 7, lambda c: c.cu_q.tolist() == [0, 0, 0]),
+            (dict(slot_mapping=i32(16, 17, 40, 39)), 2, lambda c: c.groups[0].slot_mapping.tolist() == [16, 17, -1, 39]),
+            (dict(block_table=i32(2, 5, 4, -1).view(2, 2)), 3, lambda c: c.groups[0].block_table.tolist() == [[2, 0], [4, 0]]),
+        ]
+        for over, code, repaired in cases:
+            ctx = step(**over)
+            o.sanitize_step(ctx, vocab_size=10, num_positions=16, max_kv_len=16, num_state_slots=2)
+            torch.cuda.synchronize()
+            assert words[1] == code and words[0] == 0, (over, int(words[1]))
+            assert repaired(ctx), over
+            with pytest.raises(o.DeviceError):
+                o.raise_on_device_error()
+            words[:] = 0
+    finally:
+        words[:] = 0

@@ -6,6 +6,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 
+#: what ``check_indices`` is when an engine is configured without saying (tests switch it on)
+CHECK_INDICES_DEFAULT = False
+
 DTYPE_NAMES = {"bfloat16": "bfloat16", "bf16": "bfloat16", "float32": "float32", "fp32": "float32"}
 
 
@@ -22,8 +25,13 @@ class EngineConfig:
     use_cuda_graphs: bool = True        # replay captured decode steps
     seed: int = 0
     device: str = "cuda:0"
+    # debug pass: check every index buffer of every step on the host before it is uploaded, and
+    # again on the device before the kernels run (the stand-in for a memory checker)
+    check_indices: bool = None
 
     def __post_init__(self):
+        if self.check_indices is None:
+            self.check_indices = CHECK_INDICES_DEFAULT
         if self.dtype not in DTYPE_NAMES:
             raise ValueError(f"dtype must be one of {sorted(DTYPE_NAMES)}, got {self.dtype!r}")
         self.dtype = DTYPE_NAMES[self.dtype]

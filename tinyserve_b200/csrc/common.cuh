@@ -11,12 +11,6 @@
 
 #define TS_EXPORT extern "C" __attribute__((visibility("default")))
 
-#ifdef TS_CHECK_BOUNDS
-#define TS_BOUNDS_BUILD 1
-#else
-#define TS_BOUNDS_BUILD 0
-#endif
-
 // element type codes shared with the Python bindings
 enum TsDtype : int { TS_F32 = 0, TS_BF16 = 1 };
 
@@ -96,11 +90,12 @@ __device__ __forceinline__ void timeline_mark_thread(int, int) {}
 #endif
 
 // ---------------------------------------------------------------- status words
-// Kernels never trap.  A kernel that gives up on a bounded wait, or (in a TS_CHECK_BOUNDS build)
-// meets an index outside its buffer, skips the access and stores a code into a few words of
-// pinned host memory that the engine reads after it has synchronised for a step's tokens anyway.
-// Word 0: a wait ran out.  Word 1: an index was out of range (the code says which buffer).
-// ts_set_status_words() hands the words' address to the library once per device.
+// Kernels never trap.  A kernel that gives up on a bounded wait, and the index check of a step
+// (ts_sanitize_step / ts_sanitize_group in elementwise.cu) when it meets an index outside its
+// buffer, store a code into a few words of pinned host memory that the engine reads after it has
+// synchronised for a step's tokens anyway.  Word 0: a wait ran out.  Word 1: an index was out of
+// range (the code says which buffer).  ts_set_status_words() hands the words' address to the
+// library once per device.
 static __device__ int* g_status_words = nullptr;
 enum { TS_STATUS_WAIT = 0, TS_STATUS_BOUNDS = 1 };
 enum { TS_BAD_TOKEN_ID = 1, TS_BAD_CACHE_SLOT = 2, TS_BAD_PAGE = 3, TS_BAD_POSITION = 4, TS_BAD_ROW = 5,
@@ -112,21 +107,12 @@ __device__ __forceinline__ void ts_raise_status(int word, int code) {
     __threadfence_system();
   }
 }
-#ifdef TS_CHECK_BOUNDS
-// true if the index is fine; otherwise records `code` and the caller skips the access
-#define TS_IN_BOUNDS(cond, code) ((cond) ? true : (ts_raise_status(TS_STATUS_BOUNDS, (code)), false))
-#else
-#define TS_IN_BOUNDS(cond, code) true
-#endif
 
 #define TS_DEFINE_LAST_ERROR() \
   TS_DEFINE_TIMELINE()         \
   TS_EXPORT const char* ts_last_error() { return ts_error_message; }                                  \
   TS_EXPORT int ts_set_status_words(int* words) {                                                     \
     return cudaMemcpyToSymbol(g_status_words, &words, sizeof(words)) == cudaSuccess ? 0 : 1;          \
-  }                                                                                                   \
-  TS_EXPORT int ts_checks_bounds() {                                                                  \
-    return sizeof(char[TS_BOUNDS_BUILD + 1]) - 1;                                                     \
   }
 
 // ---------------------------------------------------------------- programmatic dependent launch

@@ -43,6 +43,104 @@ TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, floa
   return 0;
 }
 
+// ------------------------------------------------------------------ index check of a step
+// The debug pass that stands where a memory checker would: before a step's kernels run, one small
+// kernel looks at every index the step brings.  An index outside its buffer is replaced by a
+// harmless one (token 0, position 0, row 0, "no cache slot", the null page, an empty request), so
+// that no later kernel reads or writes out of bounds, and its kind is stored in the status words
+// (common.cuh), which the engine turns into an error.  Off in serving; tests switch it on.
+__global__ void sanitize_step_kernel(int* token_ids, int T, int vocab, int* slot_tokens, int num_state_slots,
+                                     int* positions, int num_positions, int* logit_rows, int W, int* cu_q,
+                                     int* kv_lens, int B, int max_kv_len, int* state_slots) {
+  pdl_trigger();
+  pdl_wait();
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const int id = token_ids[t];
+    if (id >= vocab) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_TOKEN_ID);
+      token_ids[t] = 0;
+    } else if (id < 0) {
+      const int slot = -1 - id;
+      if (slot_tokens == nullptr || slot >= num_state_slots) {
+        ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_STATE_SLOT);
+        token_ids[t] = 0;
+      } else if (slot_tokens[slot] < 0 || slot_tokens[slot] >= vocab) {
+        ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_TOKEN_ID);
+        slot_tokens[slot] = 0;
+      }
+    }
+    if (positions[t] < 0 || positions[t] >= num_positions) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_POSITION);
+      positions[t] = 0;
+    }
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    if (logit_rows[i] < 0 || logit_rows[i] >= T) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_ROW);
+      logit_rows[i] = 0;
+    }
+  __shared__ int bad_requests;
+  if (threadIdx.x == 0) bad_requests = cu_q[0] != 0 || cu_q[B] > T;
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += blockDim.x) {
+    const int n = cu_q[b + 1] - cu_q[b];
+    if (n < 0) atomicOr(&bad_requests, 1);
+    if (kv_lens[b] < 0 || kv_lens[b] > max_kv_len || (n > 0 && kv_lens[b] < n)) atomicOr(&bad_requests, 1);
+    if (state_slots[b] < 0 || state_slots[b] >= num_state_slots) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_STATE_SLOT);
+      state_slots[b] = 0;
+    }
+  }
+  __syncthreads();
+  if (bad_requests) {
+    // the requests' extents do not fit the batch: nobody brings a token, nobody holds a key
+    if (threadIdx.x == 0) ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_REQUEST);
+    for (int b = threadIdx.x; b <= B; b += blockDim.x) {
+      cu_q[b] = 0;
+      if (b < B) kv_lens[b] = 0;
+    }
+  }
+}
+
+__global__ void sanitize_group_kernel(int* slot_mapping, int T, long long total_slots, int* block_table, int B,
+                                      int max_blocks, int row_stride, int num_pages) {
+  pdl_trigger();
+  pdl_wait();
+  for (int t = threadIdx.x; t < T; t += blockDim.x)
+    if (slot_mapping[t] < -1 || slot_mapping[t] >= total_slots) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_CACHE_SLOT);
+      slot_mapping[t] = -1;
+    }
+  for (int i = threadIdx.x; i < B * max_blocks; i += blockDim.x) {
+    int* entry = block_table + (size_t)(i / max_blocks) * row_stride + i % max_blocks;
+    if (*entry < 0 || *entry >= num_pages) {
+      ts_raise_status(TS_STATUS_BOUNDS, TS_BAD_PAGE);
+      *entry = 0;
+    }
+  }
+}
+
+// token_ids, positions [T]; logit_rows [W]; cu_q [B + 1]; kv_lens, state_slots [B]; slot_tokens
+// [num_state_slots] or null.  All are read and, where out of range, rewritten in place.
+TS_EXPORT int ts_sanitize_step(int* token_ids, int T, int vocab, int* slot_tokens, int num_state_slots, int* positions,
+                               int num_positions, int* logit_rows, int W, int* cu_q, int* kv_lens, int B,
+                               int max_kv_len, int* state_slots, cudaStream_t stream) {
+  TS_REQUIRE(T > 0 && B > 0 && W >= 0 && vocab > 0 && num_positions > 0, "sanitize_step: empty step");
+  TS_LAUNCH("sanitize_step", sanitize_step_kernel, 1, 256, 0, stream, token_ids, T, vocab, slot_tokens, num_state_slots,
+            positions, num_positions, logit_rows, W, cu_q, kv_lens, B, max_kv_len, state_slots);
+  return 0;
+}
+
+// slot_mapping [T] (page * page_size + slot, -1: none) of a pool of total_slots slots; block_table
+// [B, max_blocks] with rows row_stride apart, entries below num_pages.
+TS_EXPORT int ts_sanitize_group(int* slot_mapping, int T, long long total_slots, int* block_table, int B, int max_blocks,
+                                int row_stride, int num_pages, cudaStream_t stream) {
+  TS_REQUIRE(T > 0 && B > 0 && max_blocks > 0 && num_pages > 0, "sanitize_group: empty step");
+  TS_LAUNCH("sanitize_group", sanitize_group_kernel, 1, 256, 0, stream, slot_mapping, T, total_slots, block_table, B,
+            max_blocks, row_stride, num_pages);
+  return 0;
+}
+
 // ------------------------------------------------------------------ residual add + RMSNorm
 // One block per output row.  v = residual[r] + x[r] (x may be null), residual[r] = v when
 // `write_residual`, out[i] = v * rsqrt(mean(v^2) + eps) * w.  With `rows`, output row i reads

@@ -23,6 +23,7 @@ class GroupView:
     max_blocks: int
     slot_mapping: torch.Tensor      # int32 [T]: page * page_size + slot of each new token, -1 = none
     block_table: torch.Tensor       # int32 [B, max_blocks]
+    num_pages: int = 0              # pages of the group's pool (the null page included)
 
 
 class StepContext:

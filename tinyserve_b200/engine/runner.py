@@ -237,7 +237,7 @@ class ModelRunner:
         for g in range(len(self.model.cache_groups)):
             table = self._seg(d, f"block_table{g}").view(self.cfg.max_num_seqs, self.max_blocks)
             ctx.groups.append(GroupView(self.page_size, self.max_blocks,
-                                        self._seg(d, f"slot_mapping{g}", T), table[:B]))
+                                        self._seg(d, f"slot_mapping{g}", T), table[:B], self.num_pages))
         ctx.device_cache = self.device_cache
         ctx.dtype = self.dtype
         ctx.slot_tokens = self.slot_tokens
@@ -245,6 +245,40 @@ class ModelRunner:
 
     def _upload(self, buf=0):
         self._dev.copy_(self._hosts[buf], non_blocking=True)
+
+    def _check_host(self, ctx, buf):
+        """The host half of the index check: every index buffer of the packed step against the size
+        of what it indexes, before anything is uploaded."""
+        h = self._hosts_np[buf]
+        seg = lambda name, n: self._seg(h, name, n)
+        T, B, cfg = ctx.num_tokens, ctx.num_requests, self.cfg
+        S, vocab = cfg.max_num_seqs, self.model.vocab_size
+        ids, pos, cu, kv = seg("token_ids", T), seg("positions", T), seg("cu_q", B + 1), seg("kv_lens", B)
+        problems = []
+        if ((ids >= vocab) | (ids < -S)).any():
+            problems.append(f"a token id outside [0, {vocab}) that names no state slot")
+        if ((pos < 0) | (pos >= cfg.max_model_len)).any():
+            problems.append(f"a position outside [0, {cfg.max_model_len})")
+        rows = seg("logit_rows", ctx.num_logit_rows)
+        if ((rows < 0) | (rows >= T)).any():
+            problems.append(f"a wanted row outside the batch of {T} tokens")
+        q_lens = np.diff(cu)
+        if cu[0] != 0 or (q_lens < 0).any() or cu[B] > T:
+            problems.append("query offsets that are not 0 .. T in ascending order")
+        elif ((kv < q_lens) | (kv > cfg.max_model_len)).any():
+            problems.append("a request whose length is below its new tokens or above max_model_len")
+        slots = seg("state_slots", B)
+        if ((slots < 0) | (slots >= S)).any():
+            problems.append(f"a state slot outside [0, {S})")
+        for g in range(len(self.model.cache_groups)):
+            sm = seg(f"slot_mapping{g}", T)
+            if ((sm < -1) | (sm >= self.num_pages * self.page_size)).any():
+                problems.append(f"group {g}: a cache slot outside the pool of {self.num_pages} pages")
+            table = self._seg(h, f"block_table{g}").reshape(S, self.max_blocks)[:B]
+            if ((table < 0) | (table >= self.num_pages)).any():
+                problems.append(f"group {g}: a page number outside [0, {self.num_pages})")
+        if problems:
+            raise ValueError("the packed step holds " + "; ".join(problems))
 
     # ------------------------------------------------------------------ stepping
     def prepare(self, entries) -> Prepared:
@@ -263,6 +297,8 @@ class ModelRunner:
             self._seg(self._hosts_np[buf], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
         else:
             ctx = self._pack(entries, buf)
+        if self.cfg.check_indices:
+            self._check_host(ctx, buf)
         return Prepared(entries, ctx, graph, buf)
 
     @torch.inference_mode()
@@ -284,11 +320,17 @@ class ModelRunner:
             logits = out[:len(prep.entries)]
         else:
             with ops.stream_scope():
-                logits = self.model.forward(self._bind_device_views(prep.ctx))
+                logits = self._forward(self._bind_device_views(prep.ctx))
         for e in prep.entries:
             if self.manager.is_live(e.rid):      # a request may have ended since it was packed
                 self.manager.commit(e.rid, len(e.tokens))
         return logits
+
+    def _forward(self, ctx):
+        if self.cfg.check_indices:
+            ops.sanitize_step(ctx, self.model.vocab_size, self.cfg.max_model_len, self.cfg.max_model_len,
+                              self.cfg.max_num_seqs)
+        return self.model.forward(ctx)
 
     def step(self, entries):
         """Run one batch.  Returns float32 logits [number of wanted places, vocab] on the
@@ -348,13 +390,13 @@ class ModelRunner:
                 stream = torch.cuda.Stream(self.device)
                 stream.wait_stream(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(stream), ops.stream_scope():
-                    self.model.forward(ctx)           # warm-up outside capture
+                    self._forward(ctx)                # warm-up outside capture
                 torch.cuda.current_stream(self.device).wait_stream(stream)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
                 with torch.cuda.graph(graph, pool=pool), ops.stream_scope():
-                    out = self.model.forward(ctx)
+                    out = self._forward(ctx)
                 pool = pool or graph.pool()
                 self.graphs[size] = (graph, out, size, ops.launch_count() - before)
         finally:

@@ -49,20 +49,31 @@ def find_nvcc() -> str:
                      "/usr/local/cuda/bin and PATH); the CUDA kernels cannot be built")
 
 
+_build_dir = None
+
+
 def build_dir() -> str:
-    env = os.environ.get("TINYSERVE_BUILD_DIR")
-    here = env or os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build")
-    try:
-        os.makedirs(here, exist_ok=True)
-        probe = os.path.join(here, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.remove(probe)
-        return here
-    except OSError:
-        alt = os.path.join(tempfile.gettempdir(), f"tinyserve_b200_build_{os.getuid()}")
-        os.makedirs(alt, exist_ok=True)
-        return alt
+    """Where libraries go: ``kernels/_build`` inside the package (or $TINYSERVE_BUILD_DIR), or a
+    per-user folder under the temporary directory when that cannot be written.  Decided once per
+    process."""
+    global _build_dir
+    with _lock:
+        if _build_dir is not None:
+            return _build_dir
+        env = os.environ.get("TINYSERVE_BUILD_DIR")
+        here = env or os.path.join(os.path.dirname(os.path.abspath(__file__)), "_build")
+        try:
+            os.makedirs(here, exist_ok=True)
+            probe = os.path.join(here, f".w{os.getpid()}.{threading.get_ident()}")
+            with open(probe, "w"):
+                pass
+            os.remove(probe)
+            _build_dir = here
+        except OSError:
+            alt = os.path.join(tempfile.gettempdir(), f"tinyserve_b200_build_{os.getuid()}")
+            os.makedirs(alt, exist_ok=True)
+            _build_dir = alt
+        return _build_dir
 
 
 def unit_path(source: str, defines: dict) -> tuple:

@@ -398,6 +398,24 @@ def units_for(head_dims) -> list:
 
 
 # ----------------------------------------------------------------------------- ops
+def sanitize_step(ctx, vocab_size, num_positions, max_kv_len, num_state_slots):
+    """The device half of the index check (see csrc/elementwise.cu): every index of the step in
+    ``ctx`` that lies outside its buffer is replaced by a harmless one and reported through the
+    status words.  One small kernel, plus one per cache group."""
+    lib = _elementwise()
+    _cuda(ctx.token_ids, ctx.positions, ctx.cu_q, ctx.kv_lens, ctx.state_slots)
+    _check(lib, lib.ts_sanitize_step(
+        _ptr(ctx.token_ids), c_int(ctx.num_tokens), c_int(vocab_size), _ptr(ctx.slot_tokens),
+        c_int(num_state_slots), _ptr(ctx.positions), c_int(num_positions), _ptr(ctx.logit_rows),
+        c_int(ctx.num_logit_rows), _ptr(ctx.cu_q), _ptr(ctx.kv_lens), c_int(ctx.num_requests), c_int(max_kv_len),
+        _ptr(ctx.state_slots), _stream()))
+    for view in ctx.groups:
+        _check(lib, lib.ts_sanitize_group(
+            _ptr(view.slot_mapping), c_int(ctx.num_tokens), c_longlong(view.num_pages * view.page_size),
+            _ptr(view.block_table), c_int(ctx.num_requests), c_int(view.max_blocks),
+            c_int(view.block_table.stride(0)), c_int(view.num_pages), _stream()))
+
+
 def embed_lookup(table, ids, slot_tokens=None):
     """float32 [T, n] = table[ids]; ids int32.  An id < 0 names a state slot (-1 - slot) whose
     last sampled token is read from ``slot_tokens`` on the device."""
