@@ -132,8 +132,36 @@ def _prefill(serve, engine, tokens, vocab, seed, repeats=3):
     return min(times[1:])
 
 
+def burst(serve, raw: dict, seed: int) -> dict:
+    """The reference's own burst workload (README.md:114-116) at Qwen3-0.6B shapes: 256 requests at
+    once, prompts of 1 to 2,048 random tokens, 128 greedy tokens each, 2,048 tokens a step."""
+    import torch
+    V = raw["vocab_size"]
+    folder = _scratch_dir(4 << 30)
+    try:
+        write_model_folder(raw, folder, seed)
+        engine = serve.Engine(serve.Config(model=folder, max_model_len=4096, max_num_seqs=256,
+                                           max_num_batched_tokens=2048))
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(1, 2049, (256,), generator=g).tolist()
+    prompts = [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+    warm = serve.SamplingParams(temperature=0.0, max_tokens=4, repetition_penalty=1.0, ignore_eos=True)
+    engine.generate([torch.randint(0, V, (64,), generator=g).tolist() for _ in range(8)], warm)
+    params = serve.SamplingParams(temperature=0.0, max_tokens=128, repetition_penalty=1.0, ignore_eos=True)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    generated = sum(len(o.token_ids) for o in outs)
+    return {"burst_0p6b_total_tok_s": round((generated + sum(lens)) / dt, 1),
+            "burst_0p6b_gen_tok_s": round(generated / dt, 1), "burst_0p6b_seconds": round(dt, 3)}
+
+
 def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int, prompt_len: int,
-        prefill_tokens: int, points: bool, peaks: dict, clock_sampler=None) -> dict:
+        prefill_tokens: int, points: bool, peaks: dict, clock_sampler=None, burst_raw: dict = None) -> dict:
     """The reference's JSON line as a dict; raises if the reference cannot start."""
     if not os.path.isfile(os.path.join(REF, "serve.py")):
         raise RuntimeError("baseline/_ref/serve.py is not there (copy the reference's serve.py, "
@@ -188,4 +216,13 @@ def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int,
         ms = _prefill(serve, engine, prefill_tokens, V, seed + 2)
         line["prefill"] = {"value": round(prefill_tokens * 1000.0 / ms, 1), "tokens": prefill_tokens,
                            "ms": round(ms, 3), "timed": "wall clock of Engine.generate, max_tokens 1"}
+        if burst_raw is not None:
+            import gc
+            del engine
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                line["points"].update(burst(serve, burst_raw, seed))
+            except Exception as exc:              # noqa: BLE001 - named in the line, the rest still prints
+                line["points"]["burst_0p6b_error"] = f"{type(exc).__name__}: {exc}"[:200]
     return line

@@ -35,6 +35,12 @@ QWEN3_8B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_s
 CONTEXT = 4096
 PROMPT_LEN = 512
 PREFILL_TOKENS = 2048
+# the other two configurations of the baseline: a burst of short requests on a small model (it
+# measures the host path and mixed batches) and a large model at long context
+QWEN3_0P6B = dict(QWEN3_8B, hidden_size=1024, num_hidden_layers=28, num_attention_heads=16,
+                  num_key_value_heads=8, intermediate_size=3072, tie_word_embeddings=True)
+QWEN3_32B = dict(QWEN3_8B, hidden_size=5120, num_hidden_layers=64, num_attention_heads=64,
+                 num_key_value_heads=8, intermediate_size=25600)
 
 
 def load_peaks():
@@ -100,8 +106,8 @@ def prefill_flops(cfg, layers, T):
     return linear + attention
 
 
-def run_decode(llm, batch, steps, warmup, seed, clock=None):
-    """Prefill `batch` prompts of PROMPT_LEN tokens, then time `steps` decode steps."""
+def run_decode(llm, batch, steps, warmup, seed, clock=None, prompt_len=PROMPT_LEN):
+    """Prefill `batch` prompts of `prompt_len` tokens, then time `steps` decode steps."""
     import torch
     from tinyserve_b200.engine.batch import StepEntry
     from tinyserve_b200.kernels import ops
@@ -115,12 +121,21 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None):
     last = []
     for rid in rids:
         runner.manager.begin(rid)
-    per_step = max(1, runner.cfg.max_num_batched_tokens // PROMPT_LEN)
-    for i in range(0, batch, per_step):
-        group = rids[i:i + per_step]
-        prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=gen).tolist() for _ in group]
-        logits = runner.step([StepEntry(r, p, [PROMPT_LEN - 1]) for r, p in zip(group, prompts)])
-        last += logits.argmax(-1).tolist()
+    budget = runner.cfg.max_num_batched_tokens
+    if prompt_len <= budget:
+        per_step = max(1, budget // prompt_len)
+        for i in range(0, batch, per_step):
+            group = rids[i:i + per_step]
+            prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).tolist() for _ in group]
+            logits = runner.step([StepEntry(r, p, [prompt_len - 1]) for r, p in zip(group, prompts)])
+            last += logits.argmax(-1).tolist()
+    else:
+        for rid in rids:                      # a long prompt goes in portions of the budget
+            ids = torch.randint(0, vocab, (prompt_len,), generator=gen).tolist()
+            for at in range(0, prompt_len, budget):
+                part = ids[at:at + budget]
+                logits = runner.step([StepEntry(rid, part, [len(part) - 1] if at + budget >= prompt_len else [])])
+            last += logits.argmax(-1).tolist()
 
     # Tokens stay on the device: the sampler leaves each request's token at its state slot and the
     # next step's embedding lookup reads it there.  The host packs step n+1 while step n runs and
@@ -156,7 +171,7 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None):
     torch.cuda.synchronize()
     clocks = clock.stop() if clock else None
     ms = start.elapsed_time(end) / steps
-    ctx = PROMPT_LEN + warmup + steps / 2
+    ctx = prompt_len + warmup + steps / 2
     for rid in rids:
         runner.manager.free(rid)
     return {"ms": ms, "tok_s": batch * 1000.0 / ms, "ctx": ctx,
@@ -213,6 +228,87 @@ def run_prefill(llm, seed, repeats=3):
     return min(times[1:])
 
 
+def _release(llm):
+    import gc
+    import torch
+    del llm
+    gc.collect()
+    torch.cuda.empty_cache()
+
+
+def run_burst_0p6b(seed, block_size=16):
+    """Qwen3-0.6B shapes: 256 requests arrive at once, prompts of 1 to 2,048 tokens, 128 greedy
+    tokens each, 2,048 tokens a step, through LLM.generate.  Returns tokens per second (prompt +
+    generated, and generated alone) over the whole run, wall clock."""
+    import torch
+    from tinyserve_b200 import LLM, Qwen3Config, SamplingParams
+    llm = LLM(model_config=Qwen3Config.from_dict(QWEN3_0P6B), random_weights=True, dtype="bfloat16",
+              max_model_len=4096, block_size=block_size, max_num_seqs=256, max_num_batched_tokens=2048, seed=seed)
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(1, 2049, (256,), generator=g).tolist()
+    prompts = [torch.randint(0, QWEN3_0P6B["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    params = SamplingParams(temperature=0.0, max_tokens=128, repetition_penalty=1.0, ignore_eos=True)
+    llm.generate(prompts[:8], SamplingParams(temperature=0.0, max_tokens=4, repetition_penalty=1.0, ignore_eos=True))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, params)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    generated = sum(len(o.token_ids) for o in outs)
+    steps = llm.num_steps
+    _release(llm)
+    return {"burst_0p6b_total_tok_s": round((generated + sum(lens)) / dt, 1),
+            "burst_0p6b_gen_tok_s": round(generated / dt, 1), "burst_0p6b_seconds": round(dt, 3),
+            "burst_0p6b_steps": steps}
+
+
+def run_large_32b(seed, block_size=16):
+    """Qwen3-32B shapes at 8,192 context: 16 requests with prompts of 4,096 tokens and 256 greedy
+    tokens each.  Returns prompt tokens per second while the prompts run and decoded tokens per
+    second afterwards (CUDA events around the two phases, through LLM.step)."""
+    import torch
+    from tinyserve_b200 import LLM, Qwen3Config, SamplingParams
+    llm = LLM(model_config=Qwen3Config.from_dict(QWEN3_32B), random_weights=True, dtype="bfloat16",
+              max_model_len=8192, block_size=block_size, max_num_seqs=16, max_num_batched_tokens=4096,
+              num_blocks=16 * (8192 // block_size) // 2 + 64, seed=seed)
+    g = torch.Generator().manual_seed(seed)
+    params = SamplingParams(temperature=0.0, max_tokens=256, repetition_penalty=1.0, ignore_eos=True)
+    for i in range(16):
+        llm.add_request(torch.randint(0, QWEN3_32B["vocab_size"], (4096,), generator=g).tolist(), params, request_id=f"big{i}")
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    torch.cuda.synchronize()
+    marks[0].record()
+    while any(r.num_computed_tokens < r.prompt_len for r in llm.requests.values()) or llm.scheduler.waiting:
+        llm.step()
+    marks[1].record()
+    decoded = 0
+    while llm.has_work():
+        decoded += len(llm.step())
+    marks[2].record()
+    torch.cuda.synchronize()
+    prefill_ms, decode_ms = marks[0].elapsed_time(marks[1]), marks[1].elapsed_time(marks[2])
+    _release(llm)
+    return {"large_32b_prefill_tok_s": round(16 * 4096 * 1000.0 / prefill_ms, 1),
+            "large_32b_decode_b16_tok_s": round(decoded * 1000.0 / decode_ms, 1)}
+
+
+def run_long_context(seed, steps, warmup, block_size=16):
+    """Qwen3-8B shapes, batch 8, decode at 4,096 and at 16,384 tokens of context."""
+    import torch
+    from tinyserve_b200 import LLM, Qwen3Config
+    from tinyserve_b200.engine.batch import StepEntry
+    out = {}
+    llm = LLM(model_config=Qwen3Config.from_dict(QWEN3_8B), random_weights=True, dtype="bfloat16",
+              max_model_len=16384 + 256, block_size=block_size, max_num_seqs=8, max_num_batched_tokens=4096,
+              num_blocks=8 * (16384 + 256) // block_size + 16, use_cuda_graphs=False, seed=seed)
+    llm.runner.capture_decode_graphs([8])
+    for name, ctx in (("decode_b8_ctx4k_tok_s", 4096), ("decode_b8_ctx16k_tok_s", 16384)):
+        r = run_decode(llm, 8, steps, warmup, seed + ctx, prompt_len=ctx - warmup - steps)
+        out[name] = round(r["tok_s"], 1)
+    _release(llm)
+    return out
+
+
 def reference_main(a) -> int:
     """``--impl reference``: priyammaz/tinyserve, unmodified, from baseline/_ref, through its own
     Engine (see baseline/reference_arm.py).  If it cannot start here, the line says why."""
@@ -224,7 +320,8 @@ def reference_main(a) -> int:
         import reference_arm
         raw = dict(QWEN3_8B, num_hidden_layers=a.layers)
         line = reference_arm.run(raw, a.batch, a.steps, max(a.warmup, 3), a.seed, CONTEXT, PROMPT_LEN,
-                                 PREFILL_TOKENS, not a.no_points, load_peaks(), ClockSampler())
+                                 PREFILL_TOKENS, not a.no_points, load_peaks(), ClockSampler(),
+                                 burst_raw=None if a.no_workloads else QWEN3_0P6B)
     except BaseException as exc:                      # noqa: BLE001 - the reason goes into the line
         if isinstance(exc, KeyboardInterrupt):
             raise
@@ -248,6 +345,8 @@ def main() -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the 0.6B burst, the 32B run and the long-context decode")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_main(a)
@@ -278,6 +377,15 @@ def main() -> int:
         flops = prefill_flops(raw, a.layers, PREFILL_TOKENS)
         prefill = {"value": round(PREFILL_TOKENS * 1000.0 / ms, 1), "tokens": PREFILL_TOKENS,
                    "ms": round(ms, 3), "frac": round(flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)}
+    if not a.no_points and not a.no_workloads and a.layers == QWEN3_8B["num_hidden_layers"]:
+        _release(llm)
+        llm = None
+        for fn, args in ((run_burst_0p6b, (a.seed, a.block_size)), (run_large_32b, (a.seed, a.block_size)),
+                         (run_long_context, (a.seed, min(a.steps, 32), warmup, a.block_size))):
+            try:
+                points.update(fn(*args))
+            except Exception as exc:                  # noqa: BLE001 - a workload that fails is named, the line still prints
+                points[fn.__name__ + "_error"] = f"{type(exc).__name__}: {exc}"[:200]
     nbytes = decode_bytes(raw, a.layers, a.batch, main_run["ctx"])
     achieved = nbytes / (main_run["ms"] * 1e-3) / 1e9
     line = {
