@@ -83,7 +83,7 @@ def write_model_folder(raw: dict, folder: str, seed: int) -> None:
             os.path.join(folder, f"model-layer{i:03d}.safetensors"))
 
 
-def _decode(serve, engine, batch, prompt_len, steps, warmup, vocab, seed):
+def _decode(serve, engine, batch, prompt_len, steps, warmup, vocab, seed, clock=None):
     import torch
     gen = torch.Generator().manual_seed(seed)
     params = serve.SamplingParams(temperature=0.0, max_tokens=warmup + steps + 8, repetition_penalty=1.0,
@@ -100,6 +100,8 @@ def _decode(serve, engine, batch, prompt_len, steps, warmup, vocab, seed):
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    if clock:
+        clock.window(True)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     produced = 0
     t0 = time.perf_counter()
@@ -109,6 +111,8 @@ def _decode(serve, engine, batch, prompt_len, steps, warmup, vocab, seed):
     end.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
+    if clock:
+        clock.window(False)
     ms = start.elapsed_time(end) / steps
     for r in rids:
         engine.abort(r)
@@ -170,6 +174,8 @@ def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int,
         "the reference arm must not load tinyserve_b200"
     if REF not in sys.path:
         sys.path.insert(0, REF)
+    if clock_sampler:
+        clock_sampler.start()
     import torch
     h, L, V = raw["hidden_size"], raw["num_hidden_layers"], raw["vocab_size"]
     H, Hkv, D, I = (raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"],
@@ -187,9 +193,7 @@ def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int,
         engine = serve.Engine(cfg)
     finally:
         shutil.rmtree(folder, ignore_errors=True)
-    if clock_sampler:
-        clock_sampler.start()
-    main = _decode(serve, engine, batch, prompt_len, steps, warmup, V, seed)
+    main = _decode(serve, engine, batch, prompt_len, steps, warmup, V, seed, clock_sampler)
     clocks = clock_sampler.stop() if clock_sampler else None
     line = {
         "metric": "decode tok/s (Qwen3-8B shapes, random weights)", "value": round(main["tok_s"], 1),

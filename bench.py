@@ -53,20 +53,25 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  It runs from ``start()`` on (the
+    tool needs a moment to come up, and the timed region may be shorter than that); ``window()``
+    marks the timed region, and ``stop()`` reports the samples that fall into it (or, if the
+    region was shorter than a sampling period, the samples nearest to it)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
-        self.samples, self.proc = [], None
+        self.samples, self.proc, self.t0, self.t1 = [], None, None, None
 
     def start(self):
+        if self.proc is not None:
+            return
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -76,17 +81,29 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.monotonic(), parts))
+
+    def window(self, begin: bool):
+        if begin:
+            self.t0 = time.monotonic()
+        else:
+            self.t1 = time.monotonic()
 
     def stop(self):
         if self.proc is not None:
+            time.sleep(0.12)                      # one more sample after the region
             self.proc.terminate()
-        mhz = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        t0, t1 = self.t0 or 0.0, self.t1 or float("inf")
+        inside = [s for t, s in self.samples if t0 <= t <= t1]
+        if not inside and self.samples:
+            mid = (t0 + min(t1, t0 + 3600)) / 2
+            inside = [s for _, s in sorted(self.samples, key=lambda ts: abs(ts[0] - mid))[:3]]
+        mhz = [int(s[0]) for s in inside if s[0].isdigit()]
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in inside)]
+        mx = [int(s[1]) for s in inside if s[1].isdigit()]
         return {"sm_mhz": int(statistics.median(mhz)) if mhz else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons}
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(inside)}
 
 
 def decode_bytes(cfg, layers, batch, ctx):
@@ -161,7 +178,7 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None, prompt_len=PROMPT_LE
         one_step()
     torch.cuda.synchronize()
     if clock:
-        clock.start()
+        clock.window(True)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = ops.launch_count()
     start.record()
@@ -169,6 +186,8 @@ def run_decode(llm, batch, steps, warmup, seed, clock=None, prompt_len=PROMPT_LE
         one_step()
     end.record()
     torch.cuda.synchronize()
+    if clock:
+        clock.window(False)
     clocks = clock.stop() if clock else None
     ms = start.elapsed_time(end) / steps
     ctx = prompt_len + warmup + steps / 2
@@ -270,7 +289,7 @@ def run_large_32b(seed, block_size=16):
     from tinyserve_b200 import LLM, Qwen3Config, SamplingParams
     llm = LLM(model_config=Qwen3Config.from_dict(QWEN3_32B), random_weights=True, dtype="bfloat16",
               max_model_len=8192, block_size=block_size, max_num_seqs=16, max_num_batched_tokens=4096,
-              num_blocks=16 * (8192 // block_size) // 2 + 64, seed=seed)
+              gpu_memory_utilization=0.9, seed=seed)        # the rest of the memory goes to the cache
     g = torch.Generator().manual_seed(seed)
     params = SamplingParams(temperature=0.0, max_tokens=256, repetition_penalty=1.0, ignore_eos=True)
     for i in range(16):
@@ -343,7 +362,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN3_8B["num_hidden_layers"])
     ap.add_argument("--impl", default="tinyserve_b200")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--block-size", type=int, default=64, help="tokens per cache page")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 0.6B burst, the 32B run and the long-context decode")
@@ -353,6 +372,8 @@ def main() -> int:
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
+    sampler = ClockSampler()
+    sampler.start()                   # early: nvidia-smi takes longer to come up than a short timed region lasts
     import torch
     from tinyserve_b200 import LLM, Qwen3Config
     from tinyserve_b200.kernels import ops
@@ -363,10 +384,11 @@ def main() -> int:
     sizes = sorted({1, a.batch, 64}) if not a.no_points else [a.batch]
     llm = LLM(model_config=config, random_weights=True, dtype="bfloat16", max_model_len=CONTEXT,
               block_size=a.block_size, max_num_seqs=max(sizes), max_num_batched_tokens=PREFILL_TOKENS,
-              num_blocks=max(sizes) * (CONTEXT // 16) // 2 + 256, use_cuda_graphs=False, seed=a.seed)
+              num_blocks=max(sizes) * (CONTEXT // a.block_size) // 2 + 4096 // a.block_size, use_cuda_graphs=False,
+              seed=a.seed)
     llm.runner.capture_decode_graphs(sizes)
 
-    main_run = run_decode(llm, a.batch, a.steps, warmup, a.seed, ClockSampler())
+    main_run = run_decode(llm, a.batch, a.steps, warmup, a.seed, sampler)
     e2e = run_e2e(llm, a.batch, a.steps, warmup, a.seed)
     points, prefill = {}, None
     if not a.no_points:
@@ -380,7 +402,7 @@ def main() -> int:
     if not a.no_points and not a.no_workloads and a.layers == QWEN3_8B["num_hidden_layers"]:
         _release(llm)
         llm = None
-        for fn, args in ((run_burst_0p6b, (a.seed, a.block_size)), (run_large_32b, (a.seed, a.block_size)),
+        for fn, args in ((run_burst_0p6b, (a.seed, a.block_size)), (run_large_32b, (a.seed, 16)),
                          (run_long_context, (a.seed, min(a.steps, 32), warmup, a.block_size))):
             try:
                 points.update(fn(*args))

@@ -40,7 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--no-cuda-graphs", action="store_true")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
-    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--block-size", type=int, default=0, help="tokens per cache page (0: 64 from 2,048 tokens of context on, else 16)")
     ap.add_argument("--num-blocks", type=int, default=0, help="cache pages per group (0: from memory)")
     # random-weights
     ap.add_argument("--config", help="random-weights: a config.json to make weights for")
