@@ -221,7 +221,7 @@ def run_e2e(llm, batch, steps, warmup, seed):
     dt = time.perf_counter() - t0
     for rid in list(llm.requests):
         llm.abort(rid)
-    h2d = llm.runner._dev.numel() * 4
+    h2d = llm.runner.last_upload_bytes
     return {"value": produced / dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": batch * 4}
 

@@ -139,3 +139,31 @@ def test_random_orders_keep_the_invariants(seed):
         m.free(rid)
     m.check_invariants()
     assert all(p.num_free == p.num_usable for p in m.pools)
+
+
+def test_block_table_changes_travel_once_and_again_if_not_acknowledged():
+    """The device keeps every request's block-table row; the manager says what that copy lacks."""
+    m = CacheManager([GroupSpec("full"), GroupSpec("window", 8)], 32, 4, 4)
+    m.begin("a")
+    assert m.allocate("a", 10)                          # three pages in both groups
+    changes, receipt = m.table_updates("a", 0)
+    assert [i for i, _ in changes] == [0, 1, 2] and [p for _, p in changes] == m.block_table("a", 0)
+    again, _ = m.table_updates("a", 0)
+    assert again == changes, "a packed step that is never launched sends its entries again"
+    m.table_synced(receipt)
+    assert m.table_updates("a", 0)[0] == []
+    m.commit("a", 10)
+    assert m.allocate("a", 3)                           # one more page
+    changes, receipt = m.table_updates("a", 0)
+    assert changes == [(3, m.block_table("a", 0)[3])]
+    m.table_synced(receipt)
+    # the window group gives pages back behind the window: those entries travel as zeros
+    w_changes, w_receipt = m.table_updates("a", 1)
+    m.table_synced(w_receipt)
+    m.commit("a", 3)                                    # 13 computed: keys below 13 - 8 + 1 = 6 are gone: page 0
+    released, receipt = m.table_updates("a", 1)
+    assert (0, 0) in released and m.block_table("a", 1)[0] == 0
+    m.table_synced(receipt)
+    assert m.table_updates("a", 1)[0] == []
+    m.free("a")
+    m.check_invariants()

@@ -270,11 +270,16 @@ def test_host_index_check_refuses_a_corrupted_step(tmp_path):
     h = runner._hosts_np[0]
     for name, at, value, what in (("token_ids", 1, 256, "token id"), ("positions", 0, 64, "position"),
                                   ("logit_rows", 0, 3, "wanted row"), ("slot_mapping0", 2, 7 * 16, "cache slot"),
-                                  ("block_table0", 0, 7, "page number"), ("state_slots", 0, 2, "state slot"),
+                                  ("pairs", 1, 7, "page number"), ("pairs", 0, 10 ** 6, "block-table change"),
+                                  ("state_slots", 0, 3, "state slot"),
                                   ("cu_q", 1, 9, "query offsets")):
         ctx = runner._pack([StepEntry("a", [4, 5, 6], [2])], 0)
         runner._check_host(ctx, 0)
-        runner._seg(h, name)[at] = value
+        if name == "pairs":
+            h[runner._offsets["meta"][0]] = 1               # one block-table change: (index, page)
+            h[runner._pairs_at + 1 - at], h[runner._pairs_at + at] = 1, value
+        else:
+            runner._seg(h, name)[at] = value
         with pytest.raises(ValueError, match=what):
             runner._check_host(ctx, 0)
     runner.manager.free("a")

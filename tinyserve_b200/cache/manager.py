@@ -65,6 +65,8 @@ class GroupSpec:
 class _RequestPages:
     pages: list = field(default_factory=list)   # logical page -> physical page (0 = released)
     first_live: int = 0                          # logical pages below this are released
+    synced: int = 0                              # leading entries that the device's copy of the row holds
+    dirty: list = field(default_factory=list)    # entries below ``synced`` that changed since (released pages)
 
 
 class SlotPool:
@@ -178,6 +180,8 @@ class CacheManager:
             if page:
                 self.pools[g].give_back(page, rid)
                 rp.pages[logical] = 0
+                if logical < rp.synced:
+                    rp.dirty.append(logical)
         rp.first_live = max(rp.first_live, first)
 
     def commit(self, rid, num_new: int) -> None:
@@ -193,6 +197,21 @@ class CacheManager:
 
     def block_table(self, rid, g: int) -> list:
         return self.requests[rid].groups[g].pages
+
+    def table_updates(self, rid, g: int):
+        """What the device's copy of this request's block-table row lacks: ([(index, page), ...],
+        receipt).  Nothing is marked as sent until ``table_synced(receipt)``: a packed step that is
+        never launched leaves the entries to be sent again."""
+        rp = self.requests[rid].groups[g]
+        changes = [(i, rp.pages[i]) for i in rp.dirty]
+        changes += [(i, rp.pages[i]) for i in range(rp.synced, len(rp.pages))]
+        return changes, (rp, len(rp.pages), len(rp.dirty))
+
+    @staticmethod
+    def table_synced(receipt) -> None:
+        rp, length, num_dirty = receipt
+        rp.synced = max(rp.synced, length)
+        del rp.dirty[:num_dirty]
 
     def slot_of_position(self, rid, g: int, pos: int) -> int:
         page = self.requests[rid].groups[g].pages[pos // self.page_size]

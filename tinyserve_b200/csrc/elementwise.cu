@@ -43,6 +43,52 @@ TS_EXPORT int ts_embed_lookup(int dtype, const void* table, const int* ids, floa
   return 0;
 }
 
+// ------------------------------------------------------------------ block tables on the device
+// Every state slot keeps its request's block-table row on the device ("resident", [groups][slots +
+// 1][max_blocks]); a step uploads only the entries that changed (pairs of flat index and page) and
+// these two kernels bring the rows of the step's requests into the [groups][requests][max_blocks]
+// tables that the attention kernels index by request.  The number of pairs is read from device
+// memory, so that a captured graph serves any step.
+__global__ void block_table_scatter_kernel(int* __restrict__ resident, long long resident_size,
+                                           const int* __restrict__ pairs, const int* __restrict__ num_pairs,
+                                           int capacity) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = min(*num_pairs, capacity);
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int at = pairs[2 * i];
+    if (at >= 0 && at < resident_size) resident[at] = pairs[2 * i + 1];
+  }
+}
+
+__global__ void block_table_gather_kernel(const int* __restrict__ resident, int* __restrict__ step_tables,
+                                          const int* __restrict__ state_slots, int num_slots, int max_requests,
+                                          int max_blocks) {
+  pdl_trigger();
+  pdl_wait();
+  const int b = blockIdx.x, g = blockIdx.y;
+  int slot = state_slots[b];
+  if (slot < 0 || slot > num_slots) slot = num_slots;          // the spare row: all null pages
+  const int* src = resident + ((size_t)g * (num_slots + 1) + slot) * max_blocks;
+  int* dst = step_tables + ((size_t)g * max_requests + b) * max_blocks;
+  for (int i = threadIdx.x; i < max_blocks; i += blockDim.x) dst[i] = src[i];
+}
+
+// resident [groups][num_slots + 1][max_blocks]; pairs [capacity][2] and num_pairs [1] on the device;
+// step_tables [groups][max_requests][max_blocks]; state_slots [num_requests].
+TS_EXPORT int ts_block_tables_step(int* resident, const int* pairs, const int* num_pairs, int capacity,
+                                   int* step_tables, const int* state_slots, int num_requests, int max_requests,
+                                   int num_slots, int max_blocks, int groups, cudaStream_t stream) {
+  TS_REQUIRE(num_requests > 0 && num_requests <= max_requests && groups > 0 && max_blocks > 0 && capacity >= 0,
+             "block_tables_step: empty step");
+  const long long size = (long long)groups * (num_slots + 1) * max_blocks;
+  TS_LAUNCH("block_table_scatter", block_table_scatter_kernel, 8, 256, 0, stream, resident, size, pairs, num_pairs,
+            capacity);
+  TS_LAUNCH("block_table_gather", block_table_gather_kernel, dim3(num_requests, groups), 128, 0, stream,
+            (const int*)resident, step_tables, state_slots, num_slots, max_requests, max_blocks);
+  return 0;
+}
+
 // ------------------------------------------------------------------ index check of a step
 // The debug pass that stands where a memory checker would: before a step's kernels run, one small
 // kernel looks at every index the step brings.  An index outside its buffer is replaced by a

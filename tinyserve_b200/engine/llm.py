@@ -46,6 +46,25 @@ class Output:
     was_chunked_prefill: bool = False
 
 
+@dataclass
+class _Packed:
+    """A step that is scheduled and packed on the host, not launched yet."""
+
+    batch: list          # ScheduledRequest, in batch order
+    wants: list          # per request: the step reaches its last known token, so a token is sampled
+    prepared: object
+
+
+@dataclass
+class _Sampled:
+    """A step whose tokens were sampled on the device and are on their way to the host."""
+
+    rows: list           # (row of the logits, request, place of the token in request.token_ids)
+    host: object         # pinned int32 tensor that receives the tokens
+    arrived: object      # event after the copy
+    raw: object          # unmodified logits, if a request wants log-probabilities
+
+
 def _stop_ids(model_dir, tokenizer) -> set:
     """EOS of the tokenizer plus generation_config.json's eos_token_id (serve.py:2392-2403)."""
     ids = set()
@@ -76,7 +95,7 @@ class LLM:
         self.stop_ids = _stop_ids(model, self.tokenizer)
         self.scheduler = Scheduler(self.runner.manager, self.cfg.max_num_seqs,
                                    self.cfg.max_num_batched_tokens)
-        self.sampler = Sampler(self.cfg.seed, self.runner.device)
+        self.sampler = Sampler(self.cfg.seed, self.runner.device, self.cfg.max_num_seqs)
         if self.cfg.use_cuda_graphs:
             self.runner.capture_decode_graphs()
         self.requests: dict = {}
@@ -93,8 +112,8 @@ class LLM:
         self._slot_devs = [torch.empty(self.cfg.max_num_seqs, dtype=torch.int32, device=self.runner.device)
                            for _ in range(2)]
         self._flip = 0
-        self._next = None          # (batch, wants, prepared step) scheduled and packed, not launched
-        self._in_flight = None     # (live rows, host buffer, event, logits) sampled, not read back
+        self._next = None          # _Packed: scheduled and packed, not launched
+        self._in_flight = None     # _Sampled: sampled on the device, not read back
         self._spare_slot = self.cfg.max_num_seqs
         if verbose:
             print(f"[tinyserve_b200] engine ready in {time.time() - t0:.1f}s", flush=True)
@@ -132,9 +151,9 @@ class LLM:
             self.scheduler.finish(req, "abort")
             self.detok.pop(request_id, None)
         # a packed step, or tokens on their way, that only concern ended requests are dropped
-        if self._next is not None and all(s.req.finished for s in self._next[0]):
+        if self._next is not None and all(s.req.finished for s in self._next.batch):
             self._next = None
-        if self._in_flight is not None and all(r.request_id not in self.requests for _, r, _ in self._in_flight[0]):
+        if self._in_flight is not None and all(r.request_id not in self.requests for _, r, _ in self._in_flight.rows):
             self._in_flight = None
 
     def has_work(self) -> bool:
@@ -143,88 +162,97 @@ class LLM:
     # ------------------------------------------------------------------ one step
     def step(self) -> list:
         """One engine step; returns the outputs of the requests that got a token."""
-        return self._step_async() if self.async_scheduling else self._step_sync()
+        return self._step_pipelined() if self.async_scheduling else self._step_sync()
 
-    # ------------------------------------------------------------------ the host runs one step ahead
-    def _entries(self, batch):
+    def _plan(self):
+        """Schedule the next step and pack it on the host.  Returns a _Packed or None."""
+        batch = self.scheduler.schedule()
+        if not batch:
+            return None
         entries, wants = [], []
         for s in batch:
             req = s.req
-            tokens = req.token_ids[s.num_computed:s.num_computed + s.num_new]
-            want = s.completes_prompt
-            if not want:
+            wanted = s.completes_prompt                    # the step reaches the request's last known token
+            if not wanted:
                 req.was_chunked_prefill = True
             if s.num_computed < req.prompt_len:
                 self.num_prompt_tokens_run += min(s.num_new, req.prompt_len - s.num_computed)
-            entries.append(StepEntry(req.request_id, tokens, [s.num_new - 1] if want else []))
-            wants.append(want)
-        return entries, wants
+            entries.append(StepEntry(req.request_id, req.token_ids[s.num_computed:s.num_computed + s.num_new],
+                                     [s.num_new - 1] if wanted else []))
+            wants.append(wanted)
+        return _Packed(batch, wants, self.runner.prepare(entries))
 
+    def _over_length(self, req: Request) -> bool:
+        return len(req.output_ids) >= req.params.max_tokens or req.num_tokens >= self.cfg.max_model_len
+
+    # The host runs one step ahead of the device, as tinyserve's engine does (serve.py:2509-2601): a
+    # call launches the step that the call before packed, reads the tokens of the step before that,
+    # samples the launched step on the device and packs the next one, with PENDING in the place of
+    # every token that is still on the device.
     @torch.inference_mode()
-    def _step_async(self) -> list:
-        """The four stages of serve.py:2509-2601: launch the step packed last call; finish the
-        step before it (its tokens have arrived or are waited for); sample this step's logits and
-        give its requests placeholders; schedule and pack the next step while the device works."""
-        cur, self._next = self._next, None
+    def _step_pipelined(self) -> list:
+        packed, self._next = self._next, None
         logits = None
-        if cur is not None:
-            logits = self.runner.launch(cur[2])
+        if packed is not None:
+            logits = self.runner.launch(packed.prepared)
             self.num_steps += 1
-        outputs = []
-        if self._in_flight is not None:
-            outputs = self._finish_async(*self._in_flight)
-            self._in_flight = None
+        outputs = self._collect(self._in_flight) if self._in_flight is not None else []
+        self._in_flight = None
         outputs += [self._output(r) for r in self._take_dropped()]
-        if cur is not None and logits is not None:
-            batch, wants, prep = cur
-            rows = [s.req for s, w in zip(batch, wants) if w]          # one per row of logits
-            n = len(rows)
-            if n == len(batch):
-                slots = self.runner.state_slots_on_device(n)
-            else:
-                manager = self.runner.manager
-                staged = self._slot_bufs[self._flip]
-                staged[:n] = torch.tensor([manager.slot(r.request_id) if manager.is_live(r.request_id)
-                                           else self._spare_slot for r in rows], dtype=torch.int32)
-                slots = self._slot_devs[self._flip][:n]
-                slots.copy_(staged[:n], non_blocking=True)
-            raw = logits.clone() if any(r.params.return_logprobs for r in rows) else None
-            tokens_dev = self.sampler(logits, rows, slot_tokens=self.runner.slot_tokens, slots=slots)
-            host = self._token_bufs[self._flip]
-            self._flip ^= 1
-            host[:n].copy_(tokens_dev, non_blocking=True)
-            event = torch.cuda.Event()
-            event.record()
-            live = []
-            for i, req in enumerate(rows):
-                if req.finished:
-                    continue           # ended (stop, abort) while this step was already packed
-                forced = req.params.forced_token_ids
-                req.token_ids.append(int(forced[len(req.output_ids)]) if forced is not None else PENDING)
-                self.num_generated_tokens += 1
-                if len(req.output_ids) >= req.params.max_tokens or req.num_tokens >= self.cfg.max_model_len:
-                    self.scheduler.finish(req, "length")
-                live.append((i, req, len(req.token_ids) - 1))
-            self._in_flight = (live, host, event, raw)
-        batch = self.scheduler.schedule()
-        if batch:
-            entries, wants = self._entries(batch)
-            self._next = (batch, wants, self.runner.prepare(entries))
+        if logits is not None:
+            self._in_flight = self._sample_on_device(packed, logits)
+        self._next = self._plan()
         return outputs
 
-    def _finish_async(self, live, host, event, raw) -> list:
-        event.synchronize()
+    def _sample_on_device(self, packed, logits):
+        """Sample the launched step; its tokens stay on the device (each at its request's state
+        slot, where the next step's embedding lookup finds it) and start their way to the host."""
+        rows = [s.req for s, wanted in zip(packed.batch, packed.wants) if wanted]       # one per row of logits
+        n = len(rows)
+        if n == len(packed.batch):
+            slots = self.runner.state_slots_on_device(n)
+        else:
+            manager = self.runner.manager
+            staged = self._slot_bufs[self._flip]
+            staged[:n] = torch.tensor([manager.slot(r.request_id) if manager.is_live(r.request_id)
+                                       else self._spare_slot for r in rows], dtype=torch.int32)
+            slots = self._slot_devs[self._flip][:n]
+            slots.copy_(staged[:n], non_blocking=True)
+        raw = logits.clone() if any(r.params.return_logprobs for r in rows) else None
+        tokens_dev = self.sampler(logits, rows, slot_tokens=self.runner.slot_tokens, slots=slots)
+        host = self._token_bufs[self._flip]
+        self._flip ^= 1
+        host[:n].copy_(tokens_dev, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record()
+        waiting_for = []
+        for row, req in enumerate(rows):
+            if req.finished:
+                continue                   # ended (stop string, abort) after this step was packed
+            forced = req.params.forced_token_ids
+            req.token_ids.append(int(forced[len(req.output_ids)]) if forced is not None else PENDING)
+            self.num_generated_tokens += 1
+            if self._over_length(req):
+                # its last token is on its way; nothing more is scheduled for it
+                self.scheduler.finish(req, "length")
+            waiting_for.append((row, req, len(req.token_ids) - 1))
+        return _Sampled(waiting_for, host, arrived, raw)
+
+    def _collect(self, flight) -> list:
+        """The tokens of a sampled step have arrived (or are waited for): fill them in, look for
+        stop tokens, make the outputs."""
+        flight.arrived.synchronize()
         self.runner.raise_on_device_error()
-        tokens = host.tolist()
+        tokens = flight.host.tolist()
         outputs = []
-        for i, req, at in live:
+        for row, req, at in flight.rows:
             if req.request_id not in self.requests:
                 continue               # aborted meanwhile
             if req.token_ids[at] == PENDING:
-                req.token_ids[at] = tokens[i]
+                req.token_ids[at] = tokens[row]
             tok = req.token_ids[at]
             if req.params.return_logprobs:
-                req.logprobs.append(raw[i].log_softmax(-1).cpu())
+                req.logprobs.append(flight.raw[row].log_softmax(-1).cpu())
             if tok in self.stop_ids and not req.params.ignore_eos:
                 if req.finished:
                     req.finish_reason = "stop"
@@ -236,56 +264,40 @@ class LLM:
     # ------------------------------------------------------------------ one step at a time
     @torch.inference_mode()
     def _step_sync(self) -> list:
-        batch = self.scheduler.schedule()
-        outputs = [self._output(r) for r in self._take_dropped()]
-        if not batch:
+        outputs = []
+        packed = self._plan()
+        outputs += [self._output(r) for r in self._take_dropped()]
+        if packed is None:
             return outputs
-        entries, live = [], []
-        for s in batch:
-            req = s.req
-            tokens = req.token_ids[s.num_computed:s.num_computed + s.num_new]
-            want = [s.num_new - 1] if s.completes_prompt else []
-            if not s.completes_prompt:
-                req.was_chunked_prefill = True
-            else:
-                live.append(req)
-            if s.num_computed < req.prompt_len:
-                self.num_prompt_tokens_run += min(s.num_new, req.prompt_len - s.num_computed)
-            entries.append(StepEntry(req.request_id, tokens, want))
-        logits = self.runner.step(entries)
+        logits = self.runner.launch(packed.prepared)
         self.num_steps += 1
-        if not live:
+        rows = [s.req for s, wanted in zip(packed.batch, packed.wants) if wanted]
+        if not rows:
             return outputs
-        forced = [r for r in live if r.params.forced_token_ids is not None]
-        raw = logits.clone() if any(r.params.return_logprobs for r in live) else None
-        tokens_dev = self.sampler(logits, live)
-        n = len(live)
+        raw = logits.clone() if any(r.params.return_logprobs for r in rows) else None
+        tokens_dev = self.sampler(logits, rows)
+        n = len(rows)
         self._tokens_host[:n].copy_(tokens_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         self.runner.raise_on_device_error()
         tokens = self._tokens_host[:n].tolist()
         self.num_generated_tokens += n
-        for i, req in enumerate(live):
-            tok = tokens[i]
-            if forced and req.params.forced_token_ids is not None:
-                tok = int(req.params.forced_token_ids[len(req.output_ids)])
+        for row, req in enumerate(rows):
+            forced = req.params.forced_token_ids
+            tok = int(forced[len(req.output_ids)]) if forced is not None else tokens[row]
             req.token_ids.append(tok)
             if req.params.return_logprobs:
-                req.logprobs.append(raw[i].log_softmax(-1).cpu())
-            outputs.append(self._after_token(req, tok))
+                req.logprobs.append(raw[row].log_softmax(-1).cpu())
+            if tok in self.stop_ids and not req.params.ignore_eos:
+                self.scheduler.finish(req, "stop")
+            elif self._over_length(req):
+                self.scheduler.finish(req, "length")
+            outputs.append(self._output(req))
         return outputs
 
     def _take_dropped(self):
         dropped, self.scheduler.dropped = self.scheduler.dropped, []
         return dropped
-
-    def _after_token(self, req: Request, tok: int) -> Output:
-        p = req.params
-        if tok in self.stop_ids and not p.ignore_eos:
-            self.scheduler.finish(req, "stop")
-        elif len(req.output_ids) >= p.max_tokens or req.num_tokens >= self.cfg.max_model_len:
-            self.scheduler.finish(req, "length")
-        return self._output(req)
 
     def _output(self, req: Request) -> Output:
         d = self.detok.get(req.request_id)

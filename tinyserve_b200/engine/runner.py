@@ -11,7 +11,9 @@ positions, slots, query starts, lengths and the block table per request
 (serve.py:1853-1875), ``_upload`` copies them into persistent buffers
 (serve.py:1910-1915) and decode-only batches replay captured graphs
 (serve.py:1969-2053).  It always returns the last row of every request
-(serve.py:1875, 2077); here the caller says which rows it wants."""
+(serve.py:1875, 2077); here the caller says which rows it wants.  Here every state slot keeps
+its request's block-table row on the device and a step uploads only the entries that changed;
+the attention work lists of a step with prompt portions travel in the same copy."""
 from __future__ import annotations
 
 import numpy as np
@@ -70,6 +72,7 @@ class ModelRunner:
         self._make_buffers()
         self.graphs: dict = {}
         self.kernel_launches = 0
+        self.last_upload_bytes = 0
         if verbose:
             print(f"[tinyserve_b200] weights {self.weight_bytes / 2**30:.2f} GiB, "
                   f"{self.num_pages - 1} pages of {self.page_size} tokens per cache group "
@@ -107,26 +110,41 @@ class ModelRunner:
         return 4 * widest * 4
 
     def _make_buffers(self):
+        """One staging layout for everything a step uploads: a header, the per-request and per-token
+        arrays, the attention work lists of the tile sizes the mixers announce, and at the end the
+        block-table changes (pairs of flat index and page), of which only the used part is copied."""
         cfg = self.cfg
         N, S = cfg.max_num_batched_tokens, cfg.max_num_seqs
         G = len(self.model.cache_groups)
-        sizes = [("token_ids", N), ("positions", N), ("logit_rows", N), ("cu_q", S + 1),
-                 ("kv_lens", S), ("state_slots", S), ("fresh", S)]
+        self._tile_sizes = sorted({q for block in self.model.blocks
+                                   for q in [block.mixer.work_tile_queries(self.dtype, self.page_size)] if q > 0})
+        sizes = [("meta", 4), ("cu_q", S + 1), ("kv_lens", S), ("state_slots", S), ("fresh", S),
+                 ("token_ids", N), ("positions", N), ("logit_rows", N)]
         for g in range(G):
             sizes.append((f"slot_mapping{g}", N))
-        for g in range(G):
-            sizes.append((f"block_table{g}", S * self.max_blocks))
+        for q in self._tile_sizes:
+            sizes += [(f"tile_req{q}", N // q + S), (f"tile_q0{q}", N // q + S)]
+        if self._tile_sizes:
+            sizes += [("dec_req", S), ("dec_tok", S)]
         self._offsets, total = {}, 0
         for name, n in sizes:
             self._offsets[name] = (total, n)
             total += (n + 3) // 4 * 4
+        self._pairs_at = total
+        self._pairs_capacity = max(1, G * S * self.max_blocks)
+        total += 2 * self._pairs_capacity
         # two staging buffers: a step is packed while the copy of the one before may be pending
         self._hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() if self.device.type == "cuda"
                        else torch.zeros(total, dtype=torch.int32) for _ in range(2)]
         self._hosts_np = [h.numpy() for h in self._hosts]
+        self._used = [total, total]      # words of each staging buffer that the packed step uses
         self._copied = [None, None]      # event after the last copy out of each staging buffer
         self._next_buf = 0
         self._dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        # block tables: a resident row per state slot (and a spare row of null pages), the rows of the
+        # step's requests gathered from them
+        self._resident_tables = torch.zeros(max(G, 1), S + 1, self.max_blocks, dtype=torch.int32, device=self.device)
+        self._step_tables = torch.zeros(max(G, 1), S, self.max_blocks, dtype=torch.int32, device=self.device)
         # last sampled token of every state slot (one spare entry for rows nobody waits for)
         self.slot_tokens = torch.zeros(S + 1, dtype=torch.int32, device=self.device)
 
@@ -151,9 +169,10 @@ class ModelRunner:
         seg = lambda name, n=None: self._seg(h, name, n)
         ids, pos, rows = seg("token_ids"), seg("positions"), seg("logit_rows")
         cu_q, kv_lens, slots, fresh = seg("cu_q"), seg("kv_lens"), seg("state_slots"), seg("fresh")
-        G = len(self.model.cache_groups)
+        G, S, MB = len(self.model.cache_groups), cfg.max_num_seqs, self.max_blocks
         slot_maps = [seg(f"slot_mapping{g}") for g in range(G)]
-        tables = [seg(f"block_table{g}").reshape(cfg.max_num_seqs, self.max_blocks) for g in range(G)]
+        pairs = h[self._pairs_at:]
+        num_pairs, receipts = 0, []
         t = w = 0
         max_q = max_kv = 0
         cu_q[0] = 0
@@ -166,29 +185,33 @@ class ModelRunner:
                 raise ValueError(f"request {e.rid!r} would hold {start + n} tokens, max_model_len is {cfg.max_model_len}")
             if any(mgr.pages_needed(e.rid, n)) and not mgr.allocate(e.rid, n):
                 raise CacheError(f"no cache pages left for request {e.rid!r}")
+            slot = mgr.slot(e.rid)
+            for g in range(G):
+                # only what the device's copy of the request's row lacks travels
+                changes, receipt = mgr.table_updates(e.rid, g)
+                if changes:
+                    base = (g * (S + 1) + slot) * MB
+                    for index, page in changes:
+                        pairs[2 * num_pairs] = base + index
+                        pairs[2 * num_pairs + 1] = page
+                        num_pairs += 1
+                    receipts.append(receipt)
             if n == 1:
                 # a decoded token: scalars, no temporaries
                 tok = e.tokens[0]
-                ids[t] = tok if tok >= 0 else -1 - mgr.slot(e.rid)     # pending: read on the device
+                ids[t] = tok if tok >= 0 else -1 - slot                # pending: read on the device
                 pos[t] = start
                 for g in range(G):
-                    pages = mgr.block_table(e.rid, g)
-                    row = tables[g][b]
-                    row[:len(pages)] = pages
-                    row[len(pages):] = 0
-                    slot_maps[g][t] = pages[start // ps] * ps + start % ps
+                    slot_maps[g][t] = mgr.block_table(e.rid, g)[start // ps] * ps + start % ps
             else:
                 if min(e.tokens) < 0:
                     raise ValueError(f"request {e.rid!r}: only a single decoded token may be pending")
                 ids[t:t + n] = e.tokens
                 pos[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+                p = np.arange(start, start + n)
                 for g in range(G):
-                    pages = mgr.block_table(e.rid, g)
-                    row = tables[g][b]
-                    row[:len(pages)] = pages
-                    row[len(pages):] = 0
-                    p = np.arange(start, start + n)
-                    slot_maps[g][t:t + n] = np.asarray(pages, dtype=np.int64)[p // ps] * ps + p % ps
+                    pages = np.asarray(mgr.block_table(e.rid, g), dtype=np.int64)
+                    slot_maps[g][t:t + n] = pages[p // ps] * ps + p % ps
             for j in e.want:
                 if not 0 <= j < n:
                     raise ValueError(f"request {e.rid!r} wants place {j} of {n} tokens")
@@ -197,10 +220,11 @@ class ModelRunner:
             t += n
             cu_q[b + 1] = t
             kv_lens[b] = start + n
-            slots[b] = mgr.slot(e.rid)
+            slots[b] = slot
             fresh[b] = 1 if start == 0 else 0
             max_q, max_kv = max(max_q, n), max(max_kv, start + n)
-        # padding of a captured shape: token rows that write nowhere, requests without tokens
+        # padding of a captured shape: token rows that write nowhere, requests without tokens (their
+        # block-table rows are the spare row of null pages)
         if Tp > T:
             ids[T:Tp] = 0
             pos[T:Tp] = 0
@@ -209,10 +233,10 @@ class ModelRunner:
         for b in range(B, Bp):
             cu_q[b + 1] = T
             kv_lens[b] = 0
-            slots[b] = 0
+            slots[b] = S
             fresh[b] = 0
-            for g in range(G):
-                tables[g][b, :] = 0
+        seg("meta")[0] = num_pairs
+        self._used[buf] = self._pairs_at + 2 * num_pairs
         ctx = StepContext()
         ctx.num_tokens, ctx.num_requests = Tp, Bp
         ctx.max_q_len, ctx.max_kv_len = max_q, max_kv
@@ -220,7 +244,18 @@ class ModelRunner:
         ctx.num_logit_rows = w
         ctx.host = {"real_tokens": T, "real_requests": B, "cu_q": cu_q[:Bp + 1].tolist(),
                     "kv_lens": kv_lens[:Bp].tolist(), "state_slots": slots[:Bp].tolist(),
-                    "fresh": fresh[:Bp].tolist()}
+                    "fresh": fresh[:Bp].tolist(), "table_receipts": receipts, "work": {}}
+        if not ctx.decode_only:
+            # attention work lists of the step, for the block sizes the mixers announced
+            for q in self._tile_sizes:
+                tile_req, tile_q0, dec_req, dec_tok, longest = ops.cut_attention_work(
+                    ctx.host["cu_q"], ctx.host["kv_lens"], Bp, q)
+                nt, nd = len(tile_req), len(dec_req)
+                seg(f"tile_req{q}")[:nt] = tile_req
+                seg(f"tile_q0{q}")[:nt] = tile_q0
+                seg("dec_req")[:nd] = dec_req
+                seg("dec_tok")[:nd] = dec_tok
+                ctx.host["work"][q] = (nt, nd, longest)
         return ctx
 
     def _bind_device_views(self, ctx):
@@ -235,16 +270,39 @@ class ModelRunner:
         ctx.fresh = self._seg(d, "fresh", B)
         ctx.groups = []
         for g in range(len(self.model.cache_groups)):
-            table = self._seg(d, f"block_table{g}").view(self.cfg.max_num_seqs, self.max_blocks)
-            ctx.groups.append(GroupView(self.page_size, self.max_blocks,
-                                        self._seg(d, f"slot_mapping{g}", T), table[:B], self.num_pages))
+            ctx.groups.append(GroupView(self.page_size, self.max_blocks, self._seg(d, f"slot_mapping{g}", T),
+                                        self._step_tables[g, :B], self.num_pages))
+        for q, (nt, nd, longest) in ctx.host.get("work", {}).items():
+            work = ops.AttentionWork()
+            work.num_tiles, work.num_decode, work.max_decode_kv = nt, nd, longest
+            work.tile_req, work.tile_q0 = self._seg(d, f"tile_req{q}", nt), self._seg(d, f"tile_q0{q}", nt)
+            work.dec_req, work.dec_tok = self._seg(d, "dec_req", nd), self._seg(d, "dec_tok", nd)
+            ctx.tile_cache[(q, True)] = work
         ctx.device_cache = self.device_cache
         ctx.dtype = self.dtype
         ctx.slot_tokens = self.slot_tokens
         return ctx
 
-    def _upload(self, buf=0):
-        self._dev.copy_(self._hosts[buf], non_blocking=True)
+    def _copy_in(self, buf=0):
+        """One copy: the used part of staging buffer ``buf``."""
+        used = self._used[buf]
+        self._dev[:used].copy_(self._hosts[buf][:used], non_blocking=True)
+        self.last_upload_bytes = used * 4
+
+    def _tables_step(self, num_requests=None):
+        """The step's block-table changes go into the resident rows; the rows of its requests are
+        gathered into the tables that the attention kernels index by request."""
+        if not len(self.model.cache_groups):
+            return
+        pairs = self._dev[self._pairs_at:].view(self._pairs_capacity, 2)
+        B = num_requests if num_requests is not None else self.cfg.max_num_seqs
+        ops.block_tables_step(self._resident_tables, pairs, self._seg(self._dev, "meta", 1), self._step_tables,
+                              self._seg(self._dev, "state_slots"), B)
+
+    def _upload(self, buf=0, num_requests=None):
+        self._copy_in(buf)
+        with ops.stream_scope():
+            self._tables_step(num_requests)
 
     def _check_host(self, ctx, buf):
         """The host half of the index check: every index buffer of the packed step against the size
@@ -268,15 +326,18 @@ class ModelRunner:
         elif ((kv < q_lens) | (kv > cfg.max_model_len)).any():
             problems.append("a request whose length is below its new tokens or above max_model_len")
         slots = seg("state_slots", B)
-        if ((slots < 0) | (slots >= S)).any():
-            problems.append(f"a state slot outside [0, {S})")
+        if ((slots < 0) | (slots > S)).any():               # S itself is the spare slot of padded requests
+            problems.append(f"a state slot outside [0, {S}]")
         for g in range(len(self.model.cache_groups)):
             sm = seg(f"slot_mapping{g}", T)
             if ((sm < -1) | (sm >= self.num_pages * self.page_size)).any():
                 problems.append(f"group {g}: a cache slot outside the pool of {self.num_pages} pages")
-            table = self._seg(h, f"block_table{g}").reshape(S, self.max_blocks)[:B]
-            if ((table < 0) | (table >= self.num_pages)).any():
-                problems.append(f"group {g}: a page number outside [0, {self.num_pages})")
+        n = int(self._seg(h, "meta", 1)[0])
+        pairs = h[self._pairs_at:self._pairs_at + 2 * n].reshape(n, 2)
+        if n < 0 or n > self._pairs_capacity or ((pairs[:, 0] < 0) | (pairs[:, 0] >= self._resident_tables.numel())).any():
+            problems.append("a block-table change outside the resident tables")
+        elif ((pairs[:, 1] < 0) | (pairs[:, 1] >= self.num_pages)).any():
+            problems.append(f"a page number outside [0, {self.num_pages})")
         if problems:
             raise ValueError("the packed step holds " + "; ".join(problems))
 
@@ -304,7 +365,13 @@ class ModelRunner:
     @torch.inference_mode()
     def launch(self, prep: Prepared):
         """Upload and run a prepared step; its tokens are computed afterwards."""
-        self._upload(prep.buf)
+        # (a captured graph holds the block-table kernels itself: only the copy happens here)
+        if prep.graph is not None:
+            self._copy_in(prep.buf)
+        else:
+            self._upload(prep.buf, prep.ctx.num_requests)
+        for receipt in prep.ctx.host.get("table_receipts", ()):
+            self.manager.table_synced(receipt)
         if self.device.type == "cuda":
             if self._copied[prep.buf] is None:
                 self._copied[prep.buf] = torch.cuda.Event()
@@ -328,8 +395,9 @@ class ModelRunner:
 
     def _forward(self, ctx):
         if self.cfg.check_indices:
+            # (slot max_num_seqs is the spare one that padded requests of a captured shape name)
             ops.sanitize_step(ctx, self.model.vocab_size, self.cfg.max_model_len, self.cfg.max_model_len,
-                              self.cfg.max_num_seqs)
+                              self.cfg.max_num_seqs + 1)
         return self.model.forward(ctx)
 
     def step(self, entries):
@@ -386,16 +454,18 @@ class ModelRunner:
                 self._seg(self._hosts_np[0], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
                 ctx.max_kv_len = self.cfg.max_model_len
                 self._bind_device_views(ctx)
-                self._upload()
+                self._copy_in(0)
                 stream = torch.cuda.Stream(self.device)
                 stream.wait_stream(torch.cuda.current_stream(self.device))
                 with torch.cuda.stream(stream), ops.stream_scope():
+                    self._tables_step(size)
                     self._forward(ctx)                # warm-up outside capture
                 torch.cuda.current_stream(self.device).wait_stream(stream)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
                 with torch.cuda.graph(graph, pool=pool), ops.stream_scope():
+                    self._tables_step(size)           # every replay applies its step's block-table changes
                     out = self._forward(ctx)
                 pool = pool or graph.pool()
                 self.graphs[size] = (graph, out, size, ops.launch_count() - before)

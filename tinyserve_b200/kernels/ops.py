@@ -398,6 +398,19 @@ def units_for(head_dims) -> list:
 
 
 # ----------------------------------------------------------------------------- ops
+def block_tables_step(resident, pairs, num_pairs, step_tables, state_slots, num_requests):
+    """Apply a step's block-table changes to the resident rows and gather the rows of the step's
+    requests.  resident int32 [G, slots + 1, max_blocks]; pairs int32 [capacity, 2] (flat index
+    into resident, page); num_pairs int32 [1]; step_tables int32 [G, max_requests, max_blocks];
+    state_slots int32 [>= num_requests]: all on the device.  Two small launches."""
+    _cuda(resident, pairs, num_pairs, step_tables, state_slots)
+    G, slots1, max_blocks = resident.shape
+    lib = _elementwise()
+    _check(lib, lib.ts_block_tables_step(
+        _ptr(resident), _ptr(pairs), _ptr(num_pairs), c_int(pairs.shape[0]), _ptr(step_tables), _ptr(state_slots),
+        c_int(num_requests), c_int(step_tables.shape[1]), c_int(slots1 - 1), c_int(max_blocks), c_int(G), _stream()), 2)
+
+
 def sanitize_step(ctx, vocab_size, num_positions, max_kv_len, num_state_slots):
     """The device half of the index check (see csrc/elementwise.cu): every index of the step in
     ``ctx`` that lies outside its buffer is replaced by a harmless one and reported through the
@@ -583,21 +596,15 @@ class AttentionWork:
     __slots__ = ("tile_req", "tile_q0", "num_tiles", "dec_req", "dec_tok", "num_decode", "max_decode_kv")
 
 
-def attention_work(ctx, queries_per_tile, device, split_decodes=True):
-    """Cuts a step's attention into work lists (int32 device tensors).  Requests with several
-    tokens are cut into blocks of ``queries_per_tile`` queries, (request, first query) each,
-    heaviest (most keys) first, so that a long portion beside many short requests launches no
-    block for nothing.  With ``split_decodes``, requests of one token are listed apart, (request,
-    token) each: they go to the decode kernel, which does not spend a block of rows on one query."""
-    cache = getattr(ctx, "tile_cache", None)
-    key = (queries_per_tile, split_decodes)
-    if cache is not None and key in cache:
-        return cache[key]
-    host = getattr(ctx, "host", None) or {}
-    cu = host.get("cu_q") or ctx.cu_q.tolist()
-    kv = host.get("kv_lens") or ctx.kv_lens.tolist()
+def cut_attention_work(cu, kv, num_requests, queries_per_tile, split_decodes=True):
+    """The host half: (tile_req, tile_q0, dec_req, dec_tok, longest decode context) as lists.
+    Requests with several tokens are cut into blocks of ``queries_per_tile`` queries, (request,
+    first query) each, heaviest (most keys) first, so that a long portion beside many short
+    requests launches no block for nothing.  With ``split_decodes``, requests of one token are
+    listed apart, (request, token) each, longest context first: they go to the decode kernel,
+    which does not spend a block of rows on one query."""
     tiles, decodes = [], []
-    for b in range(ctx.num_requests):
+    for b in range(num_requests):
         n = cu[b + 1] - cu[b]
         if n == 1 and split_decodes:
             decodes.append((kv[b], b, cu[b]))
@@ -605,14 +612,27 @@ def attention_work(ctx, queries_per_tile, device, split_decodes=True):
         for q0 in range(0, n, queries_per_tile):
             tiles.append((kv[b] - n + q0, b, q0))
     tiles.sort(reverse=True)
-    decodes.sort(reverse=True)               # the longest contexts start first
-    dec_req, dec_tok = [d[1] for d in decodes], [d[2] for d in decodes]
-    max_decode_kv = decodes[0][0] if decodes else 0
+    decodes.sort(reverse=True)
+    return ([t[1] for t in tiles], [t[2] for t in tiles], [d[1] for d in decodes], [d[2] for d in decodes],
+            decodes[0][0] if decodes else 0)
+
+
+def attention_work(ctx, queries_per_tile, device, split_decodes=True):
+    """A step's attention work lists (int32 device tensors) for blocks of ``queries_per_tile``
+    queries.  The engine's step function packs them with the rest of the step (one upload) for
+    the tile sizes its mixers announce; for any other caller they are cut and uploaded here."""
+    cache = getattr(ctx, "tile_cache", None)
+    key = (queries_per_tile, split_decodes)
+    if cache is not None and key in cache:
+        return cache[key]
+    host = getattr(ctx, "host", None) or {}
+    cu = host.get("cu_q") or ctx.cu_q.tolist()
+    kv = host.get("kv_lens") or ctx.kv_lens.tolist()
+    tile_req, tile_q0, dec_req, dec_tok, max_decode_kv = cut_attention_work(
+        cu, kv, ctx.num_requests, queries_per_tile, split_decodes)
     work = AttentionWork()
-    work.num_tiles, work.num_decode, work.max_decode_kv = len(tiles), len(dec_req), max_decode_kv
-    packed = torch.tensor([t[1] for t in tiles] + [t[2] for t in tiles] + dec_req + dec_tok, dtype=torch.int32)
-    if device.type == "cuda":
-        packed = packed.pin_memory().to(device, non_blocking=True)
+    work.num_tiles, work.num_decode, work.max_decode_kv = len(tile_req), len(dec_req), max_decode_kv
+    packed = torch.tensor(tile_req + tile_q0 + dec_req + dec_tok, dtype=torch.int32).to(device)
     nt, nd = work.num_tiles, work.num_decode
     work.tile_req, work.tile_q0 = packed[:nt], packed[nt:2 * nt]
     work.dec_req, work.dec_tok = packed[2 * nt:2 * nt + nd], packed[2 * nt + nd:]

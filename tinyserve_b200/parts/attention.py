@@ -65,6 +65,9 @@ class Attention(Mixer):
 
     accepts_scaled_rows = True
 
+    def work_tile_queries(self, dtype, page_size):
+        return ops.prefill_tile_queries(dtype, self.num_heads, self.num_kv_heads, self.head_dim, page_size)
+
     def forward(self, h, ctx, call):
         qkv = ops.linear(h, self.w["qkv_proj.weight"], self.w.get("qkv_proj.bias"), allow_partials=True)
         cache = ctx.cache(call.cache)

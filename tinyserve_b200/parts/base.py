@@ -180,6 +180,12 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def work_tile_queries(self, dtype, page_size: int) -> int:
+        """Queries per block of the attention work lists this mixer will ask for
+        (``kernels.ops.attention_work``) in steps that bring prompt portions, or 0.  The step
+        function then packs those lists with the step's other inputs."""
+        return 0
+
     def forward(self, h, ctx, call):
         """h [T, hidden] in the compute dtype -> [T, hidden] (a tensor, or what ops.linear
         returned with allow_partials=True).  ``call`` is the

@@ -29,10 +29,38 @@ def recent_tokens(params, token_ids) -> list:
 
 
 class Sampler:
-    def __init__(self, seed: int, device):
+    def __init__(self, seed: int, device, max_rows: int = 0):
         self.seed = int(seed)
         self.device = device
         self._zeros: dict = {}
+        self._staging = None
+        self._rows = max_rows
+        self._flip = 0
+
+    def _settings(self, temps, ks, ps, streams, steps):
+        """The per-row settings as device tensors, through one pinned staging buffer and one copy
+        (two buffers take turns: the copy of the step before may still be pending)."""
+        n = len(temps)
+        if self._staging is None or n > self._rows:
+            self._rows = max(self._rows, n, 8)
+            words = 6 * self._rows                    # float32 temp, float32 top_p, int32 top_k, int32 steps, int64 streams
+            pin = torch.device(self.device).type == "cuda"
+            self._staging = [(torch.zeros(words, dtype=torch.int32).pin_memory() if pin
+                              else torch.zeros(words, dtype=torch.int32)) for _ in range(2)]
+            self._device_words = torch.zeros(words, dtype=torch.int32, device=self.device)
+        R = self._rows
+        host = self._staging[self._flip]
+        self._flip ^= 1
+        h = host.numpy()
+        h[0:n].view("float32")[:] = temps
+        h[R:R + n].view("float32")[:] = ps
+        h[2 * R:2 * R + n] = ks
+        h[3 * R:3 * R + n] = steps
+        h[4 * R:4 * R + 2 * n].view("int64")[:] = streams
+        d = self._device_words
+        d.copy_(host, non_blocking=True)
+        return (d[0:n].view(torch.float32), d[R:R + n].view(torch.float32), d[2 * R:2 * R + n],
+                d[3 * R:3 * R + n], d[4 * R:4 * R + 2 * n].view(torch.int64))
 
     def _greedy_args(self, n):
         """Device tensors for an all-greedy batch (temperature 0 ignores the noise arguments)."""
@@ -77,11 +105,6 @@ class Sampler:
                                          table.to(dev), torch.tensor(pen_vals, dtype=torch.float32, device=dev))
         need_k = any(k > 0 for k, t in zip(ks, temps) if t > 0)
         need_p = any(p < 1.0 for p, t in zip(ps, temps) if t > 0)
-        return ops.sample(
-            logits,
-            torch.tensor(temps, dtype=torch.float32, device=dev),
-            torch.tensor(streams, dtype=torch.int64, device=dev),
-            torch.tensor(steps, dtype=torch.int32, device=dev),
-            self.seed,
-            top_k=torch.tensor(ks, dtype=torch.int32, device=dev) if need_k else None,
-            top_p=torch.tensor(ps, dtype=torch.float32, device=dev) if need_p else None, **feedback)
+        d_temps, d_ps, d_ks, d_steps, d_streams = self._settings(temps, ks, ps, streams, steps)
+        return ops.sample(logits, d_temps, d_streams, d_steps, self.seed, top_k=d_ks if need_k else None,
+                          top_p=d_ps if need_p else None, **feedback)
