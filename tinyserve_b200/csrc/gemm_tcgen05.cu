@@ -6,8 +6,11 @@
 // the tensor core) and the tokens, padded to TILE_T in {16, 32, 64, 128}, as its N side.  The
 // accumulator D[128 weight rows x TILE_T tokens] lives in tensor memory.  Per 64-wide slice of K
 // one thread issues two TMA loads (W tile 128 x 64, x tile TILE_T x 64, 128-byte swizzle) into a
-// ring of shared-memory stages guarded by mbarriers; another thread issues four
-// tcgen05.mma (K = 16 each) per slice and commits the stage back to the loader.
+// ring of shared-memory stages guarded by mbarriers; four threads of four warps issue one
+// tcgen05.mma (K = 16) each per slice, into an accumulator of their own, and commit the stage back
+// to the loader.  (One thread can issue a tcgen05.mma every 196 cycles, however small the MMA:
+// measured on B200.  Four issuing warps give four times the rate, which a block needs to keep
+// up with its share of the memory bandwidth when few blocks stream a product.)
 //
 // Shapes with few row tiles (N = 4096: 32 tiles for 148 SMs) are also cut along K.  Every block
 // then stores its partial tile to scratch and bumps the tile's counter; the block that arrives
@@ -30,7 +33,8 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int TILE_N = 128;          // weight rows of a block (MMA M)
 constexpr int BK = 64;               // K elements of a stage: 128 bytes, one swizzle row
-constexpr int THREADS = 128;
+constexpr int ISSUERS = BK / 16;     // issuing threads: one per K step of a stage, each with its own accumulator
+constexpr int THREADS = 32 * (1 + ISSUERS);      // warp 0 loads, warps 1..4 issue, warps 0..3 do the epilogue
 constexpr int W_STAGE_BYTES = TILE_N * BK * 2;
 
 struct GemmParams {
@@ -64,10 +68,9 @@ __host__ __device__ constexpr uint32_t instr_desc(int tile_t) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(tile_t >> 3) << 17) |
          (static_cast<uint32_t>(TILE_N >> 4) << 24);
 }
-// Consecutive MMAs into one accumulator depend on each other, and an MMA of 16 tokens is all
-// latency; the four K steps of a stage therefore go to ACCS independent accumulators, which the
+// The four K steps of a stage go to four accumulators, one per issuing thread, which the
 // epilogue adds up.
-template <int TILE_T> struct Accs { static constexpr int N = TILE_T <= 64 ? 4 : 2; };
+template <int TILE_T> struct Accs { static constexpr int N = ISSUERS; };
 
 template <int TILE_T>
 __device__ __forceinline__ void tmem_load8_sum(uint32_t addr, float (&v)[8]) {
@@ -119,9 +122,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(smem_u32(&full[s]), 1);
-      mbar_init(smem_u32(&empty[s]), 1);
+      mbar_init(smem_u32(&empty[s]), ISSUERS);       // every issuing thread commits its own MMA
     }
-    mbar_init(smem_u32(accum), 1);
+    mbar_init(smem_u32(accum), ISSUERS);
     *abort_flag = 0;
     *is_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -169,11 +172,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try_wait(bar, (i / C::STAGES) & 1); ++w) {}
       }
     }
-  } else if (threadIdx.x == 32) {
-    // issuer: four MMAs of K = 16 per stage
+  } else if (warp >= 1 && lane == 0) {
+    // issuer `k` of four: the k-th K step (16 wide) of every stage, into accumulator k
+    const int k = warp - 1;
     pdl_wait();
     const uint32_t idesc = instr_desc(TILE_T);
     const uint64_t desc0 = smem_desc(smem_u32(smem));
+    const uint32_t acc = tmem_base + k * TILE_T;
     bool ok = true;
     for (int i = 0; i < nkb && ok; ++i) {
       const int s = i % C::STAGES;
@@ -182,21 +187,22 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       tcgen05_fence_after();
       // one descriptor per operand and stage; a K step of 16 is 32 bytes = 2 address units on
       const uint64_t ad = desc0 + (uint64_t)s * (C::STAGE_BYTES >> 4), bd = ad + (W_STAGE_BYTES >> 4);
-#pragma unroll
-      for (int k = 0; k < BK / 16; ++k)
-        umma(tmem_base + (k % Accs<TILE_T>::N) * TILE_T, ad + 2 * k, bd + 2 * k, idesc,
-             (i > 0 || k >= Accs<TILE_T>::N) ? 1u : 0u);
+      umma(acc, ad + 2 * k, bd + 2 * k, idesc, i > 0 ? 1u : 0u);
       tcgen05_commit(smem_u32(&empty[s]));
     }
     if (ok && nkb > 0) tcgen05_commit(smem_u32(accum));
   } else {
     pdl_wait();
-    if (p.x_sumsq != nullptr && threadIdx.x >= 64 && threadIdx.x < 64 + TILE_T) {
-      const int j = threadIdx.x - 64, m = t_tile * TILE_T + j;
-      float sum = 0.f;
-      if (m < p.M)
-        for (int t = 0; t < p.x_tiles; ++t) sum += __ldcg(p.x_sumsq + (size_t)t * SUMSQ_STRIDE + m);
-      row_scale[j] = rsqrtf(sum / (float)p.K + p.x_eps);
+    // (lanes 1.. of warps 1..4: they do not issue, they have time for the rows' norm factors)
+    const int idle = (warp - 1) * 31 + lane - 1;          // 0 .. 123 over the non-issuing lanes of warps 1..4
+    if (p.x_sumsq != nullptr && warp >= 1) {
+      for (int j = idle; j < TILE_T; j += 31 * ISSUERS) {
+        const int m = t_tile * TILE_T + j;
+        float sum = 0.f;
+        if (m < p.M)
+          for (int t = 0; t < p.x_tiles; ++t) sum += __ldcg(p.x_sumsq + (size_t)t * SUMSQ_STRIDE + m);
+        row_scale[j] = rsqrtf(sum / (float)p.K + p.x_eps);
+      }
     }
   }
   __syncthreads();
@@ -207,9 +213,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (have) have = mbar_wait(smem_u32(accum), 0, abort_flag);
   have = __all_sync(0xffffffffu, have);      // tcgen05.ld is warp-wide: decide per warp
   tcgen05_fence_after();
+  // warps 0..3 own the 128 lanes of tensor memory (a warp reaches the quarter of its index mod 4);
+  // warp 4 only takes part in the barriers
+  const bool epi = warp < 4;
+  have = have && epi;
   const int n = n_tile * TILE_N + warp * 32 + lane;
   const int t0 = t_tile * TILE_T;
-  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
   if (p.residual != nullptr) {
     // residual form.  Every block of the cluster leaves its partial tile in its shared memory
     // (the ring is idle: all MMAs have completed); rank r then owns the tokens r, r + splits, ...:
@@ -224,10 +234,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
       }
+      if (epi) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) red[(c + i) * TILE_N + threadIdx.x] = scaled ? v[i] * row_scale[c + i] : v[i];
+        for (int i = 0; i < 8; ++i) red[(c + i) * TILE_N + threadIdx.x] = scaled ? v[i] * row_scale[c + i] : v[i];
+      }
     }
-    const float wn = n < p.N ? p.norm_w[n] : 0.f;
+    const float wn = (epi && n < p.N) ? p.norm_w[n] : 0.f;
     cluster_arrive();
     cluster_wait();
     for (int j = split; j < TILE_T && t0 + j < p.M; j += p.splits) {
@@ -235,9 +247,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       float part[8];
 #pragma unroll
       for (int s = 0; s < 8; ++s)
-        if (s < p.splits) part[s] = cluster_load_f32(red + j * TILE_N + threadIdx.x, s);
+        if (epi && s < p.splits) part[s] = cluster_load_f32(red + j * TILE_N + threadIdx.x, s);
       float sq = 0.f;
-      if (n < p.N) {
+      if (epi && n < p.N) {
         float sum = 0.f;
 #pragma unroll
         for (int s = 0; s < 8; ++s)
@@ -270,7 +282,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int i = 0; i < 8; ++i) acc[c + i] = scaled ? v[i] * row_scale[c + i] : v[i];
       }
       float* up = reinterpret_cast<float*>(smem);               // [64][TILE_T + 1]
-      if (warp >= 2) {
+      if (warp >= 2 && epi) {
 #pragma unroll
         for (int i = 0; i < TILE_T; ++i) up[(threadIdx.x - 64) * (TILE_T + 1) + i] = acc[i];
       }
@@ -302,7 +314,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] += bn;
-      if (n < p.N) {
+      if (epi && n < p.N) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int m = t0 + c + i;
@@ -324,8 +336,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[i] = 0.f;
       }
+      if (epi) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = scaled ? v[i] * row_scale[c + i] : v[i];
+        for (int i = 0; i < 8; ++i) mine[(c + i) * TILE_N + warp * 32 + lane] = scaled ? v[i] * row_scale[c + i] : v[i];
+      }
     }
     if (p.out != nullptr) {
       __threadfence();
@@ -336,7 +350,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (*is_last) p.counters[tile] = 0;
       }
       __syncthreads();
-      if (*is_last) {
+      if (*is_last && epi) {
         __threadfence();
         const float* base = p.partials + (size_t)tile * (TILE_T * TILE_N);
         const size_t split_stride = (size_t)tiles * (TILE_T * TILE_N);
