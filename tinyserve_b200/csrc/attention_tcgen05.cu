@@ -9,11 +9,17 @@
 //            and V pages of the request's block table (2-D TMA boxes of one page x 64 columns,
 //            128-byte swizzle), keys and values in rings of two stages each, the keys one tile
 //            ahead of the values;
-//   warp 1   issues tcgen05.mma: S_g = Q_g K^T into tensor memory, and O_g += P_g V (P_g read from
-//            tensor memory, V as an N-contiguous operand) once the probabilities are there; the
-//            scores of tile g's next key tile follow its P V at once (the tensor pipe runs in order).
-//            One thread issues for both query tiles: that keeps the two tiles half a period apart
-//            (with an issuing thread per tile they fell into step and ran 8 % slower);
+//   warp 1 and the last ISSUERS - 1 warps issue tcgen05.mma: S_g = Q_g K^T into tensor memory, and
+//            O_g += P_g V (P_g read from tensor memory, V as an N-contiguous operand) once the
+//            probabilities are there; the scores of tile g's next key tile follow its P V at once.
+//            A thread can issue one tcgen05.mma per 196 cycles, whatever its size (measured), and
+//            the products of a tile's chain (scores -> softmax -> P V -> next scores) lie on the
+//            critical path: every product's K steps are therefore dealt to ISSUERS threads of
+//            different warps, which walk the products in the same order.  Two hand-overs keep the
+//            tensor pipe's order right: the P V steps of a tile must all be issued before the first
+//            step of its next scores (which overwrites P), and that first step (it overwrites S)
+//            before the other steps of the same scores.  O starts as zeros, so that no P V step
+//            is the first one;
 //   warps 2-5 (tile 0) and 6-9 (tile 1), one thread per row: read the row of S from tensor memory,
 //            mask (key j is visible to the query at position p iff j <= p and, with a window
 //            W > 0, j > p - W: serve.py:668-680), online softmax in 32-bit with exp2
@@ -40,7 +46,13 @@ static_assert(D == 64 || D == 128, "the tcgen05 prefill kernel takes head sizes 
 constexpr int BM = 128;                      // rows of a query tile
 constexpr int BN = 128;                      // keys of a tile
 constexpr int GROUPS = 2;                    // query tiles of a block
-constexpr int THREADS = 64 + GROUPS * 128;
+#ifndef TS_ATTN_ISSUERS
+#define TS_ATTN_ISSUERS 3
+#endif
+constexpr int ISSUERS = TS_ATTN_ISSUERS;     // threads that issue the MMAs of every product
+constexpr int SOFTMAX_WARP0 = 2;             // warps 2..9: one thread per row of the two query tiles
+constexpr int EXTRA_WARP0 = SOFTMAX_WARP0 + GROUPS * 4;     // warps 10..: issuers 1.. (issuer 0 is warp 1)
+constexpr int THREADS = 32 * (EXTRA_WARP0 + ISSUERS - 1);
 constexpr int K_STAGES = 2;
 constexpr int V_STAGES = 2;
 constexpr int DCH = D / 64;                  // 64-column chunks of a head
@@ -91,24 +103,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   uint64_t* s_full = v_empty + V_STAGES;         // [GROUPS] S_g holds the scores of a key tile
   uint64_t* p_full = s_full + GROUPS;            // [GROUPS] P_g is in tensor memory, O_g is rescaled
   uint64_t* o_ready = p_full + GROUPS;           // [GROUPS] O_g holds the sum over the key tiles so far
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_ready + GROUPS);
+  uint64_t* pv_issued = o_ready + GROUPS;        // [GROUPS] every issuer has issued its P V steps of the key tile
+  uint64_t* s_first = pv_issued + GROUPS;        // [GROUPS] the first step of the scores (it overwrites S_g) is issued
+  uint64_t* o_zeroed = s_first + GROUPS;         // [GROUPS] O_g holds zeros
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_zeroed + GROUPS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(q_full), 1);
+    // (every issuer commits its own MMAs: what they complete counts ISSUERS arrivals)
     for (int s = 0; s < K_STAGES; ++s) {
       mbar_init(smem_u32(&k_full[s]), 1);
-      mbar_init(smem_u32(&k_empty[s]), 1);
+      mbar_init(smem_u32(&k_empty[s]), ISSUERS);
     }
     for (int s = 0; s < V_STAGES; ++s) {
       mbar_init(smem_u32(&v_full[s]), 1);
-      mbar_init(smem_u32(&v_empty[s]), 1);
+      mbar_init(smem_u32(&v_empty[s]), ISSUERS);
     }
     for (int g = 0; g < GROUPS; ++g) {
-      mbar_init(smem_u32(&s_full[g]), 1);
+      mbar_init(smem_u32(&s_full[g]), ISSUERS);
       mbar_init(smem_u32(&p_full[g]), 4);
-      mbar_init(smem_u32(&o_ready[g]), 1);
+      mbar_init(smem_u32(&o_ready[g]), ISSUERS);
+      mbar_init(smem_u32(&pv_issued[g]), ISSUERS);
+      mbar_init(smem_u32(&s_first[g]), 1);
+      mbar_init(smem_u32(&o_zeroed[g]), 4);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -195,28 +214,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         if (traced && lane == 0) timeline_mark_thread(30, t);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp >= EXTRA_WARP0) {
     if (lane == 0 && n_tiles > 0) {
+      // issuer `me` of ISSUERS: its share of the K steps of every product, products in one order
+      const int me = warp == 1 ? 0 : warp - EXTRA_WARP0 + 1;
       constexpr uint32_t idesc_qk = make_idesc(BM, BN, false);
       constexpr uint32_t idesc_pv = make_idesc(BM, D, true);
+      constexpr int QK_STEPS = D / 16, PV_STEPS = BN / 16;
+      const int qk_lo = me * QK_STEPS / ISSUERS, qk_hi = (me + 1) * QK_STEPS / ISSUERS;
+      const int pv_lo = me * PV_STEPS / ISSUERS, pv_hi = (me + 1) * PV_STEPS / ISSUERS;
       const uint64_t q_desc = smem_desc(smem_u32(Qs)), k_desc = smem_desc(smem_u32(Ks));
       const uint64_t v_desc = smem_desc_mn(smem_u32(Vs), CHUNK_BYTES);
-      // S_g = Q_g K^T of key tile t
-      auto scores = [&](int g, int t) -> bool {
+      // S_g = Q_g K^T of key tile t.  `after_pv`: the P V of tile g's previous key tile read P_g
+      // from S_g's columns; all of its steps must be in the pipe before step 0 here.
+      auto scores = [&](int g, int t, bool after_pv) -> bool {
         const int s = t % K_STAGES;
-        // (S_g is free: the P V of tile g's previous key tile, which read P_g from its columns,
-        // was issued before and the tensor pipe runs in order)
-        if (!mbar_wait(smem_u32(&k_full[s]), (t / K_STAGES) & 1, abort_flag)) return false;
+        if (!mbar_spin_wait(smem_u32(&k_full[s]), (t / K_STAGES) & 1, abort_flag)) return false;
+        if (me == 0) {
+          if (after_pv && !mbar_spin_wait(smem_u32(&pv_issued[g]), (t - 1) & 1, abort_flag)) return false;
+        } else {
+          if (!mbar_spin_wait(smem_u32(&s_first[g]), t & 1, abort_flag)) return false;
+        }
         tcgen05_fence_after();
-        if (traced) timeline_mark_thread(10 + g, t);
+        if (traced && me == 0) timeline_mark_thread(10 + g, t);
         // descriptors: a base made once, plus the operand's offset in 16-byte units (the address is
-        // the descriptor's low field; shared memory ends below its range).  The issuing thread is
+        // the descriptor's low field; shared memory ends below its range).  An issuing thread is
         // one serial chain of instructions: whatever it computes per MMA delays every MMA.
         const uint64_t qd = q_desc + g * (Q_BYTES >> 4), kd = k_desc + s * (KV_BYTES >> 4);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
+        for (int k = 0; k < QK_STEPS; ++k) {
+          if (k < qk_lo || k >= qk_hi) continue;
           const uint64_t off = ((k / 4) * CHUNK_BYTES + (k % 4) * 32) >> 4;
           umma(tmem_base + g * BN, qd + off, kd + off, idesc_qk, k > 0 ? 1u : 0u);
+          if (k == 0) {
+            // step 0 is in the pipe: the other issuers may add theirs
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&s_first[g]));
+          }
         }
         tcgen05_commit(smem_u32(&s_full[g]));
         if (g == groups - 1) tcgen05_commit(smem_u32(&k_empty[s]));
@@ -225,31 +259,37 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // O_g += P_g V of key tile t
       auto values = [&](int g, int t) -> bool {
         const int s = t % V_STAGES;
-        if (!mbar_wait(smem_u32(&v_full[s]), (t / V_STAGES) & 1, abort_flag) ||
-            !mbar_wait(smem_u32(&p_full[g]), t & 1, abort_flag))
+        if (!mbar_spin_wait(smem_u32(&v_full[s]), (t / V_STAGES) & 1, abort_flag) ||
+            !mbar_spin_wait(smem_u32(&p_full[g]), t & 1, abort_flag))
           return false;
         tcgen05_fence_after();
-        if (traced) timeline_mark_thread(12 + g, t);
+        if (traced && me == 0) timeline_mark_thread(12 + g, t);
         const uint64_t vd = v_desc + s * (KV_BYTES >> 4);
         const uint32_t o_addr = tmem_base + 2 * BN + g * 128, p_addr = tmem_base + g * BN;
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k)
-          umma_ts(o_addr, p_addr + k * 8, vd + ((k * 16 * 128) >> 4), idesc_pv, (t > 0 || k > 0) ? 1u : 0u);
+        for (int k = 0; k < PV_STEPS; ++k) {
+          if (k < pv_lo || k >= pv_hi) continue;
+          umma_ts(o_addr, p_addr + k * 8, vd + ((k * 16 * 128) >> 4), idesc_pv, 1u);
+        }
+        // this issuer's steps are in the pipe (the next scores of the tile wait for all issuers')
+        tcgen05_fence_before();
+        mbar_arrive(smem_u32(&pv_issued[g]));
         tcgen05_commit(smem_u32(&o_ready[g]));
         if (g == groups - 1) tcgen05_commit(smem_u32(&v_empty[s]));
         return true;
       };
-      bool ok = mbar_wait(smem_u32(q_full), 0, abort_flag);
-      for (int g = 0; ok && g < groups; ++g) ok = scores(g, 0);
+      bool ok = mbar_spin_wait(smem_u32(q_full), 0, abort_flag);
+      for (int g = 0; ok && g < groups; ++g) ok = scores(g, 0, false);
+      for (int g = 0; ok && g < groups; ++g) ok = mbar_spin_wait(smem_u32(&o_zeroed[g]), 0, abort_flag);
       for (int t = 0; ok && t < n_tiles; ++t)
         for (int g = 0; ok && g < groups; ++g) {
           ok = values(g, t);
-          if (ok && t + 1 < n_tiles) ok = scores(g, t + 1);
+          if (ok && t + 1 < n_tiles) ok = scores(g, t + 1, true);
         }
     }
   } else {
     // one thread per row of query tile g
-    const int g = (warp - 2) >> 2;
+    const int g = (warp - SOFTMAX_WARP0) >> 2;
     if (g < groups && n_tiles > 0) {
       const int q4 = warp & 3;
       const int r = q4 * 32 + lane;
@@ -265,6 +305,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool tracer = traced && (threadIdx.x & 127) == 64;
       float m = -INFINITY, l = 0.f;
       bool ok = true;
+      {
+        // O_g starts as zeros: every P V step then accumulates, whichever issuer's comes first
+        float zeros[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) zeros[e] = 0.f;
+#pragma unroll
+        for (int c = 0; c < D; c += 32) tmem_store32(tmem_o + lane_addr + c, zeros);
+        tmem_store_wait();
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&o_zeroed[g]));
+      }
       for (int t = 0; t < n_tiles; ++t) {
         const int j0 = (first_tile + t) * BN;
         ok = mbar_wait(smem_u32(&s_full[g]), t & 1, abort_flag);

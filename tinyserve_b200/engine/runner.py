@@ -423,36 +423,49 @@ class ModelRunner:
             sizes.append(S)
         return sorted(set(sizes))
 
+    def context_bounds(self):
+        """Context lengths for which decode graphs are captured apart: the number of key ranges a
+        decode attention launch is cut into is fixed in a captured graph, and the best number for
+        a few hundred keys (a cluster of up to 8 ranges) is far from the best for 16,000."""
+        bounds = [b for b in (1024, 4096, 16384, 65536) if b < self.cfg.max_model_len]
+        return bounds + [self.cfg.max_model_len]
+
     def _graph_for(self, entries):
         if not self.graphs or not self.model.capturable:
             return None
         if any(len(e.tokens) != 1 or list(e.want) != [0] for e in entries):
             return None
+        mgr = self.manager
+        longest = max(mgr.num_computed(e.rid) for e in entries) + 1
         for size in self._graph_sizes:
             if size >= len(entries):
-                return self.graphs[size]
+                for bound in self._graph_bounds:
+                    if bound >= longest:
+                        return self.graphs[(size, bound)]
+                return None
         return None
 
     @torch.inference_mode()
     def capture_decode_graphs(self, sizes=None):
-        """Capture one graph per decode batch size: every request brings one token and
-        wants its logits.  Smaller batches run the next larger graph with empty requests.
+        """Capture one graph per decode batch size and context bound: every request brings one
+        token and wants its logits.  Smaller batches run the next larger graph with empty requests.
         A model with a part that is not ``capturable`` (it reads host-side lists of the step,
         which a replay would not refresh) is not captured: every step then runs eagerly."""
         if not self.model.capturable:
             return 0
         sizes = sorted(sizes or self.decode_buckets(), reverse=True)
+        bounds = self.context_bounds()
         pool = None
         dummy = "__capture__"
         self.manager.begin(dummy)
         try:
-            for size in sizes:
+            for size, bound in [(s, b) for s in sizes for b in bounds]:
                 entries = [StepEntry(dummy, [0], [0])]
                 ctx = self._pack(entries, 0, pad_requests=size, pad_tokens=size)
                 # captured shape: `size` requests of one token, all rows wanted
                 ctx.num_logit_rows = size
                 self._seg(self._hosts_np[0], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
-                ctx.max_kv_len = self.cfg.max_model_len
+                ctx.max_kv_len = bound                # the longest context this graph is chosen for
                 self._bind_device_views(ctx)
                 self._copy_in(0)
                 stream = torch.cuda.Stream(self.device)
@@ -468,9 +481,10 @@ class ModelRunner:
                     self._tables_step(size)           # every replay applies its step's block-table changes
                     out = self._forward(ctx)
                 pool = pool or graph.pool()
-                self.graphs[size] = (graph, out, size, ops.launch_count() - before)
+                self.graphs[(size, bound)] = (graph, out, size, ops.launch_count() - before)
         finally:
             self.manager.free(dummy)
-        self._graph_sizes = sorted(self.graphs)
+        self._graph_sizes = sorted({size for size, _ in self.graphs})
+        self._graph_bounds = sorted({bound for _, bound in self.graphs})
         return len(self.graphs)
 
