@@ -182,7 +182,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     bool ok = true;
     for (int i = 0; i < nkb && ok; ++i) {
       const int s = i % C::STAGES;
-      ok = mbar_wait(smem_u32(&full[s]), (i / C::STAGES) & 1, abort_flag);
+      ok = mbar_spin_wait(smem_u32(&full[s]), (i / C::STAGES) & 1, abort_flag);
       if (!ok) break;
       tcgen05_fence_after();
       // one descriptor per operand and stage; a K step of 16 is 32 bytes = 2 address units on
@@ -210,7 +210,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   // epilogue: lane = weight row, columns = tokens
   bool have = nkb > 0;
-  if (have) have = mbar_wait(smem_u32(accum), 0, abort_flag);
+  if (have) have = mbar_spin_wait(smem_u32(accum), 0, abort_flag);
   have = __all_sync(0xffffffffu, have);      // tcgen05.ld is warp-wide: decide per warp
   tcgen05_fence_after();
   // warps 0..3 own the 128 lanes of tensor memory (a warp reaches the quarter of its index mod 4);
