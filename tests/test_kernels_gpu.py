@@ -10,7 +10,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-TOL = {torch.float32: 2e-5, torch.bfloat16: 2e-2}     # relative to the reference's scale
+TOL = {torch.float32: 2e-5, torch.bfloat16: 8e-3}     # relative to the reference's scale; bfloat16: one rounding of the output (2^-9) and of each input
 
 
 def ops():

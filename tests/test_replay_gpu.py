@@ -20,8 +20,14 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 # Largest absolute logit difference allowed, relative to the largest plain logit.
 # float32: rounding of 32-bit sums only (the plain side is float64).  bfloat16: activations
-# carry 8 bits of mantissa (2^-8 = 0.4 %) through a few layers.
-TOLERANCE = {"float32": 2e-5, "bfloat16": 2.5e-2}
+# carry 8 bits of mantissa (2^-8 = 0.4 %) through a few layers; per configuration, twice the
+# largest value measured on a B200, and beside it the largest root-mean-square difference over
+# the vocabulary at one position (a fault at one position moves its whole row).
+# Measured (largest, rms): float32 5.2e-7, 1.3e-7 at most; bfloat16 A 2.7e-3, 8.5e-4;
+# B 6.3e-3, 1.7e-3; C 6.3e-3, 1.8e-3; D 4.8e-3, 1.7e-3.
+TOLERANCE = {"float32": 2e-6, "bfloat16": 1.3e-2}
+BF16_TOLERANCE = {"A": (5.5e-3, 1.8e-3), "B": (1.3e-2, 3.5e-3), "C": (1.3e-2, 3.6e-3), "D": (1.0e-2, 3.5e-3)}
+MEASURED = {}
 LENGTHS = {"A": [5, 17, 31, 70, 2], "B": [1, 9, 40, 63, 100], "C": [90, 130, 57, 3, 75], "D": [33, 19, 80, 2, 64]}
 
 
@@ -66,7 +72,11 @@ def check(model, dtype, steps, out_dir, max_tokens=None, page=16):
         assert got[rid].shape == ref.shape
         err = (got[rid].double() - ref).abs().max(-1).values
         scale = ref.abs().max().item()
-        bad = (err > TOLERANCE[dtype] * scale).nonzero()
+        tol_max, tol_rms = (TOLERANCE[dtype],) * 2 if dtype == "float32" else BF16_TOLERANCE[model["name"]]
+        rms = (got[rid].double() - ref).pow(2).mean(-1).sqrt()
+        bad = ((err > tol_max * scale) | (rms > tol_rms * scale)).nonzero()
+        seen = MEASURED.setdefault((model["name"], dtype), [0.0, 0.0])
+        seen[0], seen[1] = max(seen[0], err.max().item() / scale), max(seen[1], rms.max().item() / scale)
         assert bad.numel() == 0, (f"{model['name']} {dtype} request {rid}: first wrong token at place "
                                   f"{int(bad[0])} (error {err[int(bad[0])]:.3e}, scale {scale:.3e})")
         worst = max(worst, err.max().item() / scale)
@@ -200,3 +210,10 @@ def test_trace_run_program(tmp_path):
         for rid, ids in reqs.items():
             ref = plain.logits(cfg, weights, ids)
             assert (got[rid].double() - ref).abs().max().item() < TOLERANCE[dtype] * ref.abs().max().item()
+
+
+def test_zz_report_measured_errors():
+    """Not a check: prints the largest errors that the tests above saw, per configuration and
+    precision (with -s), the figures the bfloat16 tolerances are taken from."""
+    for key in sorted(MEASURED):
+        print(f"[measured] tiny {key[0]} {key[1]}: largest {MEASURED[key][0]:.3e}, per-position rms {MEASURED[key][1]:.3e}")
