@@ -88,11 +88,11 @@ def assert_no_kernel_gave_up(head_dim):
     ops.raise_on_device_error()
 
 
-def check(model, dtype, steps, out_dir, page, ref=None, max_live=8):
+def check(model, dtype, steps, out_dir, page, ref=None, max_live=8, graphs=False):
     from tinyserve_b200.engine import replay
     ref = ref or model["ref"]
     runner = replay.make_runner(model["folder"], dtype, max_live_tokens(steps, max(64, page)),
-                                block_size=page, max_live=max_live)
+                                block_size=page, max_live=max_live, use_cuda_graphs=graphs)
     done = []
     replay.replay(runner, lines_of(steps), str(out_dir), done.append)
     assert len(done) == len(steps)
@@ -120,6 +120,8 @@ def check(model, dtype, steps, out_dir, page, ref=None, max_live=8):
         worst_max, worst_rms = max(worst_max, e_max.max().item()), max(worst_rms, e_rms.max().item())
     assert_no_kernel_gave_up(model["cfg"]["head_dim"])
     print(f"[measured] {model['name']} {dtype} page {page}: max {worst_max:.3e} rms {worst_rms:.3e}")
+    if graphs:
+        return runner
     return worst_max, worst_rms
 
 
@@ -157,6 +159,21 @@ def test_mixed_with_pages_used_again(model, dtype, page, tmp_path):
     check(model, dtype, steps, tmp_path, page, ref=ref)
     total = sum(-(-len(i) // page) for i in {**reqs, **more}.values())
     assert total > max_live_tokens(steps, max(64, page)) // page, "the pool is too small to avoid reuse"
+
+
+@pytest.mark.parametrize("page", [16, 64])
+def test_steps_with_portions_replayed_from_graphs(model, page, tmp_path):
+    """Steps of up to 512 tokens that hold prompt portions, padded to captured shapes and replayed
+    from graphs (from the second time a shape comes up): the tcgen05 prefill kernel and the decode
+    kernel run over work lists whose unused entries name an empty request."""
+    reqs = dict(model["requests"])
+    more = {f"{rid}x": ids for rid, ids in reqs.items()}
+    ref = {**model["ref"], **{f"{r}x": v for r, v in model["ref"].items()}}
+    steps = schedule_mixed({**reqs, **more}, max_live=4, seed=1, chunk_sizes=(130, 2, 290, 61, 1, 40, 130, 61))
+    runner = check(model, "bfloat16", steps, tmp_path, page, ref=ref, graphs=True)
+    assert runner.mixed_graph_replays > 0, "no step with portions was replayed from a graph"
+    print(f"[measured] {model['name']} page {page}: {runner.mixed_graph_replays} of {len(steps)} steps replayed "
+          f"from {sum(1 for v in runner.mixed_graphs.values() if v != 'seen')} graphs of mixed steps")
 
 
 @pytest.mark.parametrize("graphs", [False, True])

@@ -42,9 +42,10 @@ def model(request, tmp_path_factory):
     return {"name": name, "folder": folder, "cfg": cfg, "weights": weights, "requests": reqs, "ref": ref}
 
 
-def run_replay(folder, dtype, steps, out_dir, max_tokens=None, page=16):
+def run_replay(folder, dtype, steps, out_dir, max_tokens=None, page=16, graphs=False):
     from tinyserve_b200.engine import replay
-    runner = replay.make_runner(folder, dtype, max_tokens or max_live_tokens(steps), block_size=page)
+    runner = replay.make_runner(folder, dtype, max_tokens or max_live_tokens(steps), block_size=page,
+                                use_cuda_graphs=graphs)
     done = []
     replay.replay(runner, lines_of(steps), str(out_dir), done.append)
     assert done == [f"done {s['step']}" for s in steps]
@@ -62,8 +63,8 @@ def run_replay(folder, dtype, steps, out_dir, max_tokens=None, page=16):
     return outputs, runner
 
 
-def check(model, dtype, steps, out_dir, max_tokens=None, page=16):
-    outputs, runner = run_replay(model["folder"], dtype, steps, out_dir, max_tokens, page)
+def check(model, dtype, steps, out_dir, max_tokens=None, page=16, graphs=False):
+    outputs, runner = run_replay(model["folder"], dtype, steps, out_dir, max_tokens, page, graphs)
     got = collect_logits(steps, outputs, model["cfg"]["vocab_size"])
     worst = 0.0
     for rid, ref in model["ref"].items():
@@ -124,6 +125,26 @@ def test_four_schedules_at_pages_of_8(model, dtype, tmp_path):
     for name, steps in (("whole", schedule_whole(reqs)), ("tail", schedule_tail_decode(reqs, 32)),
                         ("portions", schedule_portions(reqs)), ("mixed", schedule_mixed(reqs, max_live=4, seed=2))):
         check(model, dtype, steps, tmp_path / name, page=8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("page", [16, 8])
+def test_steps_with_portions_replayed_from_graphs(model, dtype, page, tmp_path):
+    """With graphs on, a step that holds prompt portions is padded to a captured shape (tokens,
+    requests, logit rows, context bound): the first step of a shape runs eagerly in the padded shape, the
+    second is captured and replayed, later ones are replayed.  The logits stay those of the
+    plain implementation: padding rows, empty requests and unused work-list entries change nothing."""
+    reqs = dict(model["requests"])
+    more = {f"{rid}x": ids for rid, ids in reqs.items()}
+    both = dict(model, ref={**model["ref"], **{f"{r}x": v for r, v in model["ref"].items()}})
+    replays = 0
+    for seed in (0, 1):
+        steps = schedule_mixed({**reqs, **more}, max_live=4, seed=seed)
+        _, runner = check(both, dtype, steps, tmp_path / str(seed), page=page, graphs=True)
+        assert runner.mixed_graphs_enabled
+        replays += runner.mixed_graph_replays
+        assert all(len(k) == 4 for k in runner.mixed_graphs)
+    assert replays > 0, "no step with portions was replayed from a graph"
 
 
 def test_a_bias_that_is_not_zero_reaches_the_logits(tmp_path):

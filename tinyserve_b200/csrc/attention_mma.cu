@@ -765,13 +765,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 }
 
 // out[row] = sum_s 2^(m_s - m) o_s / sum_s 2^(m_s - m) l_s over the key ranges of a row
-// (block x merges partial row x into output row x, or into head x % H of token tokens[x / H])
+// (block x merges partial row x into output row x, or into head x % H of token tokens[x / H];
+// a negative token marks an unused entry of the list)
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          bf16* __restrict__ out, int num_splits, int H,
                                          const int* __restrict__ tokens) {
   pdl_trigger();
   pdl_wait();
   const size_t row = blockIdx.x;
+  if (tokens && tokens[blockIdx.x / H] < 0) return;
   const size_t out_row = tokens ? (size_t)tokens[blockIdx.x / H] * H + blockIdx.x % H : row;
   const float* ml = part_ml + row * num_splits * 2;
   float mx = -INFINITY;

@@ -34,11 +34,19 @@ _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 PENDING = -1     # a token id that is still on the device (see ModelRunner.slot_tokens)
 
 
-class Prepared:
-    """A packed step that waits for its launch."""
+# Token counts for which steps that hold prompt portions are captured as graphs: above the
+# largest a step is busy enough with arithmetic that its launches hardly matter, and runs eagerly
+# (tinyserve's buckets are every 16 tokens up to 512, serve.py:1951-1962).
+MIXED_GRAPH_TOKENS = (16, 32, 48, 64, 96, 128, 192, 256, 384, 512)
+MIXED_GRAPHS_KEPT = 32           # captured shapes kept; the one replayed longest ago goes first
 
-    def __init__(self, entries, ctx, graph, buf):
-        self.entries, self.ctx, self.graph, self.buf = entries, ctx, graph, buf
+
+class Prepared:
+    """A packed step that waits for its launch.  ``graph``: the captured decode graph it
+    replays; ``mixed``: the captured shape (tokens, requests, logit rows, context bound) it was padded to."""
+
+    def __init__(self, entries, ctx, graph, buf, mixed=None):
+        self.entries, self.ctx, self.graph, self.buf, self.mixed = entries, ctx, graph, buf, mixed
 
 
 class _Runtime:
@@ -71,6 +79,11 @@ class ModelRunner:
         self.manager = CacheManager(groups, self.num_pages, self.page_size, cfg.max_num_seqs)
         self._make_buffers()
         self.graphs: dict = {}
+        # graphs of steps with prompt portions, captured when a shape comes up the second time
+        self.mixed_graphs: dict = {}
+        self.mixed_graphs_enabled = False
+        self.mixed_graph_replays = 0
+        self._graph_pool = None
         self.kernel_launches = 0
         self.last_upload_bytes = 0
         if verbose:
@@ -118,14 +131,15 @@ class ModelRunner:
         G = len(self.model.cache_groups)
         self._tile_sizes = sorted({q for block in self.model.blocks
                                    for q in [block.mixer.work_tile_queries(self.dtype, self.page_size)] if q > 0})
-        sizes = [("meta", 4), ("cu_q", S + 1), ("kv_lens", S), ("state_slots", S), ("fresh", S),
+        # (one request more than max_num_seqs: a captured mixed shape always ends in an empty one)
+        sizes = [("meta", 4), ("cu_q", S + 2), ("kv_lens", S + 1), ("state_slots", S + 1), ("fresh", S + 1),
                  ("token_ids", N), ("positions", N), ("logit_rows", N)]
         for g in range(G):
             sizes.append((f"slot_mapping{g}", N))
         for q in self._tile_sizes:
-            sizes += [(f"tile_req{q}", N // q + S), (f"tile_q0{q}", N // q + S)]
+            sizes += [(f"tile_req{q}", N // q + S + 1), (f"tile_q0{q}", N // q + S + 1)]
         if self._tile_sizes:
-            sizes += [("dec_req", S), ("dec_tok", S)]
+            sizes += [("dec_req", S + 1), ("dec_tok", S + 1)]
         self._offsets, total = {}, 0
         for name, n in sizes:
             self._offsets[name] = (total, n)
@@ -144,7 +158,7 @@ class ModelRunner:
         # block tables: a resident row per state slot (and a spare row of null pages), the rows of the
         # step's requests gathered from them
         self._resident_tables = torch.zeros(max(G, 1), S + 1, self.max_blocks, dtype=torch.int32, device=self.device)
-        self._step_tables = torch.zeros(max(G, 1), S, self.max_blocks, dtype=torch.int32, device=self.device)
+        self._step_tables = torch.zeros(max(G, 1), S + 1, self.max_blocks, dtype=torch.int32, device=self.device)
         # last sampled token of every state slot (one spare entry for rows nobody waits for)
         self.slot_tokens = torch.zeros(S + 1, dtype=torch.int32, device=self.device)
 
@@ -153,17 +167,23 @@ class ModelRunner:
         return buf[off:off + (cap if n is None else n)]
 
     # ------------------------------------------------------------------ packing
-    def _pack(self, entries, buf=0, pad_requests=0, pad_tokens=0):
-        """Fill host staging buffer ``buf``; returns a StepContext without device work."""
+    def _pack(self, entries, buf=0, pad_requests=0, pad_tokens=0, shape=None):
+        """Fill host staging buffer ``buf``; returns a StepContext without device work.
+        ``shape`` = (tokens, requests, logit rows, context bound) packs a step with prompt portions as the
+        captured shape of that size: token rows and requests padded, the attention work lists
+        filled up to their capacity with entries that name the last (empty) request, and the
+        context's maxima set to the shape's, so that every launch has the shape's grid."""
         cfg, mgr, ps = self.cfg, self.manager, self.page_size
         B = len(entries)
         T = sum(len(e.tokens) for e in entries)
         if B == 0 or T == 0:
             raise ValueError("a step needs at least one token")
+        if shape is not None:
+            pad_tokens, pad_requests = shape[0], shape[1]
         Bp, Tp = max(B, pad_requests), max(T, pad_tokens)
         if Tp > cfg.max_num_batched_tokens:
             raise ValueError(f"{Tp} tokens in one step, max_num_batched_tokens is {cfg.max_num_batched_tokens}")
-        if Bp > cfg.max_num_seqs:
+        if B > cfg.max_num_seqs or Bp > cfg.max_num_seqs + (shape is not None):
             raise ValueError(f"{Bp} requests in one step, max_num_seqs is {cfg.max_num_seqs}")
         h = self._hosts_np[buf]
         seg = lambda name, n=None: self._seg(h, name, n)
@@ -255,8 +275,27 @@ class ModelRunner:
                 seg(f"tile_q0{q}")[:nt] = tile_q0
                 seg("dec_req")[:nd] = dec_req
                 seg("dec_tok")[:nd] = dec_tok
+                if shape is not None:
+                    # the captured shape's lists: what is left of them names the empty last request
+                    cap_t, cap_d = self._mixed_tiles(Tp, Bp, q), Bp
+                    seg(f"tile_req{q}")[nt:cap_t] = Bp - 1
+                    seg(f"tile_q0{q}")[nt:cap_t] = 0
+                    seg("dec_req")[nd:cap_d] = Bp - 1
+                    seg("dec_tok")[nd:cap_d] = -1
+                    nt, nd, longest = cap_t, cap_d, shape[3]
                 ctx.host["work"][q] = (nt, nd, longest)
+        if shape is not None:
+            assert w <= shape[2] and B < Bp
+            rows[w:shape[2]] = 0
+            ctx.num_logit_rows = shape[2]
+            ctx.max_q_len, ctx.max_kv_len = Tp, shape[3]
         return ctx
+
+    @staticmethod
+    def _mixed_tiles(tokens, requests, queries_per_tile):
+        """Most blocks of ``queries_per_tile`` queries that ``tokens`` tokens of up to ``requests``
+        requests are cut into (every request may end in a block that is not full)."""
+        return tokens // queries_per_tile + min(requests, tokens // 2 + 1)
 
     def _bind_device_views(self, ctx):
         d = self._dev
@@ -347,6 +386,7 @@ class ModelRunner:
         request's last sampled token, which the device still holds."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         graph = self._graph_for(entries)
+        mixed = self._mixed_shape_for(entries) if graph is None else None
         buf, self._next_buf = self._next_buf, self._next_buf ^ 1
         if self._copied[buf] is not None:
             # the host may run several steps ahead of the device (nobody has to read a result
@@ -357,16 +397,19 @@ class ModelRunner:
             ctx = self._pack(entries, buf, pad_requests=size, pad_tokens=size)
             self._seg(self._hosts_np[buf], "logit_rows")[:size] = np.arange(size, dtype=np.int32)
         else:
-            ctx = self._pack(entries, buf)
+            ctx = self._pack(entries, buf, shape=mixed)
         if self.cfg.check_indices:
             self._check_host(ctx, buf)
-        return Prepared(entries, ctx, graph, buf)
+        return Prepared(entries, ctx, graph, buf, mixed)
 
     @torch.inference_mode()
     def launch(self, prep: Prepared):
         """Upload and run a prepared step; its tokens are computed afterwards."""
         # (a captured graph holds the block-table kernels itself: only the copy happens here)
-        if prep.graph is not None:
+        captured = prep.graph
+        if prep.mixed is not None:
+            captured = self._mixed_graph(prep)       # None when the shape comes up for the first time
+        if captured is not None:
             self._copy_in(prep.buf)
         else:
             self._upload(prep.buf, prep.ctx.num_requests)
@@ -380,14 +423,18 @@ class ModelRunner:
             # a request that starts in this step finds its state slot zeroed, whoever held it before
             host = prep.ctx.host
             self.device_cache.zero_state([s for s, f in zip(host["state_slots"], host["fresh"]) if f])
-        if prep.graph is not None:
-            graph, out, size, launches = prep.graph
+        if captured is not None:
+            graph, out, size, launches = captured
             graph.replay()
             ops.count_launches(launches)
-            logits = out[:len(prep.entries)]
+            wanted = len(prep.entries) if prep.mixed is None else sum(len(e.want) for e in prep.entries)
+            logits = out[:wanted] if wanted else None
         else:
             with ops.stream_scope():
                 logits = self._forward(self._bind_device_views(prep.ctx))
+            if prep.mixed is not None:
+                wanted = sum(len(e.want) for e in prep.entries)
+                logits = logits[:wanted] if wanted else None
         for e in prep.entries:
             if self.manager.is_live(e.rid):      # a request may have ended since it was packed
                 self.manager.commit(e.rid, len(e.tokens))
@@ -445,6 +492,56 @@ class ModelRunner:
                 return None
         return None
 
+    # ------------------------------------------------------------------ graphs of mixed steps
+    def _mixed_shape_for(self, entries):
+        """The captured shape (tokens, requests, logit rows, context bound) that a step with prompt
+        portions is padded to, or None where it runs as it is: graphs are off, or the step is
+        larger than the largest captured token count.  Logit rows: one per request (what serving
+        asks for) or, where more are wanted, one per token."""
+        if not self.mixed_graphs_enabled:
+            return None
+        T = sum(len(e.tokens) for e in entries)
+        B = len(entries)
+        tokens = next((t for t in MIXED_GRAPH_TOKENS if t >= T), None)
+        if tokens is None or tokens > self.cfg.max_num_batched_tokens or B > self.cfg.max_num_seqs:
+            return None
+        # one request more than the step holds: the empty one that unused work-list entries name
+        S = self.cfg.max_num_seqs
+        requests = next((r for r in (2, 4, 8, 16, 32, 64, 128, 256, 512, 1024) if B < r <= S), S + 1)
+        rows = requests if sum(len(e.want) for e in entries) <= requests else tokens
+        mgr = self.manager
+        longest = max(mgr.num_computed(e.rid) + len(e.tokens) for e in entries)
+        bound = next((b for b in self.context_bounds() if b >= longest), None)
+        return None if bound is None else (tokens, requests, rows, bound)
+
+    def _mixed_graph(self, prep):
+        """The graph of ``prep``'s captured shape.  The first step of a shape runs eagerly, in the
+        padded shape (which is also the warm-up that a capture needs); the second is captured,
+        with its own inputs on the device, and replayed; later ones are replayed."""
+        key = prep.mixed
+        seen = self.mixed_graphs.get(key)
+        if seen is None:
+            self.mixed_graphs[key] = "seen"
+            return None
+        if seen == "seen":
+            tokens, requests = key[0], key[1]
+            ctx = self._bind_device_views(prep.ctx)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph, pool=self._graph_pool), ops.stream_scope():
+                self._tables_step(requests)
+                out = self._forward(ctx)
+            self._graph_pool = self._graph_pool or graph.pool()
+            seen = (graph, out, tokens, ops.launch_count() - before)
+            captured = [k for k, v in self.mixed_graphs.items() if v != "seen"]
+            if len(captured) >= MIXED_GRAPHS_KEPT:
+                del self.mixed_graphs[captured[0]]
+        # (the dict keeps the order of insertion: a replayed shape moves to the end)
+        self.mixed_graphs.pop(key, None)
+        self.mixed_graphs[key] = seen
+        self.mixed_graph_replays += 1
+        return seen
+
     @torch.inference_mode()
     def capture_decode_graphs(self, sizes=None):
         """Capture one graph per decode batch size and context bound: every request brings one
@@ -453,9 +550,10 @@ class ModelRunner:
         which a replay would not refresh) is not captured: every step then runs eagerly."""
         if not self.model.capturable:
             return 0
+        self.mixed_graphs_enabled = True
         sizes = sorted(sizes or self.decode_buckets(), reverse=True)
         bounds = self.context_bounds()
-        pool = None
+        pool = self._graph_pool
         dummy = "__capture__"
         self.manager.begin(dummy)
         try:
@@ -480,7 +578,7 @@ class ModelRunner:
                 with torch.cuda.graph(graph, pool=pool), ops.stream_scope():
                     self._tables_step(size)           # every replay applies its step's block-table changes
                     out = self._forward(ctx)
-                pool = pool or graph.pool()
+                pool = self._graph_pool = pool or graph.pool()
                 self.graphs[(size, bound)] = (graph, out, size, ops.launch_count() - before)
         finally:
             self.manager.free(dummy)
