@@ -614,6 +614,77 @@ def test_product_with_residual_add_and_scaled_rows(M, N, K, wdtype):
     assert o.gemm_tcgen05_error() == 0
 
 
+# ----------------------------------------------------------------------------- paired tcgen05 product
+# (sizes: one tile and less; ragged edges in M, N and K; many tiles with a last wave that is cut
+# along K for 74, 5 and 3 pairs; a K of one slice)
+PAIR_SHAPES = [(65, 136, 72), (128, 256, 64), (130, 264, 520), (256, 512, 4096), (300, 1000, 136),
+               (700, 2048, 1024), (1000, 4096, 512), (2048, 1536, 256)]
+
+
+@pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
+@pytest.mark.parametrize("pairs", [74, 5, 3])
+@pytest.mark.parametrize("f32_out,with_bias", [(False, False), (True, True), (False, True)])
+def test_gemm_pair(M, N, K, pairs, f32_out, with_bias):
+    o = ops()
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
+    bias = rnd(N, seed=3, dtype=torch.bfloat16 if M % 2 else torch.float32, scale=3.0) if with_bias else None
+    out = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs)
+    torch.cuda.synchronize()
+    assert o.gemm_pair_error() == 0, "a block gave up on a wait"
+    want = x.double() @ w.double().T + (bias.double() if with_bias else 0)
+    close(out, want, torch.float32 if f32_out else torch.bfloat16, "paired gemm")
+    # (the four issuing threads add into one accumulator in whatever order the tensor core takes
+    # their instructions: two runs agree to the rounding of a 32-bit sum, not bit by bit)
+    again = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs)
+    close(again, want, torch.float32 if f32_out else torch.bfloat16, "paired gemm, second run")
+    if f32_out:
+        assert (again - out).abs().max().item() <= 1e-5 * want.abs().max().item()
+    assert int(o._pair_scratch[str(x.device)][1].abs().sum()) == 0, "tile counters returned to zero"
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 128, 72), (200, 384, 520), (512, 1024, 1024), (1100, 6144, 256)])
+@pytest.mark.parametrize("pairs", [74, 3])
+@pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
+def test_gemm_pair_gated(M, N, K, pairs, activation):
+    """Weight rows alternate in blocks of 64 (gate, up); the epilogue applies act(gate) * up."""
+    o = ops()
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
+    out = o._linear_pair(x, w, gated=o.ACTIVATIONS[activation] + 1, pairs=pairs)
+    torch.cuda.synchronize()
+    assert o.gemm_pair_error() == 0
+    full = (x.double() @ w.double().T).view(M, N // 128, 2, 64)
+    gate, up = full[:, :, 0].reshape(M, N // 2), full[:, :, 1].reshape(M, N // 2)
+    act = torch.nn.functional.silu(gate) if activation == "silu" else torch.nn.functional.gelu(gate, approximate="tanh")
+    close(out, act * up, torch.bfloat16, "gated paired gemm")
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 136, 72), (256, 4096, 1024), (300, 1000, 520), (1030, 2048, 256)])
+@pytest.mark.parametrize("pairs", [74, 3])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_gemm_pair_residual_and_scaled_rows(M, N, K, pairs, wdtype):
+    """The residual form (residual += x w^T in 32-bit, rows residual * norm weight and their sums
+    of squares) and the forms that take such rows and scale their result by the norm factor."""
+    o = ops()
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
+    res = rnd(M, N, seed=3, scale=2.0)
+    wn = rnd(N, seed=4, dtype=wdtype) + 1
+    eps = 1e-5
+    r1 = res.clone()
+    hprime, sumsq = o._linear_pair(x, w, residual=r1, norm_weight=wn, pairs=pairs)
+    rows = o.ScaledRows(hprime, sumsq, -(-N // 128), eps)
+    v = res.double().cpu() + x.double().cpu() @ w.double().cpu().T
+    assert (r1.double().cpu() - v).abs().max().item() < 1e-5 * max(1.0, v.abs().max().item()), "32-bit residual"
+    want = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps) * wn.double().cpu()
+    close(rows.materialize(), want, torch.bfloat16, "normalised rows")
+    normed = rows.materialize().double().cpu()
+    w2 = rnd(384, N, seed=7, dtype=torch.bfloat16, scale=0.1)
+    close(o._linear_pair(hprime, w2, scale=rows, pairs=pairs), normed @ w2.double().cpu().T, torch.bfloat16, "scaled product")
+    full = (normed @ w2.double().cpu().T).view(M, 3, 2, 64)
+    gated = torch.nn.functional.silu(full[:, :, 0].reshape(M, 192)) * full[:, :, 1].reshape(M, 192)
+    close(o._linear_pair(hprime, w2, scale=rows, gated=1, pairs=pairs), gated, torch.bfloat16, "scaled gated product")
+    assert o.gemm_pair_error() == 0
+
+
 @pytest.mark.parametrize("M,N,K,splits", [(8, 4096, 1024, 4), (3, 328, 512, 2), (16, 6144, 512, 3), (40, 640, 256, 2)])
 def test_split_partials_and_their_consumers(M, N, K, splits):
     """A product may stop at its split-K partial tiles; the next kernel adds them while it loads."""

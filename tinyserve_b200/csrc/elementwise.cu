@@ -471,23 +471,24 @@ TS_EXPORT int ts_rmsnorm(int dtype, const void* x, const void* weight, int weigh
 
 // ------------------------------------------------------------------ rows without their norm factor -> rows
 // out[m, :] = x[m, :] * rsqrt(sum_t sumsq[t][m] / n + eps): the normalised rows of what the residual
-// form of the tcgen05 product leaves (x = residual * norm_weight, sums of residual^2 per 128 columns)
+// forms of the tcgen05 products leave (x = residual * norm_weight, sums of residual^2 per 128
+// columns, `stride` floats apart)
 __global__ void scale_rows_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ sumsq, int tiles,
-                                  float eps, __nv_bfloat16* __restrict__ out, int n) {
+                                  int stride, float eps, __nv_bfloat16* __restrict__ out, int n) {
   pdl_trigger();
   pdl_wait();
   const int m = blockIdx.x;
   float sum = 0.f;
-  for (int t = 0; t < tiles; ++t) sum += sumsq[(size_t)t * 16 + m];
+  for (int t = 0; t < tiles; ++t) sum += sumsq[(size_t)t * stride + m];
   const float rstd = rsqrtf(sum / (float)n + eps);
   for (int c = threadIdx.x; c < n; c += blockDim.x)
     out[(size_t)m * n + c] = __float2bfloat16_rn(__bfloat162float(x[(size_t)m * n + c]) * rstd);
 }
 
-TS_EXPORT int ts_scale_rows(const void* x, const float* sumsq, int tiles, float eps, void* out, int M, int n,
-                            cudaStream_t stream) {
-  TS_REQUIRE(M > 0 && M <= 16 && n > 0 && tiles > 0, "scale_rows: up to 16 rows with their sums of squares");
-  TS_LAUNCH("scale_rows", scale_rows_kernel, M, 256, 0, stream, (const __nv_bfloat16*)x, sumsq, tiles, eps,
+TS_EXPORT int ts_scale_rows(const void* x, const float* sumsq, int tiles, int stride, float eps, void* out, int M,
+                            int n, cudaStream_t stream) {
+  TS_REQUIRE(M > 0 && M <= stride && n > 0 && tiles > 0, "scale_rows: rows with their sums of squares, at most `stride` of them");
+  TS_LAUNCH("scale_rows", scale_rows_kernel, M, 256, 0, stream, (const __nv_bfloat16*)x, sumsq, tiles, stride, eps,
             (__nv_bfloat16*)out, n);
   return 0;
 }

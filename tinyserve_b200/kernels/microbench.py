@@ -1,6 +1,7 @@
 """Time one kernel of the package at a given size, after warm-up, with CUDA events.
 
     python -m tinyserve_b200.kernels.microbench gemm --m 8 --n 24576 --k 4096 [--splits S] [--impl tcgen05|cublas]
+    python -m tinyserve_b200.kernels.microbench gemm --m 2048 --n 24576 --k 4096 --impl pair [--mode plain|gated|residual]
     python -m tinyserve_b200.kernels.microbench attention --batch 8 --q-len 1 --kv-len 640
     python -m tinyserve_b200.kernels.microbench norm --rows 8 --n 4096
     python -m tinyserve_b200.kernels.microbench rope --rows 2048
@@ -53,10 +54,18 @@ def bench_gemm(a):
     splits = a.splits or ops.gemm_splits(a.m, a.n, a.k)
     if a.impl.startswith("tcgen05"):
         fn = lambda i: ops._linear_tcgen05(x, ws[i], False, splits=splits, partials_only=a.partials_only)
+    elif a.impl == "pair":
+        # the paired kernel for many tokens, with the epilogue that the engine uses at this place
+        res = torch.randn(a.m, a.n, device="cuda") if a.mode == "residual" else None
+        wn = torch.ones(a.n, device="cuda", dtype=torch.bfloat16)
+        if a.mode == "residual":
+            fn = lambda i: ops._linear_pair(x, ws[i], residual=res, norm_weight=wn, pairs=a.pairs or None)
+        else:
+            fn = lambda i: ops._linear_pair(x, ws[i], gated=1 if a.mode == "gated" else 0, pairs=a.pairs or None)
     else:
         fn = lambda i: torch.mm(x, ws[i].t())
     us = _time(fn, copies, a.iters, a.graph)
-    err = ops.gemm_tcgen05_error() if a.impl.startswith("tcgen05") else 0
+    err = ops.gemm_tcgen05_error() if a.impl.startswith("tcgen05") else ops.gemm_pair_error() if a.impl == "pair" else 0
     return {"kernel": f"gemm_{a.impl}", "m": a.m, "n": a.n, "k": a.k, "splits": splits if a.impl.startswith("tcgen05") else None,
             "us": round(us, 2), "gbs": round((nbytes + a.m * (a.n + a.k) * 2) / us / 1e3, 1),
             "tflops": round(2.0 * a.m * a.n * a.k / us / 1e6, 2), "error_flag": err}
@@ -131,7 +140,9 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=24576)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--impl", choices=["tcgen05", "cublas"], default="tcgen05")
+    ap.add_argument("--impl", choices=["tcgen05", "cublas", "pair"], default="tcgen05")
+    ap.add_argument("--mode", choices=["plain", "gated", "residual"], default="plain", help="epilogue of --impl pair")
+    ap.add_argument("--pairs", type=int, default=0, help="pairs of blocks of --impl pair (default: all the device holds)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--q-len", type=int, default=1)
     ap.add_argument("--kv-len", type=int, default=640)

@@ -166,13 +166,21 @@ class ScaledRows:
         self.data, self.sumsq, self.tiles, self.eps = data, sumsq, tiles, eps
         self.shape, self.dtype, self.device = tuple(data.shape), data.dtype, data.device
 
+    @property
+    def stride(self):
+        """Tokens a tile's sums are apart: 16 from the product for few tokens, more from the paired one."""
+        return self.sumsq.shape[1]
+
     def args(self):
         return (_ptr(self.sumsq), c_int(self.tiles), c_float(self.eps))
+
+    def args_wide(self):
+        return (_ptr(self.sumsq), c_int(self.tiles), c_int(self.stride), c_float(self.eps))
 
     def materialize(self):
         out = torch.empty_like(self.data)
         lib = _elementwise()
-        _check(lib, lib.ts_scale_rows(_ptr(self.data), *self.args(), _ptr(out), c_int(self.shape[0]),
+        _check(lib, lib.ts_scale_rows(_ptr(self.data), *self.args_wide(), _ptr(out), c_int(self.shape[0]),
                                       c_int(self.shape[1]), _stream()))
         return out
 
@@ -357,6 +365,78 @@ def _linear_tcgen05(x, weight, out_float32, splits=None, partials_only=False, sc
     return out
 
 
+def _gemm_pair():
+    return build.load_unit("gemm_pair_tcgen05.cu")
+
+
+def gemm_pair_error() -> int:
+    """1 if a block of the paired tcgen05 kernel ever gave up on a wait (synchronises)."""
+    return _gemm_pair().ts_gemm_pair_error()
+
+
+_pair_scratch: dict = {}
+_pair_count: list = []
+
+
+def gemm_pairs() -> int:
+    """Pairs of blocks of the paired product that the device holds at once (74 on a B200 with all
+    148 SMs in pairs)."""
+    if not _pair_count:
+        n = _gemm_pair().ts_gemm_pair_max_pairs()
+        _pair_count.append(n if n > 0 else num_sms() // 2)
+    return _pair_count[0]
+
+
+def _pair_workspace(lib, M, N, K, pairs, device):
+    """Scratch for the partial tiles of the last wave and their (zeroed) counters.  One buffer per
+    device, grown on demand: products of one stream run one after the other."""
+    counters = c_int(0)
+    lib.ts_gemm_pair_scratch.restype = c_longlong
+    need = lib.ts_gemm_pair_scratch(c_int(M), c_int(N), c_int(K), c_int(pairs), ctypes.byref(counters))
+    key = str(device)
+    have = _pair_scratch.get(key)
+    if have is None or have[0].numel() < need or have[1].numel() < counters.value:
+        grow = max(need, have[0].numel() if have else 0, 1)
+        have = (torch.empty(grow, dtype=torch.float32, device=device),
+                torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=device))
+        _pair_scratch[key] = have
+    return have
+
+
+def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, residual=None, norm_weight=None,
+                 pairs=None):
+    """The product for many tokens on pairs of SMs (csrc/gemm_pair_tcgen05.cu).  Plain: returns
+    out [M, N]; ``bias`` [N]; ``scale`` the ScaledRows whose ``data`` is ``x``.  ``gated``:
+    activation code + 1, out [M, N / 2].  ``residual`` (float32 [M, N], in place) with
+    ``norm_weight``: returns (hprime, sumsq) of the new residual."""
+    M, K = x.shape
+    N = weight.shape[0]
+    lib = _gemm_pair()
+    pairs = pairs or gemm_pairs()
+    scratch, counters = _pair_workspace(lib, M, N, K, pairs, x.device)
+    out = hprime = sumsq = None
+    stride = -(-M // 4) * 4
+    if residual is not None:
+        hprime = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        sumsq = torch.empty(-(-N // 128), stride, dtype=torch.float32, device=x.device)
+    else:
+        out = torch.empty(M, N // 2 if gated else N, dtype=torch.float32 if out_float32 else torch.bfloat16,
+                          device=x.device)
+    _check(lib, lib.ts_gemm_pair(
+        _ptr(x), _ptr(weight), _ptr(out), c_int(M), c_int(N), c_int(K), c_longlong(x.stride(0)),
+        c_longlong(weight.stride(0)), c_longlong(out.stride(0) if out is not None else 0),
+        c_int(1 if out_float32 else 0), _ptr(bias),
+        c_int(_vec_flag(bias, torch.bfloat16) if bias is not None else 0),
+        *(scale.args_wide() if scale is not None else (c_void_p(0), c_int(0), c_int(0), c_float(0.0))),
+        c_int(gated), _ptr(residual), _ptr(norm_weight),
+        c_int(_vec_flag(norm_weight, torch.bfloat16) if norm_weight is not None else 0), _ptr(hprime), _ptr(sumsq),
+        c_int(stride), _ptr(scratch), c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()),
+        c_int(pairs), _stream()))
+    if residual is not None:
+        return hprime, sumsq
+    return out
+
+
 def _attention(head_dim: int):
     if head_dim not in SUPPORTED_HEAD_DIMS:
         raise ValueError(f"head size {head_dim} is not supported: attention takes multiples of 16 "
@@ -388,7 +468,8 @@ def _sampler():
 
 def units_for(head_dims) -> list:
     """The (source, defines) units a model with these head sizes needs."""
-    units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("sampler.cu", {})]
+    units = [("elementwise.cu", {}), ("gemm_simt.cu", {}), ("gemm_tcgen05.cu", {}), ("gemm_pair_tcgen05.cu", {}),
+             ("sampler.cu", {})]
     units += [("attention_simt.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))]
     units += [("attention_mma.cu", {"TS_HEAD_DIM": d}) for d in sorted(set(head_dims))
               if d <= MMA_MAX_HEAD_DIM]
