@@ -623,19 +623,20 @@ PAIR_SHAPES = [(65, 136, 72), (128, 256, 64), (130, 264, 520), (256, 512, 4096),
 
 @pytest.mark.parametrize("M,N,K", PAIR_SHAPES)
 @pytest.mark.parametrize("pairs", [74, 5, 3])
+@pytest.mark.parametrize("halves", [1, 2])
 @pytest.mark.parametrize("f32_out,with_bias", [(False, False), (True, True), (False, True)])
-def test_gemm_pair(M, N, K, pairs, f32_out, with_bias):
+def test_gemm_pair(M, N, K, pairs, halves, f32_out, with_bias):
     o = ops()
     x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
     bias = rnd(N, seed=3, dtype=torch.bfloat16 if M % 2 else torch.float32, scale=3.0) if with_bias else None
-    out = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs)
+    out = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs, halves=halves)
     torch.cuda.synchronize()
     assert o.gemm_pair_error() == 0, "a block gave up on a wait"
     want = x.double() @ w.double().T + (bias.double() if with_bias else 0)
     close(out, want, torch.float32 if f32_out else torch.bfloat16, "paired gemm")
     # (the four issuing threads add into one accumulator in whatever order the tensor core takes
     # their instructions: two runs agree to the rounding of a 32-bit sum, not bit by bit)
-    again = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs)
+    again = o._linear_pair(x, w, f32_out, bias=bias, pairs=pairs, halves=halves)
     close(again, want, torch.float32 if f32_out else torch.bfloat16, "paired gemm, second run")
     if f32_out:
         assert (again - out).abs().max().item() <= 1e-5 * want.abs().max().item()
@@ -644,12 +645,13 @@ def test_gemm_pair(M, N, K, pairs, f32_out, with_bias):
 
 @pytest.mark.parametrize("M,N,K", [(65, 128, 72), (200, 384, 520), (512, 1024, 1024), (1100, 6144, 256)])
 @pytest.mark.parametrize("pairs", [74, 3])
+@pytest.mark.parametrize("halves", [1, 2])
 @pytest.mark.parametrize("activation", ["silu", "gelu_tanh"])
-def test_gemm_pair_gated(M, N, K, pairs, activation):
+def test_gemm_pair_gated(M, N, K, pairs, halves, activation):
     """Weight rows alternate in blocks of 64 (gate, up); the epilogue applies act(gate) * up."""
     o = ops()
     x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.1)
-    out = o._linear_pair(x, w, gated=o.ACTIVATIONS[activation] + 1, pairs=pairs)
+    out = o._linear_pair(x, w, gated=o.ACTIVATIONS[activation] + 1, pairs=pairs, halves=halves)
     torch.cuda.synchronize()
     assert o.gemm_pair_error() == 0
     full = (x.double() @ w.double().T).view(M, N // 128, 2, 64)
@@ -659,9 +661,9 @@ def test_gemm_pair_gated(M, N, K, pairs, activation):
 
 
 @pytest.mark.parametrize("M,N,K", [(65, 136, 72), (256, 4096, 1024), (300, 1000, 520), (1030, 2048, 256)])
-@pytest.mark.parametrize("pairs", [74, 3])
+@pytest.mark.parametrize("pairs,halves", [(74, 1), (74, 2), (3, 1), (3, 2), (74, 0)])
 @pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
-def test_gemm_pair_residual_and_scaled_rows(M, N, K, pairs, wdtype):
+def test_gemm_pair_residual_and_scaled_rows(M, N, K, pairs, halves, wdtype):
     """The residual form (residual += x w^T in 32-bit, rows residual * norm weight and their sums
     of squares) and the forms that take such rows and scale their result by the norm factor."""
     o = ops()
@@ -670,7 +672,7 @@ def test_gemm_pair_residual_and_scaled_rows(M, N, K, pairs, wdtype):
     wn = rnd(N, seed=4, dtype=wdtype) + 1
     eps = 1e-5
     r1 = res.clone()
-    hprime, sumsq = o._linear_pair(x, w, residual=r1, norm_weight=wn, pairs=pairs)
+    hprime, sumsq = o._linear_pair(x, w, residual=r1, norm_weight=wn, pairs=pairs, halves=halves)
     rows = o.ScaledRows(hprime, sumsq, -(-N // 128), eps)
     v = res.double().cpu() + x.double().cpu() @ w.double().cpu().T
     assert (r1.double().cpu() - v).abs().max().item() < 1e-5 * max(1.0, v.abs().max().item()), "32-bit residual"
@@ -678,10 +680,10 @@ def test_gemm_pair_residual_and_scaled_rows(M, N, K, pairs, wdtype):
     close(rows.materialize(), want, torch.bfloat16, "normalised rows")
     normed = rows.materialize().double().cpu()
     w2 = rnd(384, N, seed=7, dtype=torch.bfloat16, scale=0.1)
-    close(o._linear_pair(hprime, w2, scale=rows, pairs=pairs), normed @ w2.double().cpu().T, torch.bfloat16, "scaled product")
+    close(o._linear_pair(hprime, w2, scale=rows, pairs=pairs, halves=halves), normed @ w2.double().cpu().T, torch.bfloat16, "scaled product")
     full = (normed @ w2.double().cpu().T).view(M, 3, 2, 64)
     gated = torch.nn.functional.silu(full[:, :, 0].reshape(M, 192)) * full[:, :, 1].reshape(M, 192)
-    close(o._linear_pair(hprime, w2, scale=rows, gated=1, pairs=pairs), gated, torch.bfloat16, "scaled gated product")
+    close(o._linear_pair(hprime, w2, scale=rows, gated=1, pairs=pairs, halves=halves), gated, torch.bfloat16, "scaled gated product")
     assert o.gemm_pair_error() == 0
 
 

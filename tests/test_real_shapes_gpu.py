@@ -161,6 +161,19 @@ def test_mixed_with_pages_used_again(model, dtype, page, tmp_path):
     assert total > max_live_tokens(steps, max(64, page)) // page, "the pool is too small to avoid reuse"
 
 
+def test_products_of_many_tokens_on_the_paired_kernel(model, tmp_path, monkeypatch):
+    """Every product of a step of more than 64 tokens on the paired tcgen05 kernel, with the
+    residual add, the norm factor and the gated activation in the products' epilogues (the engine
+    itself takes only the gate/up product of long prompts there): whole prompts and portions."""
+    from tinyserve_b200.kernels import ops
+    monkeypatch.setattr(ops, "PAIR_MIN_TOKENS", 65)
+    monkeypatch.setattr(ops, "PAIR_GATED_MIN_TOKENS", 65)
+    check(model, "bfloat16", schedule_whole(model["requests"]), tmp_path / "whole", 64)
+    check(model, "bfloat16", schedule_portions(model["requests"], sizes=(170, 9, 65, 3, 2, 128, 2, 31, 257)),
+          tmp_path / "portions", 16)
+    assert ops.gemm_pair_error() == 0
+
+
 @pytest.mark.parametrize("page", [16, 64])
 def test_steps_with_portions_replayed_from_graphs(model, page, tmp_path):
     """Steps of up to 512 tokens that hold prompt portions, padded to captured shapes and replayed

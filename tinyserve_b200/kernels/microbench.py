@@ -59,9 +59,9 @@ def bench_gemm(a):
         res = torch.randn(a.m, a.n, device="cuda") if a.mode == "residual" else None
         wn = torch.ones(a.n, device="cuda", dtype=torch.bfloat16)
         if a.mode == "residual":
-            fn = lambda i: ops._linear_pair(x, ws[i], residual=res, norm_weight=wn, pairs=a.pairs or None)
+            fn = lambda i: ops._linear_pair(x, ws[i], residual=res, norm_weight=wn, pairs=a.pairs or None, halves=a.halves)
         else:
-            fn = lambda i: ops._linear_pair(x, ws[i], gated=1 if a.mode == "gated" else 0, pairs=a.pairs or None)
+            fn = lambda i: ops._linear_pair(x, ws[i], gated=1 if a.mode == "gated" else 0, pairs=a.pairs or None, halves=a.halves)
     else:
         fn = lambda i: torch.mm(x, ws[i].t())
     us = _time(fn, copies, a.iters, a.graph)
@@ -142,6 +142,7 @@ def main(argv=None):
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--impl", choices=["tcgen05", "cublas", "pair"], default="tcgen05")
     ap.add_argument("--mode", choices=["plain", "gated", "residual"], default="plain", help="epilogue of --impl pair")
+    ap.add_argument("--halves", type=int, default=0, help="--impl pair: tiles of 256 (1) or 512 (2) weight rows, 0: by estimate")
     ap.add_argument("--pairs", type=int, default=0, help="pairs of blocks of --impl pair (default: all the device holds)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--q-len", type=int, default=1)

@@ -135,11 +135,12 @@ class PendingProduct:
     for a few tokens, because the residual add + norm that usually follows can run in the
     product's own kernel: ``add_rmsnorm`` then launches the residual form of the tcgen05 kernel
     (the K cuts of a row tile are a thread-block cluster; they add their partial sums through
-    distributed shared memory, add the residual and leave a ScaledRows).  Any other consumer
-    calls ``partials()`` or ``materialize()`` and gets the ordinary product."""
+    distributed shared memory, add the residual and leave a ScaledRows).  For many tokens
+    (``wide``) the paired kernel has the same form.  Any other consumer calls ``partials()`` or
+    ``materialize()`` and gets the ordinary product."""
 
-    def __init__(self, x, weight):
-        self.x, self.weight = x, weight
+    def __init__(self, x, weight, wide=False):
+        self.x, self.weight, self.wide = x, weight, wide         # wide: many tokens, the paired kernel
         self.shape = (x.shape[0], weight.shape[0])
         self.dtype, self.device = x.dtype, x.device
 
@@ -148,11 +149,13 @@ class PendingProduct:
         return min(gemm_splits(M, self.weight.shape[0], K, partials=True), FUSED_MAX_SPLITS)
 
     def partials(self):
-        if self.splits() > 1:
+        if not self.wide and self.splits() > 1:
             return _linear_tcgen05(self.x, self.weight, False, partials_only=True)
         return self.materialize()
 
     def materialize(self):
+        if self.wide:
+            return _linear_pair(self.x, self.weight)
         return _linear_tcgen05(self.x, self.weight, False)
 
 
@@ -323,6 +326,23 @@ def _tcgen05_ok(x, weight):
             and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
+#: From this many tokens on the gate/up product runs on the paired tcgen05 kernel with the
+#: activation in its epilogue.  Measured inside a whole prefill of Qwen3-8B shapes, warm, against
+#: the library product + activation kernel: 2,048 tokens +3 %, 4,096 tokens +4.5 %.
+PAIR_GATED_MIN_TOKENS = 2048
+#: From this many tokens on every product of a layer runs on the paired kernel, with the residual
+#: add, the norm factor and the activation in the products' epilogues.  Off: inside a whole
+#: prefill the other three products are 2 to 8 % slower than the library's with the kernels
+#: between them (their tiles do not fill whole waves of SM pairs); tests turn it on.
+PAIR_MIN_TOKENS = 10 ** 9
+
+
+def _pair_ok(x, weight):
+    return (x.shape[1] % 8 == 0 and weight.shape[0] % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1
+            and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
 def _tile_t(M):
     return 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
 
@@ -387,33 +407,35 @@ def gemm_pairs() -> int:
     return _pair_count[0]
 
 
-def _pair_workspace(lib, M, N, K, pairs, device):
-    """Scratch for the partial tiles of the last wave and their (zeroed) counters.  One buffer per
-    device, grown on demand: products of one stream run one after the other."""
+def _pair_workspace(lib, M, N, K, pairs, halves, out_float32, device):
+    """Where the parts of the cut tiles of the last wave are added up, and their counters: zero
+    between products (the kernel leaves them so).  One buffer per device, grown on demand:
+    products of one stream run one after the other."""
     counters = c_int(0)
     lib.ts_gemm_pair_scratch.restype = c_longlong
-    need = lib.ts_gemm_pair_scratch(c_int(M), c_int(N), c_int(K), c_int(pairs), ctypes.byref(counters))
+    need = lib.ts_gemm_pair_scratch(c_int(M), c_int(N), c_int(K), c_int(pairs), c_int(halves), c_int(1 if out_float32 else 0), ctypes.byref(counters))
     key = str(device)
     have = _pair_scratch.get(key)
     if have is None or have[0].numel() < need or have[1].numel() < counters.value:
         grow = max(need, have[0].numel() if have else 0, 1)
-        have = (torch.empty(grow, dtype=torch.float32, device=device),
+        have = (torch.zeros(grow, dtype=torch.float32, device=device),
                 torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=device))
         _pair_scratch[key] = have
     return have
 
 
 def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, residual=None, norm_weight=None,
-                 pairs=None):
+                 pairs=None, halves=0):
     """The product for many tokens on pairs of SMs (csrc/gemm_pair_tcgen05.cu).  Plain: returns
     out [M, N]; ``bias`` [N]; ``scale`` the ScaledRows whose ``data`` is ``x``.  ``gated``:
     activation code + 1, out [M, N / 2].  ``residual`` (float32 [M, N], in place) with
-    ``norm_weight``: returns (hprime, sumsq) of the new residual."""
+    ``norm_weight``: returns (hprime, sumsq) of the new residual.  ``halves``: tiles of 256 (1) or
+    512 (2) weight rows, 0: the kernel's estimate decides."""
     M, K = x.shape
     N = weight.shape[0]
     lib = _gemm_pair()
     pairs = pairs or gemm_pairs()
-    scratch, counters = _pair_workspace(lib, M, N, K, pairs, x.device)
+    scratch, counters = _pair_workspace(lib, M, N, K, pairs, halves, out_float32, x.device)
     out = hprime = sumsq = None
     stride = -(-M // 4) * 4
     if residual is not None:
@@ -431,7 +453,7 @@ def _linear_pair(x, weight, out_float32=False, bias=None, scale=None, gated=0, r
         c_int(gated), _ptr(residual), _ptr(norm_weight),
         c_int(_vec_flag(norm_weight, torch.bfloat16) if norm_weight is not None else 0), _ptr(hprime), _ptr(sumsq),
         c_int(stride), _ptr(scratch), c_longlong(scratch.numel()), _ptr(counters), c_int(counters.numel()),
-        c_int(pairs), _stream()))
+        c_int(pairs), c_int(halves), _stream()))
     if residual is not None:
         return hprime, sumsq
     return out
@@ -529,6 +551,9 @@ def _product_add_residual(pending, residual, weight, eps):
     M, K = x.shape
     N = w.shape[0]
     tiles = -(-N // 128)
+    if pending.wide:
+        hprime, sumsq = _linear_pair(x, w, residual=residual, norm_weight=weight)
+        return ScaledRows(hprime, sumsq, tiles, eps)
     hprime = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     sumsq = torch.empty(tiles, 16, dtype=torch.float32, device=x.device)
     lib = _gemm_tcgen05()
@@ -610,6 +635,11 @@ def gated_linear(x, weight, activation="silu", block=0):
     ScaledRows that add_rmsnorm returned."""
     rows = x.data if isinstance(x, ScaledRows) else x
     N, K = weight.shape
+    if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
+            and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _pair_ok(rows, weight)
+            and rows.shape[0] >= (PAIR_MIN_TOKENS if rows is not x else min(PAIR_MIN_TOKENS, PAIR_GATED_MIN_TOKENS))):
+        _cuda(rows, weight)
+        return _linear_pair(rows, weight, gated=ACTIVATIONS[activation] + 1, scale=x if rows is not x else None)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _tcgen05_ok(rows, weight)
             and rows.shape[0] <= FUSED_MAX_TOKENS          # measured: at 64 tokens the epilogue costs 9 % of the step
@@ -950,6 +980,10 @@ def linear(x, weight, bias=None, out_float32=False, allow_partials=False, allow_
     if bias is not None and tuple(bias.shape) != (N,):
         raise ValueError(f"linear: bias {tuple(bias.shape)} does not fit {N} outputs")
     x = materialize(x)
+    if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and M >= PAIR_MIN_TOKENS and _pair_ok(x, weight):
+        if allow_pending and scale is None and bias is None and not out_float32:
+            return PendingProduct(x, weight, wide=True)
+        return _linear_pair(x, weight, out_float32, bias=bias, scale=scale)
     if x.dtype == torch.bfloat16 and _tcgen05_ok(x, weight) and (scale is None or M <= FUSED_MAX_TOKENS):
         if bias is not None:
             if scale is not None:
