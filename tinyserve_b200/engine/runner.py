@@ -39,6 +39,7 @@ PENDING = -1     # a token id that is still on the device (see ModelRunner.slot_
 # (tinyserve's buckets are every 16 tokens up to 512, serve.py:1951-1962).
 MIXED_GRAPH_TOKENS = (16, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 MIXED_GRAPHS_KEPT = 32           # captured shapes kept; the one replayed longest ago goes first
+MIXED_GRAPH_SIGHTINGS = 2        # steps of a shape that run eagerly before the shape is captured
 
 
 class Prepared:
@@ -84,6 +85,7 @@ class ModelRunner:
         self.mixed_graphs_enabled = False
         self.mixed_graph_replays = 0
         self._graph_pool = None
+        self._capture_stream = None
         self.kernel_launches = 0
         self.last_upload_bytes = 0
         if verbose:
@@ -515,25 +517,36 @@ class ModelRunner:
         return None if bound is None else (tokens, requests, rows, bound)
 
     def _mixed_graph(self, prep):
-        """The graph of ``prep``'s captured shape.  The first step of a shape runs eagerly, in the
-        padded shape (which is also the warm-up that a capture needs); the second is captured,
-        with its own inputs on the device, and replayed; later ones are replayed."""
+        """The graph of ``prep``'s captured shape.  The first steps of a shape run eagerly, in the
+        padded shape (which is also the warm-up that a capture needs: a shape that comes up once
+        or twice is not worth a capture); the next is captured, with its own inputs on the
+        device, and replayed; later ones are replayed."""
         key = prep.mixed
-        seen = self.mixed_graphs.get(key)
-        if seen is None:
-            self.mixed_graphs[key] = "seen"
+        seen = self.mixed_graphs.get(key, 0)
+        if isinstance(seen, int) and seen < MIXED_GRAPH_SIGHTINGS:
+            self.mixed_graphs[key] = seen + 1
             return None
-        if seen == "seen":
+        if isinstance(seen, int):
             tokens, requests = key[0], key[1]
             ctx = self._bind_device_views(prep.ctx)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph, pool=self._graph_pool), ops.stream_scope():
-                self._tables_step(requests)
-                out = self._forward(ctx)
+            # (capture_begin / capture_end themselves: torch.cuda.graph() would also synchronise
+            # the device, collect garbage and empty the allocator's cache, 30 ms a capture)
+            if self._capture_stream is None:
+                self._capture_stream = torch.cuda.Stream(self.device)
+            self._capture_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._capture_stream), ops.stream_scope():
+                graph.capture_begin(pool=self._graph_pool) if self._graph_pool is not None else graph.capture_begin()
+                try:
+                    self._tables_step(requests)
+                    out = self._forward(ctx)
+                finally:
+                    graph.capture_end()
+            torch.cuda.current_stream(self.device).wait_stream(self._capture_stream)
             self._graph_pool = self._graph_pool or graph.pool()
             seen = (graph, out, tokens, ops.launch_count() - before)
-            captured = [k for k, v in self.mixed_graphs.items() if v != "seen"]
+            captured = [k for k, v in self.mixed_graphs.items() if not isinstance(v, int)]
             if len(captured) >= MIXED_GRAPHS_KEPT:
                 del self.mixed_graphs[captured[0]]
         # (the dict keeps the order of insertion: a replayed shape moves to the end)

@@ -328,8 +328,11 @@ def _tcgen05_ok(x, weight):
 
 #: From this many tokens on the gate/up product runs on the paired tcgen05 kernel with the
 #: activation in its epilogue.  Measured inside a whole prefill of Qwen3-8B shapes, warm, against
-#: the library product + activation kernel: 2,048 tokens +3 %, 4,096 tokens +4.5 %.
+#: the library product + activation kernel: 2,048 tokens +3 %, 4,096 tokens +4.5 %.  Only for
+#: rows of PAIR_GATED_MIN_K elements and more: a tile's epilogue (9 to 14 us beside running MMAs)
+#: hides behind a mainloop of 64 slices of K, not behind one of 16 (Qwen3-0.6B shapes: slower).
 PAIR_GATED_MIN_TOKENS = 2048
+PAIR_GATED_MIN_K = 4096
 #: From this many tokens on every product of a layer runs on the paired kernel, with the residual
 #: add, the norm factor and the activation in the products' epilogues.  Off: inside a whole
 #: prefill the other three products are 2 to 8 % slower than the library's with the kernels
@@ -637,7 +640,8 @@ def gated_linear(x, weight, activation="silu", block=0):
     N, K = weight.shape
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _pair_ok(rows, weight)
-            and rows.shape[0] >= (PAIR_MIN_TOKENS if rows is not x else min(PAIR_MIN_TOKENS, PAIR_GATED_MIN_TOKENS))):
+            and (rows.shape[0] >= PAIR_MIN_TOKENS
+                 or (rows is x and rows.shape[0] >= PAIR_GATED_MIN_TOKENS and K >= PAIR_GATED_MIN_K))):
         _cuda(rows, weight)
         return _linear_pair(rows, weight, gated=ACTIVATIONS[activation] + 1, scale=x if rows is not x else None)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
