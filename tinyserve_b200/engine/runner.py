@@ -38,7 +38,7 @@ PENDING = -1     # a token id that is still on the device (see ModelRunner.slot_
 # largest a step is busy enough with arithmetic that its launches hardly matter, and runs eagerly
 # (tinyserve's buckets are every 16 tokens up to 512, serve.py:1951-1962).
 MIXED_GRAPH_TOKENS = (16, 32, 48, 64, 96, 128, 192, 256, 384, 512)
-MIXED_GRAPHS_KEPT = 32           # captured shapes kept; the one replayed longest ago goes first
+MIXED_GRAPHS_KEPT = 16           # captured shapes kept; the one replayed longest ago goes first
 MIXED_GRAPH_SIGHTINGS = 2        # steps of a shape that run eagerly before the shape is captured
 
 
@@ -536,13 +536,22 @@ class ModelRunner:
             if self._capture_stream is None:
                 self._capture_stream = torch.cuda.Stream(self.device)
             self._capture_stream.wait_stream(torch.cuda.current_stream(self.device))
-            with torch.cuda.stream(self._capture_stream), ops.stream_scope():
-                graph.capture_begin(pool=self._graph_pool) if self._graph_pool is not None else graph.capture_begin()
-                try:
-                    self._tables_step(requests)
-                    out = self._forward(ctx)
-                finally:
-                    graph.capture_end()
+            try:
+                with torch.cuda.stream(self._capture_stream), ops.stream_scope():
+                    graph.capture_begin(pool=self._graph_pool) if self._graph_pool is not None else graph.capture_begin()
+                    try:
+                        self._tables_step(requests)
+                        out = self._forward(ctx)
+                    finally:
+                        graph.capture_end()
+            except torch.cuda.OutOfMemoryError:
+                # no room left for another graph's buffers beside the cache: steps with portions
+                # run eagerly from now on (this one too: the caller gets no graph)
+                self.mixed_graphs_enabled = False
+                self.mixed_graphs.pop(key, None)
+                del graph
+                torch.cuda.current_stream(self.device).wait_stream(self._capture_stream)
+                return None
             torch.cuda.current_stream(self.device).wait_stream(self._capture_stream)
             self._graph_pool = self._graph_pool or graph.pool()
             seen = (graph, out, tokens, ops.launch_count() - before)
