@@ -1,12 +1,13 @@
 // out[M, N] = x[M, K] * W[N, K]^T for many tokens (prompt portions: M from 65 to thousands),
 // bfloat16 operands, 32-bit accumulation, on the 5th-generation tensor cores with pairs of SMs.
 //
-// Two blocks on neighbouring SMs (a cluster of 2) share one tile of 256 tokens x 256 weight rows:
-// tcgen05.mma.cta_group::2 reads 128 token rows (A) and 128 weight rows (half of B) from each
-// block's shared memory and leaves 128 x 256 accumulators in each block's tensor memory, so every
-// SM loads and reads only half of the weight tile.  Per 64-wide slice of K each block's loader
-// thread issues two TMA loads (128-byte swizzle, no multicast) into a ring of five stages; both
-// blocks' loads complete on the first block's mbarrier.  Four threads of the first block issue
+// Two blocks on neighbouring SMs (a cluster of 2) share one tile of 256 tokens x 256 weight rows
+// (or x 512, see Cfg): tcgen05.mma.cta_group::2 reads 128 token rows (A) and 128 weight rows
+// (half of B) from each block's shared memory and leaves 128 x 256 accumulators in each block's
+// tensor memory, so every SM loads and reads only half of the weight tile.  Per 64-wide slice of
+// K each block's loader thread issues its TMA loads (128-byte swizzle, every block its own: no
+// cluster-wide copies) into a ring of five stages; both blocks' loads complete on the first
+// block's mbarrier.  Four threads of the first block issue
 // the four K steps of a stage (one thread issues a tcgen05.mma every 196 cycles at most, measured,
 // and an MMA of this size takes 128), all into the same accumulator, and commit the stage back to
 // both loaders.  Accumulators are double buffered (2 x 256 of the 512 columns): four epilogue
