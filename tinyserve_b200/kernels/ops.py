@@ -332,6 +332,7 @@ def _tcgen05_ok(x, weight):
 #: rows of PAIR_GATED_MIN_K elements and more: a tile's epilogue (9 to 14 us beside running MMAs)
 #: hides behind a mainloop of 64 slices of K, not behind one of 16 (Qwen3-0.6B shapes: slower).
 PAIR_GATED_MIN_TOKENS = 2048
+PAIR_GATED_MAX_TOKENS = 6144     # (at 8,192 tokens the library's product is 11 % faster, which is what the activation kernel costs)
 PAIR_GATED_MIN_K = 4096
 #: From this many tokens on every product of a layer runs on the paired kernel, with the residual
 #: add, the norm factor and the activation in the products' epilogues.  Off: inside a whole
@@ -641,7 +642,8 @@ def gated_linear(x, weight, activation="silu", block=0):
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
             and rows.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _pair_ok(rows, weight)
             and (rows.shape[0] >= PAIR_MIN_TOKENS
-                 or (rows is x and rows.shape[0] >= PAIR_GATED_MIN_TOKENS and K >= PAIR_GATED_MIN_K))):
+                 or (rows is x and PAIR_GATED_MIN_TOKENS <= rows.shape[0] <= PAIR_GATED_MAX_TOKENS
+                     and K >= PAIR_GATED_MIN_K))):
         _cuda(rows, weight)
         return _linear_pair(rows, weight, gated=ACTIVATIONS[activation] + 1, scale=x if rows is not x else None)
     if (block == GATED_BLOCK and N % 128 == 0 and isinstance(rows, torch.Tensor)
