@@ -421,6 +421,10 @@ def _pair_workspace(lib, M, N, K, pairs, halves, out_float32, device):
     key = str(device)
     have = _pair_scratch.get(key)
     if have is None or have[0].numel() < need or have[1].numel() < counters.value:
+        if torch.cuda.is_current_stream_capturing():
+            # (a buffer made during a capture belongs to the graph's pool: it must not outlive it here)
+            raise RuntimeError("the paired product's scratch would have to grow inside a graph capture: "
+                               "run the shape once before it is captured")
         grow = max(need, have[0].numel() if have else 0, 1)
         have = (torch.zeros(grow, dtype=torch.float32, device=device),
                 torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=device))
