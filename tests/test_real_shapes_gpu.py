@@ -174,6 +174,32 @@ def test_products_of_many_tokens_on_the_paired_kernel(model, tmp_path, monkeypat
     assert ops.gemm_pair_error() == 0
 
 
+def test_a_long_prompt_takes_the_paired_gate_up_product(model, tmp_path):
+    """A prompt of 2,200 tokens at the layer sizes of Qwen3-8B, whole and in portions of 2,048 and
+    152: the gate/up product of the long step runs on the paired tcgen05 kernel with the
+    activation in its epilogue (what the engine does by itself from 2,048 tokens on), the short
+    portion on the library's.  Both against the plain implementation."""
+    if model["name"] != "flagship_layers":
+        pytest.skip("the paired product takes rows of 4,096 elements and more")
+    from tinyserve_b200.kernels import ops
+    ids = random_ids(model["cfg"]["vocab_size"], 2200, seed=77)
+    with torch.no_grad():
+        ref = {"long": plain.logits(model["cfg"], model["weights"], ids).cpu()}
+    reqs = {"long": ids}
+    calls = []
+    original = ops._linear_pair
+    ops._linear_pair = lambda *a, **k: (calls.append(k.get("gated", 0)), original(*a, **k))[1]
+    try:
+        check(dict(model, requests=reqs), "bfloat16", schedule_whole(reqs), tmp_path / "whole", 64, ref=ref)
+        assert calls and all(calls), "the long step's gate/up products ran on the paired kernel, gated"
+        n = len(calls)
+        check(dict(model, requests=reqs), "bfloat16", schedule_portions(reqs, sizes=(2048, 152)), tmp_path / "portions", 64, ref=ref)
+        assert len(calls) == 2 * n, "the portion of 2,048 tokens too, the one of 152 not"
+    finally:
+        ops._linear_pair = original
+    assert ops.gemm_pair_error() == 0
+
+
 @pytest.mark.parametrize("page", [16, 64])
 def test_steps_with_portions_replayed_from_graphs(model, page, tmp_path):
     """Steps of up to 512 tokens that hold prompt portions, padded to captured shapes and replayed
