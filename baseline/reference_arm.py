@@ -164,6 +164,27 @@ def burst(serve, raw: dict, seed: int) -> dict:
             "burst_0p6b_gen_tok_s": round(generated / dt, 1), "burst_0p6b_seconds": round(dt, 3)}
 
 
+def long_context(serve, raw: dict, steps: int, warmup: int, seed: int) -> dict:
+    """Decode at batch 8 with 4,096 and 16,384 tokens of context (the prompt fills it but for the
+    decoded tokens), through an engine of its own with room for them."""
+    V = raw["vocab_size"]
+    h, L = raw["hidden_size"], raw["num_hidden_layers"]
+    H, Hkv, D, I = (raw["num_attention_heads"], raw["num_key_value_heads"], raw["head_dim"], raw["intermediate_size"])
+    weight_bytes = 2 * (L * ((H + 2 * Hkv) * D * h + h * H * D + 3 * I * h) + 2 * V * h)
+    folder = _scratch_dir(int(weight_bytes * 1.05) + (1 << 30))
+    try:
+        write_model_folder(raw, folder, seed)
+        engine = serve.Engine(serve.Config(model=folder, max_model_len=16384 + 256, max_num_seqs=8,
+                                           max_num_batched_tokens=4096))
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    out = {}
+    for name, ctx in (("decode_b8_ctx4k_tok_s", 4096), ("decode_b8_ctx16k_tok_s", 16384)):
+        r = _decode(serve, engine, 8, ctx - warmup - steps - 8, steps, warmup, V, seed + ctx)
+        out[name] = round(r["tok_s"], 1)
+    return out
+
+
 def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int, prompt_len: int,
         prefill_tokens: int, points: bool, peaks: dict, clock_sampler=None, burst_raw: dict = None) -> dict:
     """The reference's JSON line as a dict; raises if the reference cannot start."""
@@ -229,4 +250,10 @@ def run(raw: dict, batch: int, steps: int, warmup: int, seed: int, context: int,
                 line["points"].update(burst(serve, burst_raw, seed))
             except Exception as exc:              # noqa: BLE001 - named in the line, the rest still prints
                 line["points"]["burst_0p6b_error"] = f"{type(exc).__name__}: {exc}"[:200]
+            gc.collect()
+            torch.cuda.empty_cache()
+            try:
+                line["points"].update(long_context(serve, raw, min(steps, 32), warmup, seed))
+            except Exception as exc:              # noqa: BLE001
+                line["points"]["long_context_error"] = f"{type(exc).__name__}: {exc}"[:200]
     return line
