@@ -85,6 +85,31 @@ def test_preemption_recomputes_the_same_tokens(tmp_path, async_scheduling):
     assert tight.runner.manager.num_free_pages() == 9
 
 
+def test_many_requests_with_graphs_of_mixed_steps_under_preemption(tmp_path):
+    """Eighty requests of 1 to 120 tokens through a pool too small for them, with 48 tokens a
+    step: steps with prompt portions are padded to captured shapes and replayed from graphs,
+    requests are pre-empted and recomputed, and every request still gets the tokens that the
+    engine without graphs and with room for all gives it (32-bit, greedy)."""
+    import random
+    from tinyserve_b200 import SamplingParams
+    folder = make_model_dir(tmp_path, "B", seed=5)
+    rng = random.Random(1)
+    prompts = [random_ids(384, rng.randint(1, 120), seed=i) for i in range(80)]
+    params = [SamplingParams(temperature=0.0, max_tokens=rng.randint(1, 40), repetition_penalty=1.0, ignore_eos=True)
+              for _ in prompts]
+    kw = dict(max_model_len=192, block_size=8, max_num_seqs=12)
+    roomy = llm_for(folder, "float32", async_scheduling=False, use_cuda_graphs=False, num_blocks=400,
+                    max_num_batched_tokens=256, **kw).generate(prompts, params)
+    tight = llm_for(folder, "float32", async_scheduling=True, use_cuda_graphs=True, num_blocks=60,
+                    max_num_batched_tokens=48, **kw)
+    outs = tight.generate(prompts, params)
+    assert tight.runner.mixed_graph_replays > 20, "steps with portions were replayed from graphs"
+    assert sum(o.was_preempted for o in outs) > 0
+    assert [o.token_ids for o in outs] == [o.token_ids for o in roomy]
+    tight.runner.manager.check_invariants()
+    assert tight.runner.manager.num_free_pages() == 60
+
+
 def test_host_one_step_ahead_gives_the_same_tokens(tmp_path):
     """The loop that schedules step n+1 while step n runs (tokens fed back on the device) and the
     one-step-at-a-time loop produce the same tokens, with mixed sampling settings, chunked
