@@ -643,6 +643,45 @@ def test_gemm_pair(M, N, K, pairs, halves, f32_out, with_bias):
     assert int(o._pair_scratch[str(x.device)][1].abs().sum()) == 0, "tile counters returned to zero"
 
 
+@pytest.mark.parametrize("M,N,K,pairs", [(300, 1000, 12288, 7), (700, 1536, 16384, 20), (256, 2304, 20480, 74)])
+@pytest.mark.parametrize("mode", ["plain", "gated", "residual"])
+def test_gemm_pair_cuts_the_tiles_of_its_last_wave(M, N, K, pairs, mode):
+    """With a long K the tiles of the last, partial wave are cut along K: the pairs add their
+    parts to a sum in global memory (scratch, or the residual itself) and the block that arrives
+    last finishes the tile.  The scratch and its counters are zero again afterwards."""
+    import ctypes
+    o = ops()
+    if mode == "gated" and N % 128:
+        pytest.skip("the gated form takes whole blocks of 64 gate and 64 up rows")
+    lib = o._gemm_pair()
+    lib.ts_gemm_pair_scratch.restype = ctypes.c_longlong
+    need = lib.ts_gemm_pair_scratch(ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K), ctypes.c_int(pairs),
+                                    ctypes.c_int(1), ctypes.c_int(0), None)
+    assert need > 0, "this size is meant to cut tiles"
+    x, w = rnd(M, K, seed=1, dtype=torch.bfloat16), rnd(N, K, seed=2, dtype=torch.bfloat16, scale=0.05)
+    want = x.double() @ w.double().T
+    if mode == "plain":
+        out = o._linear_pair(x, w, pairs=pairs, halves=1)
+    elif mode == "gated":
+        out = o._linear_pair(x, w, gated=1, pairs=pairs, halves=1)
+        full = want.view(M, N // 128, 2, 64)
+        want = torch.nn.functional.silu(full[:, :, 0].reshape(M, N // 2)) * full[:, :, 1].reshape(M, N // 2)
+    else:
+        res, wn = rnd(M, N, seed=3, scale=2.0), rnd(N, seed=4) + 1
+        r1 = res.clone()
+        hprime, sumsq = o._linear_pair(x, w, residual=r1, norm_weight=wn, pairs=pairs, halves=1)
+        v = res.double() + want
+        # (a 32-bit sum over 12 to 20 thousand products: a few 1e-5 of the largest value)
+        assert (r1.double() - v).abs().max().item() < 5e-5 * v.abs().max().item(), "32-bit residual"
+        out = o.ScaledRows(hprime, sumsq, -(-N // 128), 1e-5).materialize()
+        want = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + 1e-5) * wn.double()
+    torch.cuda.synchronize()
+    assert o.gemm_pair_error() == 0
+    close(out, want, torch.bfloat16, "paired gemm with cut tiles")
+    scratch, counters = o._pair_scratch[str(x.device)]
+    assert float(scratch.abs().max()) == 0.0 and int(counters.abs().sum()) == 0, "scratch and counters returned to zero"
+
+
 @pytest.mark.parametrize("M,N,K", [(65, 128, 72), (200, 384, 520), (512, 1024, 1024), (1100, 6144, 256)])
 @pytest.mark.parametrize("pairs", [74, 3])
 @pytest.mark.parametrize("halves", [1, 2])
