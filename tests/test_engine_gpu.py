@@ -110,6 +110,24 @@ def test_many_requests_with_graphs_of_mixed_steps_under_preemption(tmp_path):
     assert tight.runner.manager.num_free_pages() == 60
 
 
+def test_a_capture_without_memory_turns_the_graphs_of_mixed_steps_off(tmp_path, monkeypatch):
+    """A capture of a mixed step that runs out of memory leaves the engine as it was, with the
+    feature off: the step runs eagerly, and so do all later ones."""
+    folder = make_model_dir(tmp_path, "A", seed=33)
+    prompts = [random_ids(256, n, seed=n) for n in (30, 28, 26, 31, 29, 27)]
+    want = llm_for(folder, "float32", async_scheduling=False).generate(prompts, greedy(12))
+    llm = llm_for(folder, "float32", use_cuda_graphs=True, max_num_batched_tokens=32, max_num_seqs=3)
+
+    def no_memory(self, *args, **kwargs):
+        raise torch.cuda.OutOfMemoryError("no memory for this capture (simulated)")
+
+    monkeypatch.setattr(torch.cuda.CUDAGraph, "capture_begin", no_memory)
+    assert llm.runner.mixed_graphs_enabled
+    outs = llm.generate(prompts, greedy(12))
+    assert not llm.runner.mixed_graphs_enabled and llm.runner.mixed_graph_replays == 0
+    assert [o.token_ids for o in outs] == [o.token_ids for o in want]
+
+
 def test_host_one_step_ahead_gives_the_same_tokens(tmp_path):
     """The loop that schedules step n+1 while step n runs (tokens fed back on the device) and the
     one-step-at-a-time loop produce the same tokens, with mixed sampling settings, chunked
